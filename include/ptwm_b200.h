@@ -1,0 +1,150 @@
+/* C ABI of libptwm_b200.so — B200 (sm_100a) decode/encode of ptwm containers.
+ *
+ * Two groups of entry points:
+ *
+ *  1. The native-extension symbols the reference's loader binds
+ *     (crates/ptwm-core/src/flavor/native.rs of khwstolle/ptwm).  Exporting
+ *     them makes this library a drop-in `hardware_backend` and `plane_codec`
+ *     contribution: one plane payload per call, synchronous.
+ *
+ *  2. The batched container API (ptwm_b200_*): parse a whole container once on
+ *     the host, then decode any subset of its tensors with a few kernel
+ *     launches.  This is what the reference's ContainerReader::decode_model /
+ *     decode_tensor (crates/ptwm-core/src/container.rs:1766-2196) do on the
+ *     CPU, and what ptwm_b200.Decompressor calls.
+ *
+ * Conventions shared by both groups (native.rs:105-129,634-657): plain
+ * pointers and sizes only; device pointers travel as uint64_t; the caller owns
+ * every buffer; return values >= 0 mean success (bytes written where that
+ * makes sense), negative values are error codes.
+ */
+#ifndef PTWM_B200_H
+#define PTWM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Return codes (native.rs:634-657). */
+#define PTWM_RC_INVALID_INPUT      (-1)
+#define PTWM_RC_BUFFER_TOO_SMALL   (-2)
+#define PTWM_RC_MISSING_CAPABILITY (-3)
+#define PTWM_RC_MISSING_NATIVE_DEP (-4)
+#define PTWM_RC_UNSUPPORTED        (-5)
+#define PTWM_RC_INTERNAL           (-6)
+#define PTWM_RC_CUDA               (-7)   /* CUDA runtime error; decoded as InternalError by the reference */
+#define PTWM_RC_CORRUPT            (-8)   /* payload failed to decode or an integrity check failed */
+
+/* ---- 1. reference native-extension ABI ---------------------------------- */
+
+/* kind = "hardware_backend".  Replaces HardwareBackendCudaStreamHandleFn
+ * (native.rs:112): the library's process-persistent stream for the device,
+ * as an integer; 0 = failure. */
+uint64_t ptwm_hardware_backend_v1_cuda_stream_handle(uint32_t device_ordinal);
+
+/* Replaces HardwareBackendCudaDispatchDecodeFn (native.rs:130-141).  Decodes
+ * one plane payload exactly as stored in a plane record or chunk frame
+ * (TAG|len|blob for huffman / rans / tans, bare bytes for identity and
+ * order1_scale_ac) from device memory into device memory and returns the
+ * decoded byte count.  codec_id is the 32-byte canonical id of a built-in
+ * codec (extension/id.rs:21-31).  state_ptr is host memory and is not read
+ * when state_len == 0.  Returns after the kernel has completed. */
+int64_t ptwm_hardware_backend_v1_dispatch_decode_cuda(uint8_t state_format_version, const uint8_t* state_ptr, size_t state_len,
+                                                      const uint8_t* codec_id_ptr, size_t codec_id_len, uint64_t in_dev_ptr, size_t in_len,
+                                                      uint64_t out_dev_ptr, size_t out_len, uint32_t device_ordinal);
+
+/* kind = "plane_codec".  Replace PlaneCodecCudaStreamHandleFn / PlaneCodecCudaDecodeFn /
+ * PlaneCodecCudaEncodeFn (native.rs:150,163-174,185-197). */
+uint64_t ptwm_plane_codec_v1_cuda_stream_handle(uint32_t device_ordinal);
+int64_t ptwm_plane_codec_v1_decode_cuda(uint8_t state_format_version, const uint8_t* state_ptr, size_t state_len, const uint8_t* codec_id_ptr,
+                                        size_t codec_id_len, uint64_t in_dev_ptr, size_t in_len, uint64_t out_dev_ptr, size_t out_cap,
+                                        uint32_t device_ordinal);
+int64_t ptwm_plane_codec_v1_encode_cuda(uint8_t state_format_version, const uint8_t* state_ptr, size_t state_len, const uint8_t* codec_id_ptr,
+                                        size_t codec_id_len, uint64_t in_dev_ptr, size_t in_len, uint64_t out_dev_ptr, size_t out_cap,
+                                        uint64_t* needed_out, uint32_t device_ordinal);
+
+/* Host-buffer pair every plane_codec library must export (PlaneCodecFn /
+ * PlaneCodecStatefulFn, native.rs:62-83).  They stage through device 0 and
+ * run the same kernels; the flat ABI carries no codec id, so they speak the
+ * rANS plane payload (TAG|len|blob), the codec the reference's own decode
+ * benchmark forces (benchmarks/decode_throughput.py:41-42). */
+int64_t ptwm_plane_codec_v1_encode(const uint8_t* in, size_t in_len, uint8_t* out, size_t out_len);
+int64_t ptwm_plane_codec_v1_decode(const uint8_t* in, size_t in_len, uint8_t* out, size_t out_len);
+int64_t ptwm_plane_codec_v1_decode_stateful(uint8_t state_version, const uint8_t* state, size_t state_len, const uint8_t* in, size_t in_len,
+                                            uint8_t* out, size_t out_cap);
+
+/* ---- 2. batched container API ------------------------------------------- */
+
+typedef struct ptwm_b200_container ptwm_b200_container;
+typedef struct ptwm_b200_plan ptwm_b200_plan;
+
+/* Message of the last failure on the calling thread. */
+const char* ptwm_b200_last_error(void);
+
+/* Parse a \x89PTWC container or a \x89PTWS frame held in host memory
+ * (ContainerReader::open, container.rs:1395-1626; compact.rs:321-405).  The
+ * bytes are only read during this call.  A frame opens as a container with one
+ * tensor named "_". */
+int64_t ptwm_b200_open(const uint8_t* blob, size_t blob_len, ptwm_b200_container** out);
+void ptwm_b200_close(ptwm_b200_container* c);
+
+typedef struct ptwm_b200_tensor_info {
+    const char* name;        /* owned by the container */
+    const char* dtype_name;  /* "" when the record stores none */
+    uint16_t dtype_code;     /* public dtype code (dtype.rs:25-50) */
+    uint8_t ndim;            /* valid when has_shape */
+    uint8_t has_shape;
+    uint8_t has_hash;        /* record carries an XXH64 payload hash */
+    uint8_t has_crc;         /* at least one plane carries a CRC-32 */
+    uint8_t supported;       /* 0: uses a chain or codec outside the hot path */
+    uint8_t kind;            /* 0 passthrough, 1 16-bit split, 2 32-bit split, 3 fp8 e4m3, 4 fp8 e5m2 */
+    uint64_t shape[8];
+    uint64_t orig_size;      /* decoded bytes */
+    uint64_t compressed;     /* plane payload bytes in the file */
+    uint64_t first_byte;     /* file span [first_byte, end_byte) holding the tensor's payload bytes */
+    uint64_t end_byte;
+    const char* unsupported_reason;
+} ptwm_b200_tensor_info;
+
+size_t ptwm_b200_tensor_count(const ptwm_b200_container* c);
+int64_t ptwm_b200_tensor_info_get(const ptwm_b200_container* c, size_t index, ptwm_b200_tensor_info* info);
+
+/* Build the launch plan for a subset of tensors (all when indices == NULL).
+ * Outputs go into one arena at 256-byte aligned offsets in the order given. */
+int64_t ptwm_b200_plan_create(const ptwm_b200_container* c, const uint32_t* indices, size_t n, ptwm_b200_plan** out);
+void ptwm_b200_plan_destroy(ptwm_b200_plan* p);
+uint64_t ptwm_b200_plan_out_bytes(const ptwm_b200_plan* p);
+uint64_t ptwm_b200_plan_scratch_bytes(const ptwm_b200_plan* p);
+uint64_t ptwm_b200_plan_out_offset(const ptwm_b200_plan* p, size_t k);   /* arena offset of the k-th planned tensor */
+/* File bytes [lo, hi) the plan reads; a caller may keep only that span on the
+ * device and pass blob_dev_ptr = span_dev_ptr - lo with blob_first = lo. */
+void ptwm_b200_plan_blob_span(const ptwm_b200_plan* p, uint64_t* lo, uint64_t* hi);
+/* Algorithmic traffic of one run: compressed payload bytes read, decoded bytes written, kernels launched. */
+void ptwm_b200_plan_stats(const ptwm_b200_plan* p, uint64_t* bytes_read, uint64_t* bytes_written, uint32_t* launches);
+
+#define PTWM_B200_VERIFY_CRC  1u   /* check the plane CRC-32s the records carry */
+#define PTWM_B200_VERIFY_HASH 2u   /* check the XXH64 payload hashes the records carry */
+#define PTWM_B200_NO_SYNC     4u   /* enqueue only; call ptwm_b200_plan_finish later */
+
+/* Decode the planned tensors.  blob_dev_ptr addresses file offset 0 of the
+ * container on the device (see ptwm_b200_plan_blob_span), of which bytes
+ * [blob_first, blob_first + blob_len) are resident.  stream: a cudaStream_t as
+ * integer, 0 = the library's stream for the device.  Without
+ * PTWM_B200_NO_SYNC the call returns after completion with all checks done
+ * (ContainerReader::decode_model semantics, container.rs:1766-1780). */
+int64_t ptwm_b200_plan_run(ptwm_b200_plan* p, uint64_t blob_dev_ptr, uint64_t blob_first, uint64_t blob_len, uint64_t out_dev_ptr, uint64_t out_cap,
+                           uint64_t scratch_dev_ptr, uint64_t scratch_cap, uint32_t flags, uint32_t device_ordinal, uint64_t stream);
+/* Wait for an enqueued run and evaluate decode status and integrity checks. */
+int64_t ptwm_b200_plan_finish(ptwm_b200_plan* p, uint32_t flags, uint32_t device_ordinal, uint64_t stream);
+
+/* CRC-32 computed the way the verification kernel does it (per-run remainders,
+ * GF(2) shifts, XOR fold), on the host, for testing that arithmetic without a GPU. */
+uint32_t ptwm_b200_crc32_by_runs(const uint8_t* data, size_t len, size_t run);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PTWM_B200_H */

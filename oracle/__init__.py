@@ -252,6 +252,7 @@ class TensorSpec:
     shape: Sequence[int]
     raw: bytes
     usage: str = "standard"
+    input_format: int = 2  # Format.TORCH (python/ptwm/_config.py)
 
 
 def source_params(shape, chain_dtype) -> bytes:
@@ -397,7 +398,7 @@ def write_container(specs: Sequence[TensorSpec], *, chunk_size: Optional[int] = 
         rec = bytearray()
         tflags = 0x08 | (0x01 if emit_hash else 0)
         rec.append(tflags)
-        rec += varint(chain_id) + varint(s.dtype_code) + bytes([0]) + varint(len(s.raw))
+        rec += varint(chain_id) + varint(s.dtype_code) + bytes([s.input_format]) + varint(len(s.raw))
         rec += varint(len(s.shape)) + b"".join(varint(int(d)) for d in s.shape)
         if emit_hash:
             rec += xxh64(s.raw).to_bytes(8, "little")
@@ -451,7 +452,7 @@ def write_compact(spec: TensorSpec, *, menu: Sequence[int] = (IDENTITY, HUFFMAN,
     raw = spec.raw
     out = bytearray(b"\x89PTWS")
     flags = 0x04
-    hdr = varint(spec.dtype_code) + bytes([0])
+    hdr = varint(spec.dtype_code) + bytes([spec.input_format])
     hdr += varint(len(spec.shape)) + b"".join(varint(int(d)) for d in spec.shape)
     if emit_hash:
         flags |= 0x01

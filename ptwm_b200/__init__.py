@@ -1,0 +1,12 @@
+"""ptwm_b200 — decode (and encode) of ptwm containers on NVIDIA B200.
+
+The package is a thin Python layer over ``libptwm_b200.so`` (CUDA kernels for
+sm_100a plus the host container parser and planner).  See
+``include/ptwm_b200.h`` for the C ABI.
+"""
+from ._config import DecompressionConfig, HeaderParseError, InvalidDTypeError
+from ._lib import EXPORTED_SYMBOLS, LIB_PATH, build
+from .container import NO_SYNC, VERIFY_CRC, VERIFY_HASH, ContainerHandle, DecodePlan, Decompressor, PtwmError, TensorIndex
+
+__all__ = ["DecompressionConfig", "HeaderParseError", "InvalidDTypeError", "EXPORTED_SYMBOLS", "LIB_PATH", "build", "ContainerHandle",
+           "DecodePlan", "Decompressor", "PtwmError", "TensorIndex", "VERIFY_CRC", "VERIFY_HASH", "NO_SYNC"]

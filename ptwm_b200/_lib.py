@@ -1,0 +1,97 @@
+"""ctypes binding of ``libptwm_b200.so`` (declared in ``include/ptwm_b200.h``).
+
+The library holds every CUDA kernel of the package.  There is no fallback: if
+it is missing or cannot be loaded, importing the decode/encode entry points
+fails with an error that says how to build it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libptwm_b200.so")
+_SOURCES = [os.path.join(_HERE, "csrc", f) for f in ("ptwm_b200.cu", "kernels.cuh", "format.hpp", "plan.h")] + [
+    os.path.join(_HERE, "..", "include", "ptwm_b200.h")]
+
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared"]
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile the CUDA library for sm_100a in-tree with nvcc."""
+    srcs = [s for s in _SOURCES if os.path.exists(s)]
+    stale = force or not os.path.exists(LIB_PATH) or any(os.path.getmtime(s) > os.path.getmtime(LIB_PATH) for s in srcs)
+    if stale:
+        nvcc = os.environ.get("NVCC", "nvcc")
+        cmd = [nvcc, *NVCC_FLAGS, "-o", LIB_PATH, os.path.join(_HERE, "csrc", "ptwm_b200.cu")]
+        if verbose:
+            cmd.insert(1, "-Xptxas=-v")
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+        if verbose:
+            print(res.stderr)
+    return LIB_PATH
+
+
+class TensorInfo(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("dtype_name", C.c_char_p), ("dtype_code", C.c_uint16), ("ndim", C.c_uint8), ("has_shape", C.c_uint8),
+                ("has_hash", C.c_uint8), ("has_crc", C.c_uint8), ("supported", C.c_uint8), ("kind", C.c_uint8), ("shape", C.c_uint64 * 8),
+                ("orig_size", C.c_uint64), ("compressed", C.c_uint64), ("first_byte", C.c_uint64), ("end_byte", C.c_uint64),
+                ("unsupported_reason", C.c_char_p)]
+
+
+_SIGNATURES = {
+    "ptwm_b200_last_error": (C.c_char_p, []),
+    "ptwm_b200_open": (C.c_int64, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
+    "ptwm_b200_close": (None, [C.c_void_p]),
+    "ptwm_b200_tensor_count": (C.c_size_t, [C.c_void_p]),
+    "ptwm_b200_tensor_info_get": (C.c_int64, [C.c_void_p, C.c_size_t, C.POINTER(TensorInfo)]),
+    "ptwm_b200_plan_create": (C.c_int64, [C.c_void_p, C.POINTER(C.c_uint32), C.c_size_t, C.POINTER(C.c_void_p)]),
+    "ptwm_b200_plan_destroy": (None, [C.c_void_p]),
+    "ptwm_b200_plan_out_bytes": (C.c_uint64, [C.c_void_p]),
+    "ptwm_b200_plan_scratch_bytes": (C.c_uint64, [C.c_void_p]),
+    "ptwm_b200_plan_out_offset": (C.c_uint64, [C.c_void_p, C.c_size_t]),
+    "ptwm_b200_plan_blob_span": (None, [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "ptwm_b200_plan_stats": (None, [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint32)]),
+    "ptwm_b200_plan_run": (C.c_int64, [C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint32,
+                                       C.c_uint32, C.c_uint64]),
+    "ptwm_b200_plan_finish": (C.c_int64, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint64]),
+    "ptwm_b200_crc32_by_runs": (C.c_uint32, [C.c_char_p, C.c_size_t, C.c_size_t]),
+    "ptwm_hardware_backend_v1_cuda_stream_handle": (C.c_uint64, [C.c_uint32]),
+    "ptwm_plane_codec_v1_cuda_stream_handle": (C.c_uint64, [C.c_uint32]),
+    "ptwm_hardware_backend_v1_dispatch_decode_cuda": (C.c_int64, [C.c_uint8, C.c_void_p, C.c_size_t, C.c_char_p, C.c_size_t, C.c_uint64, C.c_size_t,
+                                                                  C.c_uint64, C.c_size_t, C.c_uint32]),
+    "ptwm_plane_codec_v1_decode_cuda": (C.c_int64, [C.c_uint8, C.c_void_p, C.c_size_t, C.c_char_p, C.c_size_t, C.c_uint64, C.c_size_t, C.c_uint64,
+                                                    C.c_size_t, C.c_uint32]),
+    "ptwm_plane_codec_v1_encode_cuda": (C.c_int64, [C.c_uint8, C.c_void_p, C.c_size_t, C.c_char_p, C.c_size_t, C.c_uint64, C.c_size_t, C.c_uint64,
+                                                    C.c_size_t, C.POINTER(C.c_uint64), C.c_uint32]),
+    "ptwm_plane_codec_v1_encode": (C.c_int64, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t]),
+    "ptwm_plane_codec_v1_decode": (C.c_int64, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t]),
+    "ptwm_plane_codec_v1_decode_stateful": (C.c_int64, [C.c_uint8, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t]),
+}
+
+EXPORTED_SYMBOLS = tuple(_SIGNATURES)
+
+_lib = None
+
+
+def lib():
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: the CUDA kernels are not built. Run `python -c 'import __graft_entry__ as g; g.build()'` "
+                               "(needs nvcc); ptwm_b200 has no CPU fallback.")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def last_error() -> str:
+    return lib().ptwm_b200_last_error().decode("utf-8", "replace")

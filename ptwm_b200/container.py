@@ -1,0 +1,316 @@
+"""Container handle, decompressor and random-access index on CUDA.
+
+Host-side mirror of the reference's Python surface for the decode path:
+``ContainerHandle`` (crates/ptwm-py/src/handle.rs:157-227), ``Decompressor``
+(python/ptwm/core/_decompressor.py:38-139) and ``TensorIndex``
+(python/ptwm/random_access/__init__.py:36-143).  Same method names and
+argument meaning; the difference is where the bytes land: decoded tensors are
+CUDA ``torch.Tensor`` objects produced by the kernels in ``libptwm_b200.so``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+from typing import Iterable, Iterator, Optional, Sequence
+
+import torch
+
+from . import _lib
+from ._config import DecompressionConfig, HeaderParseError, InvalidDTypeError
+
+MAGIC_PTWS = b"\x89PTWS"
+MAGIC_PTWC = b"\x89PTWC\r\n\x1a\n"
+MAGIC_PTWM = b"\x89PTWM"
+
+# public dtype codes (crates/ptwm-core/src/dtype.rs:25-50)
+_TORCH_DTYPES = {1: torch.float32, 2: torch.float32, 4: torch.float16, 5: torch.float16, 6: torch.bfloat16, 13: torch.uint8, 15: torch.uint32,
+                 17: torch.int8, 18: torch.int16, 19: torch.int16, 20: torch.int32, 21: torch.int32, 22: torch.int64, 23: torch.int64,
+                 24: torch.bool, 29: torch.float8_e4m3fn, 30: torch.float8_e5m2}
+if hasattr(torch, "float4_e2m1fn_x2"):
+    _TORCH_DTYPES[31] = torch.float4_e2m1fn_x2
+
+VERIFY_CRC, VERIFY_HASH, NO_SYNC = 1, 2, 4
+
+
+class PtwmError(RuntimeError):
+    """A core decode error (the reference surfaces these as RuntimeError, crates/ptwm-py/src/handle.rs:46-48)."""
+
+
+def _check(rc: int) -> int:
+    if rc < 0:
+        msg = _lib.last_error()
+        raise PtwmError(msg if msg else f"libptwm_b200 error {rc}")
+    return rc
+
+
+def _as_u8_tensor(data) -> torch.Tensor:
+    """Host uint8 view of a bytes-like object or tensor, without copying where possible."""
+    if isinstance(data, torch.Tensor):
+        t = data.contiguous().view(torch.uint8).reshape(-1)
+        return t
+    mv = memoryview(data)
+    if mv.nbytes == 0:
+        return torch.empty(0, dtype=torch.uint8)
+    if mv.readonly:
+        return torch.frombuffer(bytearray(mv), dtype=torch.uint8)
+    return torch.frombuffer(mv, dtype=torch.uint8)
+
+
+class DecodePlan:
+    """Launch plan for a subset of tensors of one container (ptwm_b200_plan)."""
+
+    def __init__(self, handle: "ContainerHandle", indices: Optional[Sequence[int]] = None):
+        self.handle = handle
+        L = _lib.lib()
+        p = C.c_void_p()
+        if indices is None:
+            self.indices = list(range(len(handle)))
+            _check(L.ptwm_b200_plan_create(handle._h, None, 0, C.byref(p)))
+        else:
+            self.indices = [int(i) for i in indices]
+            arr = (C.c_uint32 * max(len(self.indices), 1))(*self.indices)
+            _check(L.ptwm_b200_plan_create(handle._h, arr, len(self.indices), C.byref(p)))
+        self._p = p
+        self.out_bytes = L.ptwm_b200_plan_out_bytes(p)
+        self.scratch_bytes = L.ptwm_b200_plan_scratch_bytes(p)
+        self.out_offsets = [L.ptwm_b200_plan_out_offset(p, k) for k in range(len(self.indices))]
+        lo, hi = C.c_uint64(), C.c_uint64()
+        L.ptwm_b200_plan_blob_span(p, C.byref(lo), C.byref(hi))
+        self.blob_span = (lo.value, hi.value)
+        r, w, n = C.c_uint64(), C.c_uint64(), C.c_uint32()
+        L.ptwm_b200_plan_stats(p, C.byref(r), C.byref(w), C.byref(n))
+        self.bytes_read, self.bytes_written, self.launches = r.value, w.value, n.value
+
+    def __del__(self):
+        if getattr(self, "_p", None):
+            _lib.lib().ptwm_b200_plan_destroy(self._p)
+            self._p = None
+
+    def run(self, blob_dev: torch.Tensor, out: torch.Tensor, scratch: Optional[torch.Tensor], *, blob_first: int = 0, flags: int = 0,
+            stream: Optional[int] = None) -> None:
+        """Enqueue (and unless NO_SYNC is set, finish) one decode pass.
+        ``blob_dev`` holds file bytes [blob_first, blob_first + len)."""
+        dev = out.device.index if out.device.index is not None else torch.cuda.current_device()
+        if stream is None:
+            stream = torch.cuda.current_stream(dev).cuda_stream
+        sp = scratch.data_ptr() if scratch is not None and scratch.numel() else 0
+        sc = scratch.numel() if scratch is not None else 0
+        _check(_lib.lib().ptwm_b200_plan_run(self._p, (blob_dev.data_ptr() - blob_first) if blob_dev.numel() else 0, blob_first, blob_dev.numel(),
+                                             out.data_ptr() if out.numel() else 0, out.numel(), sp, sc, flags, dev, stream))
+
+    def finish(self, device: int, flags: int = 0, stream: Optional[int] = None) -> None:
+        if stream is None:
+            stream = torch.cuda.current_stream(device).cuda_stream
+        _check(_lib.lib().ptwm_b200_plan_finish(self._p, flags, device, stream))
+
+    def views(self, out: torch.Tensor) -> list[torch.Tensor]:
+        """Typed, shaped views of the planned tensors inside the output arena."""
+        return [self.handle._view(i, out, off) for i, off in zip(self.indices, self.out_offsets)]
+
+
+class ContainerHandle:
+    """An opened container: parsed once on the host, decoded on the GPU.
+
+    ``device`` is the CUDA ordinal; the compressed bytes are copied there on
+    first use and stay resident for later random-access decodes."""
+
+    def __init__(self, buffer, skip_missing: bool = False, device: Optional[int] = None, verify: bool = True):
+        self._host = _as_u8_tensor(buffer)
+        n = self._host.numel()
+        if n < len(MAGIC_PTWS):
+            raise HeaderParseError("too short to be a .ptwm container")
+        head = bytes(self._host[:9].tolist())
+        if head.startswith(MAGIC_PTWM) and not head.startswith(MAGIC_PTWC) and not head.startswith(MAGIC_PTWS):
+            raise PtwmError("legacy \\x89PTWM layout is not read by the CUDA backend; transcode to the compact layout")
+        if not (head.startswith(MAGIC_PTWS) or head.startswith(MAGIC_PTWC)):
+            raise HeaderParseError("not a .ptwm container")
+        self._h = C.c_void_p()
+        _check(_lib.lib().ptwm_b200_open(self._host.data_ptr(), n, C.byref(self._h)))
+        self.device = torch.cuda.current_device() if device is None else int(device)
+        self.verify = verify
+        self.skip_missing = skip_missing
+        self._infos = []
+        L = _lib.lib()
+        for i in range(L.ptwm_b200_tensor_count(self._h)):
+            ti = _lib.TensorInfo()
+            _check(L.ptwm_b200_tensor_info_get(self._h, i, C.byref(ti)))
+            self._infos.append(dict(name=ti.name.decode(), dtype_name=ti.dtype_name.decode(), dtype_code=ti.dtype_code,
+                                    shape=[ti.shape[d] for d in range(ti.ndim)] if ti.has_shape else None, has_hash=bool(ti.has_hash),
+                                    has_crc=bool(ti.has_crc), supported=bool(ti.supported), kind=ti.kind, orig_size=ti.orig_size,
+                                    compressed=ti.compressed, first_byte=ti.first_byte, end_byte=ti.end_byte,
+                                    unsupported_reason=ti.unsupported_reason.decode()))
+        if not skip_missing:
+            for inf in self._infos:
+                if not inf["supported"] and "third-party" in inf["unsupported_reason"]:
+                    raise ValueError(f"container references an extension that is not installed: {inf['unsupported_reason']}")
+        self._index = {inf["name"]: i for i, inf in enumerate(self._infos)}
+        self._blob_dev: Optional[torch.Tensor] = None
+        self._plans: dict = {}
+
+    def __del__(self):
+        self._plans = {}
+        if getattr(self, "_h", None):
+            _lib.lib().ptwm_b200_close(self._h)
+            self._h = None
+
+    # -- inspection (handle.rs:168-227) ---------------------------------------
+    @property
+    def layout(self) -> str:
+        return "compact"
+
+    def names(self) -> list[str]:
+        return [inf["name"] for inf in self._infos]
+
+    def __len__(self) -> int:
+        return len(self._infos)
+
+    def __contains__(self, name: str) -> bool:
+        return name in self._index
+
+    def info(self, name: str):
+        """(shape, dtype_name, dtype_code, input_format) or None without shape metadata."""
+        inf = self._infos[self._idx(name)]
+        if inf["shape"] is None:
+            return None
+        return (list(inf["shape"]), inf["dtype_name"], inf["dtype_code"], 2)
+
+    def shape(self, name: str):
+        inf = self._infos[self._idx(name)]
+        return None if inf["shape"] is None else (list(inf["shape"]), inf["dtype_name"])
+
+    def tensor_infos(self) -> list[dict]:
+        return [dict(i) for i in self._infos]
+
+    def _idx(self, name) -> int:
+        if isinstance(name, int):
+            return name
+        try:
+            return self._index[name]
+        except KeyError:
+            raise KeyError(name) from None
+
+    # -- device residency -------------------------------------------------------
+    def blob_on_device(self) -> torch.Tensor:
+        if self._blob_dev is None:
+            self._blob_dev = self._host.to(torch.device("cuda", self.device))
+        return self._blob_dev
+
+    def plan(self, indices: Optional[Sequence[int]] = None) -> DecodePlan:
+        key = None if indices is None else tuple(int(i) for i in indices)
+        if key not in self._plans:
+            self._plans[key] = DecodePlan(self, indices)
+        return self._plans[key]
+
+    def _flags(self) -> int:
+        return (VERIFY_CRC | VERIFY_HASH) if self.verify else 0
+
+    def _view(self, i: int, out: torch.Tensor, off: int) -> torch.Tensor:
+        inf = self._infos[i]
+        raw = out[off:off + inf["orig_size"]]
+        if inf["shape"] is None:
+            return raw
+        dt = _TORCH_DTYPES.get(inf["dtype_code"])
+        if dt is None:
+            raise InvalidDTypeError(f"dtype_code={inf['dtype_code']} has no torch.dtype mapping")
+        return raw.view(dt).reshape(inf["shape"])
+
+    # -- decode (handle.rs:184-193) --------------------------------------------
+    def decode_raw(self, name) -> torch.Tensor:
+        """Decoded bytes of one tensor as a CUDA uint8 tensor."""
+        i = self._idx(name)
+        plan = self.plan([i])
+        dev = torch.device("cuda", self.device)
+        out = torch.empty(plan.out_bytes, dtype=torch.uint8, device=dev)
+        scratch = torch.empty(plan.scratch_bytes, dtype=torch.uint8, device=dev) if plan.scratch_bytes else None
+        plan.run(self.blob_on_device(), out, scratch, flags=self._flags())
+        return out[:self._infos[i]["orig_size"]]
+
+    def decode(self, name) -> torch.Tensor:
+        """One tensor, typed and shaped when the record carries shape metadata."""
+        i = self._idx(name)
+        raw = self.decode_raw(i)
+        return self._view(i, raw, 0)
+
+    def decode_model(self, names: Optional[Iterable[str]] = None) -> list[tuple[str, torch.Tensor]]:
+        """Every tensor (or the named ones) in one batched pass; the tensors
+        are views into one output arena (ContainerReader::decode_model)."""
+        indices = None if names is None else [self._idx(n) for n in names]
+        plan = self.plan(indices)
+        dev = torch.device("cuda", self.device)
+        out = torch.empty(plan.out_bytes, dtype=torch.uint8, device=dev)
+        scratch = torch.empty(plan.scratch_bytes, dtype=torch.uint8, device=dev) if plan.scratch_bytes else None
+        plan.run(self.blob_on_device(), out, scratch, flags=self._flags())
+        return [(self._infos[i]["name"], v) for i, v in zip(plan.indices, plan.views(out))]
+
+
+class Decompressor:
+    """Stateless decompressor; ``decompress`` returns a CUDA tensor."""
+
+    def __init__(self, config: Optional[DecompressionConfig] = None) -> None:
+        self.config = config or DecompressionConfig()
+
+    def decompress(self, data) -> torch.Tensor:
+        if self.config.codec is not None:
+            raise ValueError(f"DecompressionConfig.codec={self.config.codec!r} is set, but decoding always dispatches on the codec "
+                             "recorded in the container; leave codec unset.")
+        if self.config.delta_second_data is not None:
+            raise ValueError("tensor was not compressed using delta compression, but delta_second_data was provided.")
+        mv = memoryview(data) if not isinstance(data, torch.Tensor) else None
+        if mv is not None and mv.nbytes < len(MAGIC_PTWS):
+            raise HeaderParseError("too short to be a .ptwm container")
+        handle = ContainerHandle(data, self.config.skip_missing, device=self.config.device, verify=self.config.verify)
+        if "_" not in handle:
+            raise PtwmError("container holds no tensor named '_'")
+        return handle.decode("_")
+
+
+class TensorIndex:
+    """Name-indexed random-access loader over a ``.ptwm`` container file."""
+
+    def __init__(self, path, device: Optional[int] = None, verify: bool = True) -> None:
+        self._path = Path(path)
+        blob = self._path.read_bytes()
+        if not (blob.startswith(MAGIC_PTWC) or blob.startswith(MAGIC_PTWM)):
+            raise ValueError(f"{self._path} is not a .ptwm container")
+        self._handle = ContainerHandle(blob, device=device, verify=verify)
+        self._names = self._handle.names()
+
+    @classmethod
+    def open(cls, path, device: Optional[int] = None):
+        return cls(path, device=device)
+
+    @property
+    def path(self) -> Path:
+        return self._path
+
+    @property
+    def layout(self) -> str:
+        return self._handle.layout
+
+    def names(self) -> list[str]:
+        return list(self._names)
+
+    def get_bytes(self, name: str) -> bytes:
+        if name not in self._handle:
+            raise KeyError(name)
+        return bytes(self._handle.decode_raw(name).cpu().numpy().tobytes())
+
+    def get_tensor(self, name: str) -> torch.Tensor:
+        if name not in self._handle:
+            raise KeyError(name)
+        if self._handle.shape(name) is None:
+            raise TypeError(f"tensor {name!r} has no shape metadata; cannot reconstruct a torch.Tensor. Call get_bytes().")
+        return self._handle.decode(name)
+
+    def stream_tensors(self, names: Optional[Iterable[str]] = None) -> Iterator[tuple[str, torch.Tensor]]:
+        for name in (list(names) if names is not None else self.names()):
+            yield name, self.get_tensor(name)
+
+    def __len__(self) -> int:
+        return len(self._names)
+
+    def __contains__(self, name: str) -> bool:
+        return name in self._handle
+
+    def __iter__(self) -> Iterator[str]:
+        return iter(self._names)

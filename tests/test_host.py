@@ -1,0 +1,160 @@
+"""Host-side logic of the CUDA library, without a GPU: the C ABI loads and
+exports what include/ptwm_b200.h declares, the container parser agrees with
+the oracle's, plans are sized sensibly and malformed input is refused."""
+import ctypes as C
+import json
+import os
+import re
+import zlib
+
+import numpy as np
+import pytest
+
+import oracle
+import ptwm_b200
+from ptwm_b200 import _lib
+from ptwm_b200.sharding import contiguous_shards, shard_for_rank
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLD = os.path.join(ROOT, "tests", "golden")
+
+
+@pytest.fixture(scope="module")
+def L():
+    ptwm_b200.build()
+    return _lib.lib()
+
+
+def _open(L, blob):
+    buf = (C.c_char * len(blob)).from_buffer_copy(blob)
+    h = C.c_void_p()
+    rc = L.ptwm_b200_open(C.addressof(buf), len(blob), C.byref(h))
+    return rc, h
+
+
+def _infos(L, h):
+    out = []
+    for i in range(L.ptwm_b200_tensor_count(h)):
+        ti = _lib.TensorInfo()
+        assert L.ptwm_b200_tensor_info_get(h, i, C.byref(ti)) == 0
+        out.append(ti)
+    return out
+
+
+def test_every_declared_symbol_is_exported(L):
+    header = open(os.path.join(ROOT, "include", "ptwm_b200.h")).read()
+    declared = set(re.findall(r"\b(ptwm_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    assert declared == set(_lib.EXPORTED_SYMBOLS)
+    for name in declared:
+        assert hasattr(L, name), name
+
+
+def test_crc_fold_matches_zlib(L):
+    rng = np.random.default_rng(0)
+    for n in [0, 1, 5, 2047, 2048, 2049, 10000, 300001]:
+        b = rng.integers(0, 256, n, dtype=np.uint8).tobytes()
+        for run in [1, 7, 2048, 1 << 20]:
+            assert L.ptwm_b200_crc32_by_runs(b, n, run) == zlib.crc32(b)
+
+
+def test_parser_agrees_with_oracle_on_goldens(L):
+    man = json.load(open(os.path.join(GOLD, "oracle", "manifest.json")))
+    for name in man:
+        if name == "frames":
+            continue
+        blob = open(os.path.join(GOLD, "oracle", name + ".ptwm"), "rb").read()
+        rc, h = _open(L, blob)
+        assert rc == 0, _lib.last_error()
+        oc = oracle.Container(blob)
+        infos = _infos(L, h)
+        assert [t.name.decode() for t in infos] == oc.names
+        for ti, ot in zip(infos, oc.tensors):
+            assert ti.supported and ti.orig_size == ot["orig_size"] and ti.dtype_code == ot["dtype_code"] and ti.kind == ot["kind"]
+            assert list(ti.shape)[:ti.ndim] == ot["shape"] and bool(ti.has_hash) == ot["has_hash"]
+            assert ti.compressed == sum(p["payload_len"] for p in ot["planes"])
+        p = C.c_void_p()
+        assert L.ptwm_b200_plan_create(h, None, 0, C.byref(p)) == 0, _lib.last_error()
+        assert L.ptwm_b200_plan_out_bytes(p) >= sum(t["orig_size"] for t in oc.tensors)
+        r, w, n = C.c_uint64(), C.c_uint64(), C.c_uint32()
+        L.ptwm_b200_plan_stats(p, C.byref(r), C.byref(w), C.byref(n))
+        assert w.value == sum(t["orig_size"] for t in oc.tensors) and 0 < r.value <= len(blob) and n.value >= 1
+        lo, hi = C.c_uint64(), C.c_uint64()
+        L.ptwm_b200_plan_blob_span(p, C.byref(lo), C.byref(hi))
+        assert 0 < lo.value < hi.value <= len(blob)
+        L.ptwm_b200_plan_destroy(p)
+        L.ptwm_b200_close(h)
+
+
+def test_reference_fixtures_open(L):
+    blob = open(os.path.join(GOLD, "reference", "ptwc_bound_source"), "rb").read()
+    rc, h = _open(L, blob)
+    assert rc == 0
+    infos = _infos(L, h)
+    assert [t.name for t in infos] == [b"t1", b"t2", b"t3", b"t4"] and all(t.supported and t.kind == 2 and t.has_hash and t.has_crc for t in infos)
+    L.ptwm_b200_close(h)
+    # zstd planes and a delta-coded tensor: opens, tensors flagged as outside the hot path, planning refuses
+    blob = open(os.path.join(GOLD, "reference", "ptwc_trimmed"), "rb").read()
+    rc, h = _open(L, blob)
+    assert rc == 0
+    infos = _infos(L, h)
+    assert len(infos) == 6 and not any(t.supported for t in infos)
+    p = C.c_void_p()
+    assert L.ptwm_b200_plan_create(h, None, 0, C.byref(p)) == -5  # Unsupported (native.rs:634-657)
+    L.ptwm_b200_close(h)
+
+
+def test_frames_open(L):
+    for f in sorted(os.listdir(os.path.join(GOLD, "reference", "compact_decode"))):
+        blob = b"\x89PTWS" + open(os.path.join(GOLD, "reference", "compact_decode", f), "rb").read()
+        rc, h = _open(L, blob)
+        assert rc == 0, (f, _lib.last_error())
+        infos = _infos(L, h)
+        assert len(infos) == 1 and infos[0].name == b"_"
+        L.ptwm_b200_close(h)
+        rc, h = _open(L, blob + b"\x00")  # a frame is self-delimiting
+        if infos[0].supported:
+            assert rc < 0
+
+
+def test_every_byte_mutation_is_survived(L):
+    # tests/ptwc.rs:130 of the reference: mutate each byte, the reader must answer (error or success), never crash
+    blob = bytearray(open(os.path.join(GOLD, "reference", "ptwc_bound_source"), "rb").read())
+    rejected = 0
+    for i in range(len(blob)):
+        m = bytearray(blob)
+        m[i] ^= 0x5A
+        rc, h = _open(L, bytes(m))
+        if rc < 0:
+            rejected += 1
+        else:
+            L.ptwm_b200_close(h)
+    assert rejected > len(blob) // 4
+    for cut in range(0, len(blob), 7):
+        rc, h = _open(L, bytes(blob[:cut]))
+        assert rc < 0
+
+
+def test_bad_magic_and_short_input(L):
+    for blob in (b"", b"\x89PT", b"not a container at all", b"\x89PTWM\r\n\x1a\n" + b"\x00" * 64):
+        rc, h = _open(L, blob if blob else b"\x00")
+        assert rc < 0
+
+
+def test_contiguous_shards_cover_everything():
+    rng = np.random.default_rng(1)
+    costs = list(rng.integers(1, 1000, 291))
+    for world in (1, 2, 4, 8):
+        parts = contiguous_shards(costs, world)
+        assert [i for p in parts for i in p] == list(range(len(costs)))
+        sums = [sum(costs[i] for i in p) for p in parts]
+        assert max(sums) <= sum(costs) / world + max(costs)
+    infos = [dict(compressed=10, orig_size=20)] * 5
+    assert sum((shard_for_rank(infos, r, 2) for r in range(2)), []) == [0, 1, 2, 3, 4]
+
+
+def test_missing_library_fails_loudly(tmp_path, monkeypatch):
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    monkeypatch.setattr(_lib, "_lib", None)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        _lib.lib()
