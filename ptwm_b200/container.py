@@ -212,7 +212,11 @@ class ContainerHandle:
         dt = _TORCH_DTYPES.get(inf["dtype_code"])
         if dt is None:
             raise InvalidDTypeError(f"dtype_code={inf['dtype_code']} has no torch.dtype mapping")
-        return raw.view(dt).reshape(inf["shape"])
+        try:
+            return raw.view(dt).reshape(inf["shape"])
+        except (RuntimeError, TypeError):
+            # packed sub-byte dtypes some torch builds cannot view or reshape: hand back the bytes in shape
+            return raw.reshape(inf["shape"]) if dt.itemsize == 1 else raw
 
     # -- decode (handle.rs:184-193) --------------------------------------------
     def decode_raw(self, name) -> torch.Tensor:

@@ -1,0 +1,235 @@
+"""Parity of the CUDA decode path with the CPU oracle, through the C ABI.
+
+Bit-exact is the bar: every comparison is on raw bytes."""
+import ctypes as C
+import hashlib
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import ptwm_b200
+from ptwm_b200 import _lib
+from _data import mixed_model, spec_bf16, spec_f32, specs_fp8, specs_nvfp4
+
+pytestmark = pytest.mark.gpu
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+# canonical ids of the built-in codecs: blake3([0xBB]*32 | 0 | name | 0 | "1.1.0") (extension/id.rs:21-31)
+IDS = {
+    oracle.IDENTITY: "fc2dea1265e3394c57c2df3b868b732ccaa1ee876bd4b1ce27d38f842c6112b5",
+    oracle.HUFFMAN: "614155b5a8c9efb689219bcca3cbf7855e29d3023208ce61cca7a36849248e33",
+    oracle.RANS: "39c875ef9793a9c5ebe199116debac4c9d5388b8b7cf2fe6b575845f0ca1624e",
+    oracle.TANS: "e4868545e7b22282695972441494e70569ab27595d19349114e852125d96daa4",
+    oracle.O1SAC: "0b8426e0a670d114f24ee4614837c9578ff3034f11e4e9e9c0f5d92a49887770",
+}
+
+
+def bytes_of(t: torch.Tensor) -> bytes:
+    return t.contiguous().view(torch.uint8).cpu().numpy().tobytes()
+
+
+def dispatch_decode(codec, payload: bytes, decoded_len: int, state: bytes = b"", sv: int = 0, symbol="ptwm_hardware_backend_v1_dispatch_decode_cuda"):
+    """One plane payload through the reference-facing symbol."""
+    L = _lib.lib()
+    dev = torch.device("cuda", 0)
+    src = torch.frombuffer(bytearray(payload), dtype=torch.uint8).to(dev) if payload else torch.empty(0, dtype=torch.uint8, device=dev)
+    out = torch.full((max(decoded_len, 1) + 64,), 0xAB, dtype=torch.uint8, device=dev)
+    torch.cuda.synchronize()
+    st = C.create_string_buffer(state, len(state)) if state else None
+    rc = getattr(L, symbol)(sv, st, len(state), bytes.fromhex(IDS[codec]), 32, src.data_ptr() if payload else 0, len(payload), out.data_ptr(), decoded_len, 0)
+    return rc, bytes_of(out[:max(rc, 0)]), bytes_of(out[decoded_len:decoded_len + 64])
+
+
+def plane_cases():
+    rng = np.random.default_rng(7)
+    sizes = [1, 2, 3, 4, 5, 7, 8, 9, 31, 32, 33, 100, 1023, 4093, 4096, 65536, 100003, 262144]
+    for n in sizes:
+        yield "gauss", ((rng.normal(0, 3, n).astype(np.int64) + 120) % 256).astype(np.uint8).tobytes()
+        yield "two", rng.integers(0, 2, n, dtype=np.uint8).tobytes()
+        yield "const", np.full(n, 7, np.uint8).tobytes()
+        yield "nibble", rng.integers(0, 16, n, dtype=np.uint8).tobytes()
+    yield "wide", (np.arange(256 * 40) % 256).astype(np.uint8).tobytes() + bytes(9000)
+    yield "skew", np.concatenate([np.zeros(200000, np.uint8), rng.integers(0, 256, 3000, dtype=np.uint8)]).tobytes()
+    yield "random", rng.integers(0, 256, 50000, dtype=np.uint8).tobytes()
+    yield "empty", b""
+
+
+@pytest.mark.parametrize("codec", [oracle.IDENTITY, oracle.HUFFMAN, oracle.RANS, oracle.TANS])
+def test_plane_payloads_match_oracle(codec):
+    coded = 0
+    for tag, plane in plane_cases():
+        st, sv, payload = oracle.plane_encode(codec, plane)
+        assert oracle.plane_decode(codec, payload, len(plane)) == plane
+        rc, got, guard = dispatch_decode(codec, payload, len(plane))
+        assert rc == len(plane), (tag, len(plane), rc, _lib.last_error())
+        assert got == plane, (tag, len(plane), next(i for i in range(len(plane)) if got[i] != plane[i]))
+        assert guard == b"\xAB" * 64, (tag, len(plane), "wrote past the plane")
+        coded += codec != oracle.IDENTITY and payload[:1] == b"\x01"
+    if codec != oracle.IDENTITY:
+        assert coded > 20
+
+
+def test_o1sac_payloads_match_oracle():
+    rng = np.random.default_rng(8)
+    for rows, rl in [(1, 1), (3, 7), (32, 32), (64, 256), (500, 128)]:
+        walk = (np.cumsum(rng.integers(-1, 2, (rows, rl)), axis=1) + 120).astype(np.uint8).tobytes()
+        st, sv, payload = oracle.plane_encode(oracle.O1SAC, walk, 0)  # the flat ABI carries no layout: one row
+        rc, got, guard = dispatch_decode(oracle.O1SAC, payload, len(walk), st, sv, symbol="ptwm_plane_codec_v1_decode_cuda")
+        assert rc == len(walk), _lib.last_error()
+        assert got == walk and guard == b"\xAB" * 64
+
+
+def test_host_buffer_pair_decodes_rans():
+    plane = ((np.random.default_rng(9).normal(0, 2, 30000).astype(np.int64) + 100) % 256).astype(np.uint8).tobytes()
+    _, _, payload = oracle.plane_encode(oracle.RANS, plane)
+    out = C.create_string_buffer(len(plane))
+    rc = _lib.lib().ptwm_plane_codec_v1_decode(payload, len(payload), out, len(plane))
+    assert rc == len(plane) and out.raw == plane
+    small = C.create_string_buffer(10)
+    assert _lib.lib().ptwm_plane_codec_v1_decode(payload, len(payload), small, 10) == -2  # BufferTooSmall (native.rs:634-657)
+
+
+def test_stream_handle_is_persistent():
+    L = _lib.lib()
+    a = L.ptwm_hardware_backend_v1_cuda_stream_handle(0)
+    assert a != 0 and a == L.ptwm_hardware_backend_v1_cuda_stream_handle(0) == L.ptwm_plane_codec_v1_cuda_stream_handle(0)
+
+
+def test_unknown_codec_id_is_unsupported():
+    L = _lib.lib()
+    out = torch.empty(16, dtype=torch.uint8, device="cuda")
+    rc = L.ptwm_hardware_backend_v1_dispatch_decode_cuda(0, None, 0, bytes(32), 32, out.data_ptr(), 4, out.data_ptr(), 4, 0)
+    assert rc == -5
+
+
+# ---- containers -------------------------------------------------------------
+def check_container(blob: bytes, expected: dict, verify=True):
+    h = ptwm_b200.ContainerHandle(blob, device=0, verify=verify)
+    got = dict(h.decode_model())
+    assert list(got) == list(expected)
+    for name, raw in expected.items():
+        g = bytes_of(got[name])
+        assert len(g) == len(raw), name
+        if g != raw:
+            first = next(i for i in range(len(raw)) if g[i] != raw[i])
+            raise AssertionError(f"{name}: first mismatch at byte {first} of {len(raw)}")
+    return h, got
+
+
+CONTAINER_CASES = {
+    "whole": dict(),
+    "chunk4k_crc": dict(chunk_size=4096, emit_crc=True),
+    "chunk1000_hash_crc": dict(chunk_size=1000, emit_hash=True, emit_crc=True),
+    "chunk64k": dict(chunk_size=65536, emit_crc=True),
+    "huffman_8k": dict(forced_codec=oracle.HUFFMAN, chunk_size=8192, emit_crc=True, emit_hash=True),
+    "rans_8k": dict(forced_codec=oracle.RANS, chunk_size=8192, emit_crc=True, emit_hash=True),
+    "tans_8k": dict(forced_codec=oracle.TANS, chunk_size=8192, emit_crc=True),
+    "identity": dict(forced_codec=oracle.IDENTITY, emit_crc=True, emit_hash=True),
+    "menu_hr_o1": dict(menu=(oracle.HUFFMAN, oracle.RANS, oracle.O1SAC), emit_crc=True, emit_hash=True),
+    "menu_hr_chunk_odd": dict(menu=(oracle.HUFFMAN, oracle.RANS), chunk_size=777),
+}
+
+
+@pytest.mark.parametrize("case", list(CONTAINER_CASES))
+def test_mixed_model_matches_oracle(case):
+    specs = mixed_model()
+    blob = oracle.write_container(specs, **CONTAINER_CASES[case])
+    oc = oracle.Container(blob)
+    expected = {s.name: oc.decode(i) for i, s in enumerate(specs)}
+    assert all(expected[s.name] == s.raw for s in specs)
+    h, got = check_container(blob, expected)
+    # typed views: dtype and shape follow the record (python/ptwm/core/_decompressor.py:141-160)
+    assert got["blk.q.weight"].dtype == torch.bfloat16 and list(got["blk.q.weight"].shape) == list(specs[0].shape)
+    assert got["blk.gate.f32"].dtype == torch.float32 and got["blk.fp8.weight"].dtype == torch.float8_e4m3fn
+    # random access agrees with the batched pass (ContainerReader::decode_tensor)
+    for name in ("blk.k.weight", "blk.nv.weight_scale", "odd.bf16", "scalar.f32", "empty.f32"):
+        assert bytes_of(h.decode(name)) == expected[name]
+
+
+def test_committed_goldens():
+    man = json.load(open(os.path.join(GOLD, "oracle", "manifest.json")))
+    for name, meta in man.items():
+        if name == "frames":
+            for fn, (n, sha) in meta.items():
+                t = ptwm_b200.Decompressor(ptwm_b200.DecompressionConfig(device=0)).decompress(open(os.path.join(GOLD, "oracle", fn), "rb").read())
+                raw = bytes_of(t)
+                assert len(raw) == n and hashlib.sha256(raw).hexdigest() == sha, fn
+            continue
+        h = ptwm_b200.ContainerHandle(open(os.path.join(GOLD, "oracle", name + ".ptwm"), "rb").read(), device=0)
+        for tname, t in h.decode_model():
+            raw = bytes_of(t)
+            n, sha = meta["tensors"][tname]
+            assert len(raw) == n and hashlib.sha256(raw).hexdigest() == sha, (name, tname)
+
+
+def test_reference_fixtures_on_gpu():
+    # the reference's own files: Identity planes with hash + CRC, and every supported \x89PTWS seed
+    import xxhash
+    ref = os.path.join(GOLD, "reference")
+    blob = open(os.path.join(ref, "ptwc_bound_source"), "rb").read()
+    h = ptwm_b200.ContainerHandle(blob, device=0)
+    oc = oracle.Container(blob)
+    for i, (name, t) in enumerate(h.decode_model()):
+        assert bytes_of(t) == oc.decode(i)
+    assert xxhash.xxh64(bytes_of(h.decode("t1"))).hexdigest() == json.load(open(os.path.join(ref, "expected.json")))["ptwc_bound_source"]["t1"][1]
+    done = 0
+    for f in sorted(os.listdir(os.path.join(ref, "compact_decode"))):
+        frame = b"\x89PTWS" + open(os.path.join(ref, "compact_decode", f), "rb").read()
+        try:
+            want, _ = oracle.decode_compact(frame)
+        except oracle.OracleError:
+            continue  # zstd planes or IntDelta chains: outside the hot path
+        got = ptwm_b200.Decompressor(ptwm_b200.DecompressionConfig(device=0)).decompress(frame)
+        assert bytes_of(got) == want, f
+        done += 1
+    assert done >= 9
+
+
+def test_integrity_checks_fire():
+    specs = [spec_bf16("w", 64, 256, 1)]
+    for kw, needle in ((dict(emit_crc=True, chunk_size=4096), "CRC"), (dict(emit_hash=True), "hash")):
+        blob = bytearray(oracle.write_container(specs, forced_codec=oracle.IDENTITY, **kw))
+        h = ptwm_b200.ContainerHandle(bytes(blob), device=0)
+        inf = h.tensor_infos()[0]
+        blob[inf["end_byte"] - 3] ^= 0x10  # flip a stored mantissa-or-exponent byte: decodes, but to other values
+        bad = ptwm_b200.ContainerHandle(bytes(blob), device=0)
+        with pytest.raises(ptwm_b200.PtwmError, match=needle):
+            bad.decode_model()
+        assert len(ptwm_b200.ContainerHandle(bytes(blob), device=0, verify=False).decode_model()) == 1
+
+
+def test_full_size_properties():
+    # BASELINE-sized tensors: too slow for the serial oracle decode of every case, so check through
+    # self-verifying containers (hash + CRC) and against the source bytes.
+    specs = [spec_bf16("c1.bf16", 4096, 4096, 0), spec_f32("c2.f32", 4096, 1024, 1)] + specs_fp8("c3", 2048, 4096, 2) + specs_nvfp4("c4", 1024, 4096, 3)
+    for kw in (dict(chunk_size=65536, emit_crc=True, emit_hash=True, menu=(oracle.IDENTITY, oracle.HUFFMAN, oracle.RANS, oracle.O1SAC)),
+               dict(chunk_size=32768, forced_codec=oracle.HUFFMAN, emit_crc=True)):
+        blob = oracle.write_container(specs, **kw)
+        check_container(blob, {s.name: s.raw for s in specs})
+
+
+def test_partial_blob_span_and_subset_plan():
+    # a rank keeps only the byte range of its own tensors on the device
+    specs = mixed_model()
+    blob = oracle.write_container(specs, chunk_size=4096, emit_crc=True)
+    h = ptwm_b200.ContainerHandle(blob, device=0)
+    infos = h.tensor_infos()
+    from ptwm_b200.sharding import shard_for_rank
+    seen = []
+    for rank in range(3):
+        idx = shard_for_rank(infos, rank, 3)
+        seen += idx
+        plan = h.plan(idx)
+        lo, hi = plan.blob_span
+        part = torch.frombuffer(bytearray(blob[lo:hi]), dtype=torch.uint8).cuda() if hi > lo else torch.empty(0, dtype=torch.uint8, device="cuda")
+        out = torch.empty(plan.out_bytes, dtype=torch.uint8, device="cuda")
+        scratch = torch.empty(plan.scratch_bytes, dtype=torch.uint8, device="cuda")
+        plan.run(part, out, scratch, blob_first=lo, flags=ptwm_b200.VERIFY_CRC)
+        for i, v in zip(idx, plan.views(out)):
+            assert bytes_of(v) == specs[i].raw, specs[i].name
+    assert seen == list(range(len(specs)))
