@@ -140,6 +140,52 @@ int64_t ptwm_b200_plan_run(ptwm_b200_plan* p, uint64_t blob_dev_ptr, uint64_t bl
 /* Wait for an enqueued run and evaluate decode status and integrity checks. */
 int64_t ptwm_b200_plan_finish(ptwm_b200_plan* p, uint32_t flags, uint32_t device_ordinal, uint64_t stream);
 
+
+/* ---- 3. encode ------------------------------------------------------------ */
+
+/* One tensor to encode; the bytes are read from device memory. */
+typedef struct ptwm_b200_encode_tensor {
+    const char* name;
+    uint64_t dev_ptr;
+    uint64_t nbytes;
+    uint64_t shape[8];
+    uint16_t dtype_code;     /* public dtype code (dtype.rs:25-50) */
+    uint8_t ndim;
+    uint8_t usage;           /* 0 standard, 1 block scale (E4M3 / E8M0), 2 fp32 global scale, 3 packed fp4 values:
+                                which production chain the tensor gets (python/ptwm/preprocessing/_chains.py:320-357,610-727) */
+} ptwm_b200_encode_tensor;
+
+#define PTWM_B200_MENU_IDENTITY 1u
+#define PTWM_B200_MENU_HUFFMAN  2u
+#define PTWM_B200_MENU_RANS     4u
+
+typedef struct ptwm_b200_encode_options {
+    uint32_t chunk_size;     /* plane bytes per chunk (CompressorOptions.chunk_size, compressor.rs:112-113); 0 = 65536 */
+    uint32_t menu;           /* PTWM_B200_MENU_* bits the per-plane selection may use; 0 = all three */
+    int32_t forced_codec;    /* codec wire id to force on every plane (CompressorOptions.forced_codec), -1 = select */
+    uint8_t emit_plane_crc;  /* CompressorOptions.emit_plane_crc */
+    uint8_t emit_payload_hash; /* CompressorOptions.emit_payload_hash */
+    uint8_t reserved[2];
+} ptwm_b200_encode_options;
+
+typedef struct ptwm_b200_encoded ptwm_b200_encoded;
+
+/* compress_model (compressor.rs:972-1200) for the production split / passthrough
+ * chains with chunked planes, compact \x89PTWC layout: split + reorder, per-chunk
+ * histograms, table build and stream encoding run on the device; the host lays
+ * out records, index and footer.  The container is left in device memory. */
+int64_t ptwm_b200_encode_model(const ptwm_b200_encode_tensor* tensors, size_t n, const ptwm_b200_encode_options* options, uint32_t device_ordinal,
+                               uint64_t stream, ptwm_b200_encoded** out);
+uint64_t ptwm_b200_encoded_size(const ptwm_b200_encoded* e);
+uint64_t ptwm_b200_encoded_device_ptr(const ptwm_b200_encoded* e);
+/* Copy the container bytes to host memory. */
+int64_t ptwm_b200_encoded_copy(const ptwm_b200_encoded* e, uint8_t* host_dst, size_t cap);
+/* Copy the container bytes into another device buffer (same device). */
+int64_t ptwm_b200_encoded_copy_to_device(const ptwm_b200_encoded* e, uint64_t dst_dev_ptr, uint64_t cap, uint64_t stream);
+/* Codec wire id chosen for plane `plane` of tensor `tensor`, or -1. */
+int32_t ptwm_b200_encoded_plane_codec(const ptwm_b200_encoded* e, size_t tensor, size_t plane);
+void ptwm_b200_encoded_free(ptwm_b200_encoded* e);
+
 /* CRC-32 computed the way the verification kernel does it (per-run remainders,
  * GF(2) shifts, XOR fold), on the host, for testing that arithmetic without a GPU. */
 uint32_t ptwm_b200_crc32_by_runs(const uint8_t* data, size_t len, size_t run);

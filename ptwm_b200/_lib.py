@@ -12,7 +12,8 @@ import subprocess
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libptwm_b200.so")
-_SOURCES = [os.path.join(_HERE, "csrc", f) for f in ("ptwm_b200.cu", "kernels.cuh", "format.hpp", "plan.h")] + [
+_SOURCES = [os.path.join(_HERE, "csrc", f) for f in ("unity.cu", "ptwm_b200.cu", "encoder.cu", "kernels.cuh", "encode.cuh", "encode_tables.cuh",
+                                                      "format.hpp", "host_common.hpp", "plan.h")] + [
     os.path.join(_HERE, "..", "include", "ptwm_b200.h")]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared"]
@@ -24,7 +25,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     stale = force or not os.path.exists(LIB_PATH) or any(os.path.getmtime(s) > os.path.getmtime(LIB_PATH) for s in srcs)
     if stale:
         nvcc = os.environ.get("NVCC", "nvcc")
-        cmd = [nvcc, *NVCC_FLAGS, "-o", LIB_PATH, os.path.join(_HERE, "csrc", "ptwm_b200.cu")]
+        cmd = [nvcc, *NVCC_FLAGS, "-o", LIB_PATH, os.path.join(_HERE, "csrc", "unity.cu")]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         res = subprocess.run(cmd, capture_output=True, text=True)
@@ -42,7 +43,24 @@ class TensorInfo(C.Structure):
                 ("unsupported_reason", C.c_char_p)]
 
 
+class EncodeTensor(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("dev_ptr", C.c_uint64), ("nbytes", C.c_uint64), ("shape", C.c_uint64 * 8), ("dtype_code", C.c_uint16),
+                ("ndim", C.c_uint8), ("usage", C.c_uint8)]
+
+
+class EncodeOptions(C.Structure):
+    _fields_ = [("chunk_size", C.c_uint32), ("menu", C.c_uint32), ("forced_codec", C.c_int32), ("emit_plane_crc", C.c_uint8),
+                ("emit_payload_hash", C.c_uint8), ("reserved", C.c_uint8 * 2)]
+
+
 _SIGNATURES = {
+    "ptwm_b200_encode_model": (C.c_int64, [C.POINTER(EncodeTensor), C.c_size_t, C.POINTER(EncodeOptions), C.c_uint32, C.c_uint64, C.POINTER(C.c_void_p)]),
+    "ptwm_b200_encoded_size": (C.c_uint64, [C.c_void_p]),
+    "ptwm_b200_encoded_device_ptr": (C.c_uint64, [C.c_void_p]),
+    "ptwm_b200_encoded_copy": (C.c_int64, [C.c_void_p, C.c_void_p, C.c_size_t]),
+    "ptwm_b200_encoded_copy_to_device": (C.c_int64, [C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64]),
+    "ptwm_b200_encoded_plane_codec": (C.c_int32, [C.c_void_p, C.c_size_t, C.c_size_t]),
+    "ptwm_b200_encoded_free": (None, [C.c_void_p]),
     "ptwm_b200_last_error": (C.c_char_p, []),
     "ptwm_b200_open": (C.c_int64, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
     "ptwm_b200_close": (None, [C.c_void_p]),

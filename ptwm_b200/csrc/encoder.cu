@@ -1,0 +1,483 @@
+// Host side of the encode path: chain choice per tensor, per-plane codec
+// selection, the device pipeline (split, histogram, tables, streams, gather)
+// and the compact-container writer (ptwc.rs:76-93,160-226,
+// tensor_record_compact.rs:203-493, chain/wire_compact.rs:140-245,
+// extension/compact_table.rs:123-158 of the reference).
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "encode.cuh"
+#include "format.hpp"
+#include "host_common.hpp"
+
+using namespace ptwm;
+
+namespace {
+
+void put_varint(std::vector<uint8_t>& out, uint64_t v) {  // varint.rs:17-23
+    while (v >= 0x80) { out.push_back(uint8_t(v) | 0x80); v >>= 7; }
+    out.push_back(uint8_t(v));
+}
+void put_u32(std::vector<uint8_t>& out, uint32_t v) { for (int i = 0; i < 4; ++i) out.push_back(uint8_t(v >> (8 * i))); }
+void put_u64(std::vector<uint8_t>& out, uint64_t v) { for (int i = 0; i < 8; ++i) out.push_back(uint8_t(v >> (8 * i))); }
+
+struct ChainDef {
+    uint8_t kind;
+    std::vector<std::pair<uint16_t, std::vector<uint8_t>>> nodes;  // (op wire id, params)
+    std::vector<uint8_t> roles;                                    // compact terminal role bytes
+    bool operator==(const ChainDef& o) const { return nodes == o.nodes && roles == o.roles; }
+};
+
+std::vector<uint8_t> source_params(const uint64_t* shape, int ndim, uint16_t chain_dtype) {
+    std::vector<uint8_t> p;
+    p.push_back(uint8_t(ndim));
+    for (int d = 0; d < ndim; ++d) put_u32(p, uint32_t(shape[d]));
+    p.push_back(uint8_t(chain_dtype)); p.push_back(uint8_t(chain_dtype >> 8));
+    return p;
+}
+
+// Production chains (python/ptwm/preprocessing/_chains.py:320-357,610-727) and
+// their compact role bytes (chain/wire_compact.rs:434-459).
+bool chain_for(const ptwm_b200_encode_tensor& t, ChainDef& c, std::string& why) {
+    using namespace detail;
+    auto src = [&](uint16_t cd) { return std::make_pair(uint16_t(OP_SOURCE), source_params(t.shape, t.ndim, cd)); };
+    auto op = [](uint16_t id, std::vector<uint8_t> p = {}) { return std::make_pair(id, p); };
+    const uint16_t dt = t.dtype_code;
+    if (t.usage == 1) {
+        if (dt == 29) c = {K_PASS, {src(0x0010), op(OP_PASS)}, {0x01}};
+        else if (dt == 13) c = {K_PASS, {src(0x0006), op(OP_PASS)}, {0x00}};
+        else { why = "scale usage needs float8_e4m3fn or uint8"; return false; }
+    } else if (t.usage == 2) c = {K_PASS, {src(0x0003), op(OP_PASS)}, {0x08 + 3}};
+    else if (t.usage == 3 || dt == 31) c = {K_PASS, {src(0x001F), op(OP_PASS)}, {0x18}};
+    else if (dt == 6 || dt == 4) c = {K_M16, {src(0x000F), op(OP_R16), op(OP_BYTESPLIT, {2})}, {0x40 + 8 * 1 + 0, 0x19}};  // fp16 rides the bf16 chain (_chains.py:326)
+    else if (dt == 1) c = {K_M32, {src(0x0003), op(OP_R32), op(OP_BYTESPLIT, {4})}, {0x40 + 8 * 3 + 0, 0x40 + 8 * 3 + 1, 0x40 + 8 * 3 + 2, 0x19}};
+    else if (dt == 29) c = {K_E4M3, {src(0x0010), op(OP_RE4M3), op(OP_NIBSPLIT)}, {0x10, 0x11}};
+    else if (dt == 30) c = {K_E5M2, {src(0x0011), op(OP_RE5M2), op(OP_NIBSPLIT)}, {0x10, 0x11}};
+    else if (dt == 13 || dt == 17) c = {K_PASS, {src(uint16_t(chain_dtype_for_public(dt))), op(OP_PASS)}, {0xC0 + 8 - 1}};
+    else { why = "no production chain for dtype code " + std::to_string(dt); return false; }
+    return true;
+}
+
+uint8_t plane_role_byte(uint8_t role) {  // compressor.rs:124-147
+    if (role >= 0x40 && role < 0x80) return 5;
+    switch (role) {
+        case 0x00: case 0x01: case 0x0B: return 2;
+        case 0x10: case 0x19: return 3;
+        case 0x11: return 4;
+        default: return 1;
+    }
+}
+
+struct PlanePlan {
+    uint64_t len = 0, buf_off = 0;   // bytes, offset in the planes buffer
+    uint32_t first_chunk = 0, n_chunks = 0;
+    int codec = C_IDENTITY;
+    uint32_t crc = 0;
+    // layout
+    std::vector<uint64_t> frame_size;  // per chunk (or one entry for an empty plane)
+    uint64_t payload_len = 0;
+};
+struct TensorPlan {
+    ChainDef chain;
+    uint32_t chain_id = 0;
+    std::vector<PlanePlan> planes;
+    uint64_t hash = 0;
+};
+
+// Estimated size of the whole plane under each codec, the way the reference's
+// trial encode compares them (select.rs:27-64 over dispatch.rs:13-49: Huffman,
+// rANS, then Identity; the first smallest wins).  Huffman is exact up to the
+// per-stream byte rounding, rANS uses the table's information content.
+int select_codec(const unsigned long long* hist, uint64_t n, uint32_t menu) {
+    double best = 0; int best_codec = -1;
+    auto offer = [&](int codec, double size) { if (best_codec < 0 || size < best) { best = size; best_codec = codec; } };
+    uint32_t raw32[256];
+    for (int i = 0; i < 256; ++i) raw32[i] = uint32_t(hist[i]);
+    if ((menu & PTWM_B200_MENU_HUFFMAN)) {
+        double size = 1;
+        if (n) {
+            uint8_t lengths[256], alive[512], sym_of[256]; uint16_t parent[512]; uint64_t nf[512], raw[256];
+            for (int i = 0; i < 256; ++i) raw[i] = hist[i];
+            int nw = huffman_lengths<uint64_t>(raw, lengths, nf, parent, alive, sym_of);
+            double bits = 0;
+            for (int i = 0; i < 256; ++i) bits += double(hist[i]) * lengths[i];
+            double blob = (nw <= 127 ? 1 : 2) + (nw + 1) / 2 + 16 + std::ceil(bits / 8) + 2;
+            size = blob >= double(n) ? 1.0 + double(n) : 5.0 + blob;
+        }
+        offer(C_HUFFMAN, size);
+    }
+    if ((menu & PTWM_B200_MENU_RANS)) {
+        double size = 1;
+        if (n) {
+            uint16_t freqs[256];
+            int ms = rans_normalize(raw32, n, freqs);
+            if (ms < 0) size = 1.0 + double(n);
+            else {
+                double bits = 0;
+                for (int i = 0; i < 256; ++i) if (hist[i]) bits += double(hist[i]) * std::log2(2048.0 / freqs[i]);
+                double blob = 1 + 2 * (ms + 1) + 16 + 16 + std::ceil(bits / 8) + 2;
+                size = blob >= double(n) ? 1.0 + double(n) : 5.0 + blob;
+            }
+        }
+        offer(C_RANS, size);
+    }
+    if ((menu & PTWM_B200_MENU_IDENTITY)) offer(C_IDENTITY, double(n));
+    return best_codec;
+}
+
+struct Piece { uint64_t dst; std::vector<uint8_t> bytes; };
+
+}  // namespace
+
+struct ptwm_b200_encoded {
+    uint8_t* d_out = nullptr;
+    uint64_t size = 0;
+    int device = 0;
+    std::vector<std::vector<int>> plane_codecs;
+    ~ptwm_b200_encoded() { if (d_out) { DeviceGuard g{device}; cudaFree(d_out); } }
+};
+
+namespace {
+
+struct DeviceBuf {
+    void* p = nullptr;
+    ~DeviceBuf() { if (p) cudaFree(p); }
+    template <class T> T* as() { return static_cast<T*>(p); }
+    cudaError_t alloc(size_t n) { return cudaMalloc(&p, n ? n : 1); }
+};
+
+template <class T>
+cudaError_t upload_vec(DeviceBuf& b, const std::vector<T>& v, cudaStream_t st) {
+    cudaError_t e = b.alloc(v.size() * sizeof(T));
+    if (e != cudaSuccess || v.empty()) return e;
+    return cudaMemcpyAsync(b.p, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice, st);
+}
+
+int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, const ptwm_b200_encode_options& opt, int device, cudaStream_t st,
+                    CrcTables* d_tabs, ptwm_b200_encoded& enc) {
+    const uint32_t chunk_size = opt.chunk_size ? opt.chunk_size : 65536u;
+    const uint32_t menu = opt.menu ? opt.menu : 7u;
+    if (opt.forced_codec >= 0 && opt.forced_codec != C_IDENTITY && opt.forced_codec != C_HUFFMAN && opt.forced_codec != C_RANS)
+        return fail(PTWM_RC_UNSUPPORTED, "device encode offers identity, huffman and rans");
+
+    // ---- chains, registry, planes, chunks -----------------------------------
+    std::vector<TensorPlan> plan(n_tensors);
+    std::vector<ChainDef> registry;
+    std::vector<SplitItem> splits;
+    std::vector<EncChunk> chunks;
+    std::vector<HashItem> hash_items;
+    uint64_t planes_bytes = 0, slots_bytes = 0;
+    uint32_t n_planes = 0, tile = 0;
+    for (size_t i = 0; i < n_tensors; ++i) {
+        const ptwm_b200_encode_tensor& t = tensors[i];
+        std::string why;
+        if (!t.name || !*t.name || std::strlen(t.name) > 65535) return fail(PTWM_RC_INVALID_INPUT, "tensor name must be 1..65535 bytes");
+        if (t.ndim > 8) return fail(PTWM_RC_UNSUPPORTED, "more than 8 dimensions");
+        if (!chain_for(t, plan[i].chain, why)) return fail(PTWM_RC_UNSUPPORTED, std::string(t.name) + ": " + why);
+        uint64_t elems = 1;
+        for (int d = 0; d < t.ndim; ++d) { if (t.shape[d] > 0xFFFFFFFFull) return fail(PTWM_RC_UNSUPPORTED, "dimension exceeds u32"); elems *= t.shape[d]; }
+        if (elems * detail::public_dtype_bytes(t.dtype_code) != t.nbytes) return fail(PTWM_RC_INVALID_INPUT, std::string(t.name) + ": nbytes does not match shape x dtype");
+        if (t.nbytes && !t.dev_ptr) return fail(PTWM_RC_INVALID_INPUT, "null device pointer");
+        // a Source whose params equal the record's own shape/dtype is written bound (empty params): compressor.rs:708-715
+        ChainDef reg = plan[i].chain;
+        int cd = detail::chain_dtype_for_public(t.dtype_code);
+        if (cd >= 0 && reg.nodes[0].second == source_params(t.shape, t.ndim, uint16_t(cd))) reg.nodes[0].second.clear();
+        auto found = std::find(registry.begin(), registry.end(), reg);
+        if (found == registry.end()) { registry.push_back(reg); found = registry.end() - 1; }
+        plan[i].chain_id = uint32_t(found - registry.begin());
+        if (registry.size() > 0x8000) return fail(PTWM_RC_UNSUPPORTED, "more than 32768 distinct chains");
+        const int kind = plan[i].chain.kind, np = kind_planes(kind);
+        const uint64_t plane_len = t.nbytes / uint64_t(kind_elem_bytes(kind));
+        if (plane_len > 0xFFFFFFFFull) return fail(PTWM_RC_UNSUPPORTED, "plane longer than 4 GiB");
+        SplitItem sp{reinterpret_cast<const uint8_t*>(uintptr_t(t.dev_ptr)), {0, 0, 0, 0}, plane_len, uint32_t(kind), tile};
+        plan[i].planes.resize(size_t(np));
+        for (int p = 0; p < np; ++p) {
+            PlanePlan& pp = plan[i].planes[size_t(p)];
+            pp.len = plane_len; pp.buf_off = planes_bytes; pp.first_chunk = uint32_t(chunks.size());
+            sp.plane_off[p] = planes_bytes;
+            planes_bytes += align_up(plane_len, 16);
+            for (uint64_t off = 0; off < plane_len; off += chunk_size) {
+                uint32_t n = uint32_t(std::min<uint64_t>(chunk_size, plane_len - off));
+                uint32_t cap = uint32_t(align_up(uint64_t((n + 3) / 4) * 3 / 2 + 16, 16));  // <= 12 bits per symbol plus the rANS state
+                chunks.push_back(EncChunk{pp.buf_off + off, 0, n, cap, n_planes, 0});
+            }
+            pp.n_chunks = uint32_t(chunks.size()) - pp.first_chunk;
+            ++n_planes;
+        }
+        if (plane_len) { splits.push_back(sp); tile += uint32_t((plane_len + SPLIT_TILE - 1) / SPLIT_TILE); }
+        if (opt.emit_payload_hash) hash_items.push_back(HashItem{make_ref(SP_BLOB, t.dev_ptr), t.nbytes});
+    }
+    const uint32_t n_chunks = uint32_t(chunks.size());
+
+    // ---- device pipeline: split, histograms ---------------------------------
+    DeviceBuf d_planes, d_splits, d_chunks, d_hist, d_plane_hist, d_codec, d_tables, d_results, d_slots;
+    CUDA_TRY(d_planes.alloc(planes_bytes));
+    CUDA_TRY(upload_vec(d_splits, splits, st));
+    CUDA_TRY(upload_vec(d_chunks, chunks, st));
+    CUDA_TRY(d_hist.alloc(uint64_t(n_chunks) * 1024));
+    CUDA_TRY(d_plane_hist.alloc(uint64_t(n_planes) * 256 * 8));
+    CUDA_TRY(cudaMemsetAsync(d_plane_hist.p, 0, uint64_t(n_planes) * 256 * 8 + (n_planes ? 0 : 1), st));
+    if (tile) { split_kernel<<<tile, 256, 0, st>>>(d_splits.as<SplitItem>(), uint32_t(splits.size()), d_planes.as<uint8_t>()); CUDA_TRY(cudaGetLastError()); }
+    if (n_chunks) { hist_kernel<<<n_chunks, 128, 0, st>>>(d_chunks.as<EncChunk>(), d_planes.as<uint8_t>(), d_hist.as<uint32_t>(), d_plane_hist.as<unsigned long long>()); CUDA_TRY(cudaGetLastError()); }
+    std::vector<unsigned long long> plane_hist(size_t(n_planes) * 256);
+    if (n_planes) CUDA_TRY(cudaMemcpyAsync(plane_hist.data(), d_plane_hist.p, plane_hist.size() * 8, cudaMemcpyDeviceToHost, st));
+
+    // plane CRCs and payload hashes run on the same stream meanwhile
+    DeviceBuf d_verify, d_acc, d_hitems, d_hout;
+    std::vector<VerifyTensor> verify;
+    uint64_t n_runs = 0;
+    if (opt.emit_plane_crc) {
+        uint32_t acc = 0;
+        for (auto& tp : plan) for (auto& pp : tp.planes) {
+            if (pp.len) { verify.push_back(VerifyTensor{make_ref(SP_OUT, pp.buf_off), pp.len, n_runs, K_PASS, acc}); n_runs += (pp.len + VERIFY_RUN - 1) / VERIFY_RUN; }
+            ++acc;
+        }
+        CUDA_TRY(upload_vec(d_verify, verify, st));
+        CUDA_TRY(d_acc.alloc(uint64_t(n_planes) * 4));
+        CUDA_TRY(cudaMemsetAsync(d_acc.p, 0, uint64_t(n_planes) * 4 + (n_planes ? 0 : 1), st));
+        if (n_runs) {
+            Bases b{nullptr, 0, 0, nullptr, d_planes.as<uint8_t>()};
+            crc_planes_kernel<<<uint32_t((n_runs + 127) / 128), 128, 0, st>>>(d_verify.as<VerifyTensor>(), uint32_t(verify.size()), n_runs, b, d_tabs, d_acc.as<uint32_t>());
+            CUDA_TRY(cudaGetLastError());
+        }
+    }
+    std::vector<uint64_t> hashes(hash_items.size());
+    if (!hash_items.empty()) {
+        CUDA_TRY(upload_vec(d_hitems, hash_items, st));
+        CUDA_TRY(d_hout.alloc(hash_items.size() * 8));
+        Bases b{nullptr, 0, 0, nullptr, nullptr};
+        xxh64_kernel<<<uint32_t((hash_items.size() + 7) / 8), 32, 0, st>>>(d_hitems.as<HashItem>(), uint32_t(hash_items.size()), b, d_hout.as<uint64_t>());
+        CUDA_TRY(cudaGetLastError());
+        CUDA_TRY(cudaMemcpyAsync(hashes.data(), d_hout.p, hashes.size() * 8, cudaMemcpyDeviceToHost, st));
+    }
+    std::vector<uint32_t> accs(n_planes);
+    if (opt.emit_plane_crc && n_planes) CUDA_TRY(cudaMemcpyAsync(accs.data(), d_acc.p, accs.size() * 4, cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaStreamSynchronize(st));
+
+    // ---- codec per plane ------------------------------------------------------
+    std::vector<uint8_t> plane_codec(n_planes);
+    {
+        uint32_t pi = 0;
+        const CrcTables& T = crc_tables();
+        for (size_t i = 0; i < n_tensors; ++i) {
+            enc.plane_codecs.emplace_back();
+            for (auto& pp : plan[i].planes) {
+                pp.codec = opt.forced_codec >= 0 ? opt.forced_codec : select_codec(&plane_hist[size_t(pi) * 256], pp.len, menu);
+                if (pp.codec < 0) return fail(PTWM_RC_INVALID_INPUT, "empty codec menu");
+                plane_codec[pi] = uint8_t(pp.codec);
+                enc.plane_codecs.back().push_back(pp.codec);
+                if (opt.emit_plane_crc) pp.crc = pp.len ? ~(accs[pi] ^ gf2_mulmod(x_pow_8n(T.x2n, pp.len), 0xFFFFFFFFu)) : 0u;
+                if (pp.codec != C_IDENTITY)  // stream slots only for planes that get coded
+                    for (uint32_t k = 0; k < pp.n_chunks; ++k) { EncChunk& ch = chunks[pp.first_chunk + k]; ch.slot_off = slots_bytes; slots_bytes += uint64_t(ch.slot_cap) * 4; }
+                ++pi;
+            }
+            if (opt.emit_payload_hash) plan[i].hash = hashes[i];
+        }
+    }
+
+    // ---- tables and streams ---------------------------------------------------
+    CUDA_TRY(upload_vec(d_codec, plane_codec, st));
+    if (n_chunks) CUDA_TRY(cudaMemcpyAsync(d_chunks.p, chunks.data(), chunks.size() * sizeof(EncChunk), cudaMemcpyHostToDevice, st));
+    CUDA_TRY(d_tables.alloc(uint64_t(n_chunks) * ENC_TABLE_BYTES));
+    CUDA_TRY(d_results.alloc(uint64_t(n_chunks) * sizeof(EncResult)));
+    CUDA_TRY(d_slots.alloc(slots_bytes));
+    std::vector<EncResult> results(n_chunks);
+    if (n_chunks) {
+        table_kernel<<<(n_chunks + 63) / 64, 64, 0, st>>>(d_chunks.as<EncChunk>(), n_chunks, d_codec.as<uint8_t>(), d_hist.as<uint32_t>(), d_tables.as<uint8_t>(), d_results.as<EncResult>());
+        CUDA_TRY(cudaGetLastError());
+        encode_kernel<<<(n_chunks * 4 + 127) / 128, 128, 0, st>>>(d_chunks.as<EncChunk>(), n_chunks, d_codec.as<uint8_t>(), d_planes.as<uint8_t>(), d_tables.as<uint8_t>(), d_slots.as<uint8_t>(), d_results.as<EncResult>());
+        CUDA_TRY(cudaGetLastError());
+        CUDA_TRY(cudaMemcpyAsync(results.data(), d_results.p, results.size() * sizeof(EncResult), cudaMemcpyDeviceToHost, st));
+    }
+    CUDA_TRY(cudaStreamSynchronize(st));
+
+    // ---- layout: chunk frames, plane payloads, records ------------------------
+    std::vector<uint32_t> chunk_mode(n_chunks);
+    for (auto& tp : plan) for (auto& pp : tp.planes) {
+        if (pp.len == 0) {  // an empty plane is one empty chunk (compressor.rs:333-345)
+            pp.frame_size.push_back(pp.codec == C_IDENTITY ? 5 : 6);
+            pp.payload_len = pp.frame_size[0];
+            continue;
+        }
+        for (uint32_t k = 0; k < pp.n_chunks; ++k) {
+            uint32_t ci = pp.first_chunk + k;
+            const EncResult& r = results[ci];
+            uint64_t n = chunks[ci].n, size;
+            if (pp.codec == C_IDENTITY) { chunk_mode[ci] = 0; size = 5 + n; }
+            else {
+                uint64_t hdr = pp.codec == C_RANS ? 1 + 2 * (uint64_t(r.hdr_n) + 1) : (r.hdr_n <= 127 ? 1 : 2) + (uint64_t(r.hdr_n) + 1) / 2;
+                uint64_t blob = hdr + 16 + uint64_t(r.stream_len[0]) + r.stream_len[1] + r.stream_len[2] + r.stream_len[3];
+                // stored raw when coding does not shrink the chunk (compress.rs NotBeneficial) or the length rule refuses it (length_prefix.rs:29-33)
+                bool coded = r.coded && blob < n && (pp.codec != C_RANS || n <= (1ull << 30) || n <= blob * 64);
+                chunk_mode[ci] = coded ? (pp.codec == C_RANS ? 2 : 3) : 1;
+                size = coded ? 5 + 1 + 4 + blob : 5 + 1 + n;
+            }
+            pp.frame_size.push_back(size);
+            pp.payload_len += size;
+        }
+        if (pp.payload_len > 0xFFFFFFFFull) return fail(PTWM_RC_UNSUPPORTED, "chunked plane payload exceeds the u32 offset range (compressor.rs:370-372)");
+    }
+
+    // Extension Table: chain ops in registry order, then the used codecs in built-in order (container.rs:167-223)
+    std::vector<std::pair<uint8_t, uint16_t>> table;
+    for (auto& c : registry) for (auto& nd : c.nodes) if (std::find(table.begin(), table.end(), std::make_pair(uint8_t(1), nd.first)) == table.end()) table.push_back({1, nd.first});
+    for (int codec : {int(C_IDENTITY), int(C_HUFFMAN), int(C_RANS)}) {
+        bool used = false;
+        for (auto& tp : plan) for (auto& pp : tp.planes) used |= pp.codec == codec;
+        if (used) table.push_back({2, uint16_t(codec)});
+    }
+    auto table_index = [&](uint8_t tag, uint16_t id) { return uint64_t(std::find(table.begin(), table.end(), std::make_pair(tag, id)) - table.begin()); };
+    std::vector<uint8_t> et, prelude(4, 0), reg;
+    put_varint(et, table.size());
+    for (auto& e : table) { et.push_back(e.first); put_varint(et, e.second); }
+    put_varint(reg, registry.size());
+    for (auto& c : registry) {  // CW2, every edge a spine edge (chain/wire_compact.rs:140-245)
+        std::vector<uint8_t> cb;
+        put_varint(cb, c.nodes.size()); put_varint(cb, c.nodes.size() - 1); put_varint(cb, c.roles.size());
+        for (auto& nd : c.nodes) { put_varint(cb, table_index(1, nd.first)); put_varint(cb, nd.second.size()); cb.insert(cb.end(), nd.second.begin(), nd.second.end()); }
+        if (c.nodes.size() > 1) put_varint(cb, c.nodes.size() - 1);
+        for (size_t i = 0; i < c.roles.size(); ++i) { cb.push_back(uint8_t(((c.nodes.size() - 1) << 4) | i)); cb.push_back(c.roles[i]); }
+        put_varint(reg, cb.size());
+        reg.insert(reg.end(), cb.begin(), cb.end());
+    }
+    std::vector<uint8_t> head = {0x89, 'P', 'T', 'W', 'C', '\r', '\n', 0x1a, '\n', 0, 0};
+    put_varint(head, et.size()); put_varint(head, prelude.size()); put_varint(head, reg.size());
+    {
+        std::vector<uint8_t> meta = head;
+        meta.insert(meta.end(), et.begin(), et.end()); meta.insert(meta.end(), prelude.begin(), prelude.end()); meta.insert(meta.end(), reg.begin(), reg.end());
+        put_u64(head, xxh64_host(meta.data(), meta.size()));
+    }
+    head.insert(head.end(), et.begin(), et.end()); head.insert(head.end(), prelude.begin(), prelude.end()); head.insert(head.end(), reg.begin(), reg.end());
+
+    std::vector<uint8_t> staged = head;
+    std::vector<uint64_t> triples = {0, 0, head.size()};
+    std::vector<GatherItem> gathers;
+    std::vector<uint8_t> index;
+    put_varint(index, n_tensors);
+    uint64_t pos = head.size();
+    for (size_t i = 0; i < n_tensors; ++i) {
+        const ptwm_b200_encode_tensor& t = tensors[i];
+        const uint64_t rec_start = pos;
+        auto flush = [&](std::vector<uint8_t>& bytes) {
+            triples.push_back(pos); triples.push_back(staged.size()); triples.push_back(bytes.size());
+            staged.insert(staged.end(), bytes.begin(), bytes.end());
+            pos += bytes.size();
+            bytes.clear();
+        };
+        std::vector<uint8_t> b;
+        b.push_back(uint8_t(0x08 | (opt.emit_payload_hash ? 0x01 : 0)));
+        put_varint(b, plan[i].chain_id); put_varint(b, t.dtype_code); b.push_back(2 /* Format.TORCH */); put_varint(b, t.nbytes);
+        put_varint(b, t.ndim);
+        for (int d = 0; d < t.ndim; ++d) put_varint(b, t.shape[d]);
+        if (opt.emit_payload_hash) put_u64(b, plan[i].hash);
+        put_varint(b, plan[i].planes.size());
+        for (size_t p = 0; p < plan[i].planes.size(); ++p) {
+            PlanePlan& pp = plan[i].planes[p];
+            b.push_back(uint8_t(0x02 | (opt.emit_plane_crc ? 0x01 : 0)));
+            b.push_back(plane_role_byte(plan[i].chain.roles[p]));
+            put_varint(b, table_index(2, uint16_t(pp.codec)));
+            put_varint(b, pp.payload_len);
+            if (opt.emit_plane_crc) put_u32(b, pp.crc);
+            put_varint(b, pp.frame_size.size());
+            uint64_t off = 0;
+            for (size_t k = 0; k < pp.frame_size.size(); ++k) {
+                put_varint(b, off);
+                put_varint(b, pp.len ? chunks[pp.first_chunk + k].n : 0);
+                off += pp.frame_size[k];
+            }
+            if (pp.len == 0) {  // the one empty frame is host data
+                for (int z = 0; z < 5; ++z) b.push_back(0);
+                if (pp.codec != C_IDENTITY) b.push_back(0);
+                flush(b);
+                continue;
+            }
+            flush(b);
+            for (size_t k = 0; k < pp.frame_size.size(); ++k) {
+                gathers.push_back(GatherItem{pos, pp.first_chunk + uint32_t(k), chunk_mode[pp.first_chunk + k]});
+                pos += pp.frame_size[k];
+            }
+        }
+        if (!b.empty()) flush(b);
+        size_t nl = std::strlen(t.name);
+        put_varint(index, nl); index.insert(index.end(), t.name, t.name + nl); put_varint(index, pos - rec_start);
+    }
+    {
+        std::vector<uint8_t> tail = index;
+        put_u64(tail, index.size());
+        const uint8_t eofs[8] = {0x89, 'T', 'W', 'M', 'E', 'O', 'F', 0x1a};
+        tail.insert(tail.end(), eofs, eofs + 8);
+        triples.push_back(pos); triples.push_back(staged.size()); triples.push_back(tail.size());
+        staged.insert(staged.end(), tail.begin(), tail.end());
+        pos += tail.size();
+    }
+
+    // ---- write the container ----------------------------------------------------
+    enc.size = pos; enc.device = device;
+    CUDA_TRY(cudaMalloc(&enc.d_out, pos));
+    DeviceBuf d_staged, d_triples, d_gathers;
+    CUDA_TRY(upload_vec(d_staged, staged, st));
+    CUDA_TRY(upload_vec(d_triples, triples, st));
+    CUDA_TRY(upload_vec(d_gathers, gathers, st));
+    scatter_kernel<<<uint32_t(triples.size() / 3), 128, 0, st>>>(d_staged.as<uint8_t>(), d_triples.as<uint64_t>(), enc.d_out);
+    CUDA_TRY(cudaGetLastError());
+    if (!gathers.empty()) {
+        gather_kernel<<<uint32_t(gathers.size()), 128, 0, st>>>(d_gathers.as<GatherItem>(), d_chunks.as<EncChunk>(), d_results.as<EncResult>(), d_planes.as<uint8_t>(),
+                                                                d_tables.as<uint8_t>(), d_slots.as<uint8_t>(), enc.d_out);
+        CUDA_TRY(cudaGetLastError());
+    }
+    CUDA_TRY(cudaStreamSynchronize(st));
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t ptwm_b200_encode_model(const ptwm_b200_encode_tensor* tensors, size_t n, const ptwm_b200_encode_options* options, uint32_t device_ordinal, uint64_t stream,
+                               ptwm_b200_encoded** out) {
+    if ((!tensors && n) || !out) return fail(PTWM_RC_INVALID_INPUT, "null argument");
+    ptwm_b200_encode_options opt{0, 0, -1, 0, 0, {0, 0}};
+    if (options) opt = *options;
+    DeviceGuard guard{int(device_ordinal)};
+    if (guard.err != cudaSuccess) return fail(PTWM_RC_CUDA, std::string("cudaSetDevice: ") + cudaGetErrorString(guard.err));
+    DeviceState* ds;
+    int64_t rc = device_state(int(device_ordinal), &ds);
+    if (rc < 0) return rc;
+    cudaStream_t st = stream ? reinterpret_cast<cudaStream_t>(uintptr_t(stream)) : ds->stream;
+    try {
+        std::unique_ptr<ptwm_b200_encoded> e(new ptwm_b200_encoded);
+        rc = encode_impl(tensors, n, opt, int(device_ordinal), st, ds->d_tabs, *e);
+        if (rc < 0) return rc;
+        *out = e.release();
+        return 0;
+    } catch (const std::exception& ex) { return fail(PTWM_RC_INTERNAL, ex.what()); }
+}
+uint64_t ptwm_b200_encoded_size(const ptwm_b200_encoded* e) { return e ? e->size : 0; }
+uint64_t ptwm_b200_encoded_device_ptr(const ptwm_b200_encoded* e) { return e ? uint64_t(reinterpret_cast<uintptr_t>(e->d_out)) : 0; }
+int64_t ptwm_b200_encoded_copy(const ptwm_b200_encoded* e, uint8_t* host_dst, size_t cap) {
+    if (!e || !host_dst) return fail(PTWM_RC_INVALID_INPUT, "null argument");
+    if (cap < e->size) return fail(PTWM_RC_BUFFER_TOO_SMALL, "host buffer smaller than the container");
+    DeviceGuard guard{e->device};
+    CUDA_TRY(cudaMemcpy(host_dst, e->d_out, e->size, cudaMemcpyDeviceToHost));
+    return int64_t(e->size);
+}
+int64_t ptwm_b200_encoded_copy_to_device(const ptwm_b200_encoded* e, uint64_t dst_dev_ptr, uint64_t cap, uint64_t stream) {
+    if (!e || !dst_dev_ptr) return fail(PTWM_RC_INVALID_INPUT, "null argument");
+    if (cap < e->size) return fail(PTWM_RC_BUFFER_TOO_SMALL, "device buffer smaller than the container");
+    DeviceGuard guard{e->device};
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(uintptr_t(stream));
+    CUDA_TRY(cudaMemcpyAsync(reinterpret_cast<void*>(uintptr_t(dst_dev_ptr)), e->d_out, e->size, cudaMemcpyDeviceToDevice, st));
+    CUDA_TRY(cudaStreamSynchronize(st));
+    return int64_t(e->size);
+}
+int32_t ptwm_b200_encoded_plane_codec(const ptwm_b200_encoded* e, size_t tensor, size_t plane) {
+    if (!e || tensor >= e->plane_codecs.size() || plane >= e->plane_codecs[tensor].size()) return -1;
+    return e->plane_codecs[tensor][plane];
+}
+void ptwm_b200_encoded_free(ptwm_b200_encoded* e) { delete e; }
+
+}  // extern "C"

@@ -1,8 +1,6 @@
 // Host side of libptwm_b200.so: the planner that flattens a parsed container
 // into kernel work lists, the runner that launches them, and the C ABI
 // declared in include/ptwm_b200.h.
-#include "../../include/ptwm_b200.h"
-
 #include <algorithm>
 #include <map>
 #include <memory>
@@ -11,26 +9,15 @@
 #include <vector>
 
 #include "format.hpp"
-#include "kernels.cuh"
+#include "host_common.hpp"
 
 using namespace ptwm;
 
+namespace ptwm {
+
+std::string& last_error_ref() { thread_local std::string e; return e; }
+
 namespace {
-
-thread_local std::string g_err;
-int64_t fail(int64_t rc, const std::string& m) { g_err = m; return rc; }
-#define CUDA_TRY(expr)                                                                                   \
-    do {                                                                                                 \
-        cudaError_t e_ = (expr);                                                                         \
-        if (e_ != cudaSuccess) return fail(PTWM_RC_CUDA, std::string(#expr) + ": " + cudaGetErrorString(e_)); \
-    } while (0)
-
-// ---- per-device state -------------------------------------------------------
-struct DeviceState {
-    cudaStream_t stream = nullptr;
-    CrcTables* d_tabs = nullptr;
-    bool attrs = false;
-};
 std::mutex g_dev_mu;
 std::map<int, DeviceState> g_dev;
 
@@ -45,16 +32,10 @@ CrcTables host_crc_tables() {
     for (int k = 0; k < 64; ++k) { t.x2n[k] = p; p = gf2_mulmod(p, p); }
     return t;
 }
+}  // namespace
+
 const CrcTables& crc_tables() { static CrcTables t = host_crc_tables(); return t; }
 
-struct DeviceGuard {
-    int prev = -1;
-    cudaError_t err;
-    explicit DeviceGuard(int dev) { err = cudaGetDevice(&prev); if (err == cudaSuccess && prev != dev) err = cudaSetDevice(dev); }
-    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
-};
-
-// Caller holds a DeviceGuard for `dev`.
 int64_t device_state(int dev, DeviceState** out) {
     std::lock_guard<std::mutex> g(g_dev_mu);
     DeviceState& s = g_dev[dev];
@@ -73,7 +54,7 @@ int64_t device_state(int dev, DeviceState** out) {
     return 0;
 }
 
-}  // namespace
+}  // namespace ptwm
 
 struct ptwm_b200_container {
     ParsedFile file;
@@ -131,7 +112,6 @@ struct ptwm_b200_plan {
 
 namespace {
 
-uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
 int codec_class(uint16_t codec) { return codec == C_RANS ? 0 : codec == C_HUFFMAN ? 1 : codec == C_TANS ? 2 : 3; }
 
 // Turn one tensor into work items.  See DecodeItem / MergeItem in plan.h.
@@ -463,7 +443,7 @@ uint64_t stream_handle(uint32_t device) {
 
 extern "C" {
 
-const char* ptwm_b200_last_error(void) { return g_err.c_str(); }
+const char* ptwm_b200_last_error(void) { return last_error_ref().c_str(); }
 
 uint64_t ptwm_hardware_backend_v1_cuda_stream_handle(uint32_t device_ordinal) { return stream_handle(device_ordinal); }
 uint64_t ptwm_plane_codec_v1_cuda_stream_handle(uint32_t device_ordinal) { return stream_handle(device_ordinal); }

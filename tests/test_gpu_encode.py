@@ -1,0 +1,70 @@
+"""The device encoder against the CPU oracle: forced-codec containers must be
+byte-identical to what the oracle's writer (a restatement of the reference's
+compressor) produces, selected-codec containers must decode in the oracle
+and stay within 1 % of its size."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import ptwm_b200
+from ptwm_b200.compressor import CompressionConfig, HUFFMAN, IDENTITY, RANS, compress_model
+from _data import mixed_model
+
+pytestmark = pytest.mark.gpu
+
+_TORCH = {oracle.DT_BF16: torch.bfloat16, oracle.DT_F16: torch.float16, oracle.DT_F32: torch.float32, oracle.DT_E4M3: torch.float8_e4m3fn,
+          oracle.DT_U8: torch.uint8, oracle.DT_FP4X2: torch.uint8}
+
+
+def to_cuda(specs):
+    """specs -> ({name: cuda tensor}, usage map, specs as the device encoder sees them)"""
+    tensors, usage, seen = {}, {}, []
+    for s in specs:
+        dt = _TORCH[s.dtype_code]
+        t = torch.frombuffer(bytearray(s.raw), dtype=torch.uint8).view(dt).reshape(list(s.shape)) if s.raw else torch.empty(list(s.shape), dtype=dt)
+        tensors[s.name] = t.cuda()
+        spec = s
+        if s.dtype_code == oracle.DT_FP4X2:  # carried as uint8 bytes on both sides; the fp4 chain still applies through `usage`
+            spec = oracle.TensorSpec(s.name, oracle.DT_U8, s.shape, s.raw, usage="fp4")
+        if spec.usage != "standard":
+            usage[s.name] = spec.usage
+        seen.append(spec)
+    return tensors, usage, seen
+
+
+@pytest.mark.parametrize("codec", [IDENTITY, HUFFMAN, RANS])
+@pytest.mark.parametrize("chunk,crc,hash_", [(4096, True, False), (1000, False, True), (65536, True, True)])
+def test_forced_codec_bytes_equal_oracle(codec, chunk, crc, hash_):
+    tensors, usage, specs = to_cuda(mixed_model())
+    enc = compress_model(tensors, CompressionConfig(streaming_chunk=chunk, forced_codec=codec, emit_plane_crc=crc, emit_payload_hash=hash_), usage=usage)
+    got = enc.to_bytes()
+    want = oracle.write_container(specs, chunk_size=chunk, forced_codec=codec, emit_crc=crc, emit_hash=hash_)
+    if got != want:
+        first = next(i for i in range(min(len(got), len(want))) if got[i] != want[i])
+        raise AssertionError(f"container differs at byte {first} (sizes {len(got)} / {len(want)})")
+
+
+def test_selected_codecs_decode_in_oracle_and_match_size():
+    tensors, usage, specs = to_cuda(mixed_model(2))
+    for menu in ((IDENTITY, HUFFMAN, RANS), (HUFFMAN, RANS), (IDENTITY, HUFFMAN)):
+        enc = compress_model(tensors, CompressionConfig(streaming_chunk=8192, codec_menu=menu, emit_plane_crc=True), usage=usage)
+        blob = enc.to_bytes()
+        oc = oracle.Container(blob)
+        for i, s in enumerate(specs):
+            assert oc.decode(i) == s.raw, s.name
+        want = oracle.write_container(specs, chunk_size=8192, menu=menu, emit_crc=True)
+        assert abs(len(blob) - len(want)) <= 0.01 * len(want), (menu, len(blob), len(want))
+        # and the device decoder reads its own writer's output from device memory
+        h = ptwm_b200.ContainerHandle(enc.to_tensor().cpu().numpy().tobytes(), device=0)
+        for (name, t), s in zip(h.decode_model(), specs):
+            assert t.contiguous().view(torch.uint8).cpu().numpy().tobytes() == s.raw, name
+
+
+def test_encode_rejects_host_tensors_and_unknown_codec():
+    with pytest.raises(ValueError):
+        compress_model({"a": torch.zeros(4)})
+    with pytest.raises(ValueError):
+        compress_model({"a": torch.zeros(4, device="cuda")}, CompressionConfig(codec_menu=(7,)))
+    with pytest.raises(ptwm_b200.PtwmError):
+        compress_model({"a": torch.zeros(4, device="cuda")}, CompressionConfig(forced_codec=7))
