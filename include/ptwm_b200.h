@@ -128,6 +128,7 @@ void ptwm_b200_plan_stats(const ptwm_b200_plan* p, uint64_t* bytes_read, uint64_
 #define PTWM_B200_VERIFY_CRC  1u   /* check the plane CRC-32s the records carry */
 #define PTWM_B200_VERIFY_HASH 2u   /* check the XXH64 payload hashes the records carry */
 #define PTWM_B200_NO_SYNC     4u   /* enqueue only; call ptwm_b200_plan_finish later */
+#define PTWM_B200_TIME_KERNELS 8u  /* record CUDA events around every launch (read with ptwm_b200_plan_timings) */
 
 /* Decode the planned tensors.  blob_dev_ptr addresses file offset 0 of the
  * container on the device (see ptwm_b200_plan_blob_span), of which bytes
@@ -185,6 +186,14 @@ int64_t ptwm_b200_encoded_copy_to_device(const ptwm_b200_encoded* e, uint64_t ds
 /* Codec wire id chosen for plane `plane` of tensor `tensor`, or -1. */
 int32_t ptwm_b200_encoded_plane_codec(const ptwm_b200_encoded* e, size_t tensor, size_t plane);
 void ptwm_b200_encoded_free(ptwm_b200_encoded* e);
+
+/* Per-launch figures of the last finished run made with PTWM_B200_TIME_KERNELS.
+ * Twelve slots: 0-3 first-pass decoders (rANS, Huffman, tANS, Order1ScaleAC),
+ * 4 copies to scratch, 5-8 second-pass decoders (fused with the merge where a
+ * tensor has several planes), 9 stand-alone merge, 10 plane CRC, 11 XXH64.
+ * ms[s] < 0: the slot did not launch.  bytes[s]: algorithmic bytes (compressed
+ * and partner bytes read + bytes written) of the slot; items[s]: work items. */
+int64_t ptwm_b200_plan_timings(ptwm_b200_plan* p, uint32_t device_ordinal, float* ms, uint64_t* bytes, uint32_t* items);
 
 /* CRC-32 computed the way the verification kernel does it (per-run remainders,
  * GF(2) shifts, XOR fold), on the host, for testing that arithmetic without a GPU. */

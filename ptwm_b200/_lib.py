@@ -76,6 +76,7 @@ _SIGNATURES = {
     "ptwm_b200_plan_run": (C.c_int64, [C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint32,
                                        C.c_uint32, C.c_uint64]),
     "ptwm_b200_plan_finish": (C.c_int64, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint64]),
+    "ptwm_b200_plan_timings": (C.c_int64, [C.c_void_p, C.c_uint32, C.POINTER(C.c_float), C.POINTER(C.c_uint64), C.POINTER(C.c_uint32)]),
     "ptwm_b200_crc32_by_runs": (C.c_uint32, [C.c_char_p, C.c_size_t, C.c_size_t]),
     "ptwm_hardware_backend_v1_cuda_stream_handle": (C.c_uint64, [C.c_uint32]),
     "ptwm_plane_codec_v1_cuda_stream_handle": (C.c_uint64, [C.c_uint32]),

@@ -29,7 +29,8 @@ _TORCH_DTYPES = {1: torch.float32, 2: torch.float32, 4: torch.float16, 5: torch.
 if hasattr(torch, "float4_e2m1fn_x2"):
     _TORCH_DTYPES[31] = torch.float4_e2m1fn_x2
 
-VERIFY_CRC, VERIFY_HASH, NO_SYNC = 1, 2, 4
+VERIFY_CRC, VERIFY_HASH, NO_SYNC, TIME_KERNELS = 1, 2, 4, 8
+SLOT_NAMES = ("rans", "huffman", "tans", "o1sac", "copy_to_scratch", "rans_fused", "huffman_fused", "tans_final", "o1sac_final", "merge", "crc32", "xxh64")
 
 
 class PtwmError(RuntimeError):
@@ -102,6 +103,12 @@ class DecodePlan:
         if stream is None:
             stream = torch.cuda.current_stream(device).cuda_stream
         _check(_lib.lib().ptwm_b200_plan_finish(self._p, flags, device, stream))
+
+    def timings(self, device: int) -> dict:
+        """{slot name: (milliseconds, algorithmic bytes, items)} of the last run made with TIME_KERNELS."""
+        ms, by, it = (C.c_float * 12)(), (C.c_uint64 * 12)(), (C.c_uint32 * 12)()
+        _check(_lib.lib().ptwm_b200_plan_timings(self._p, device, ms, by, it))
+        return {SLOT_NAMES[s]: (ms[s], by[s], it[s]) for s in range(12) if ms[s] >= 0}
 
     def views(self, out: torch.Tensor) -> list[torch.Tensor]:
         """Typed, shaped views of the planned tensors inside the output arena."""

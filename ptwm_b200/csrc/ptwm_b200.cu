@@ -77,7 +77,10 @@ struct DevicePlan {
     uint32_t* status = nullptr;        // [0] = summary, [1 + id] per item
     uint32_t* acc = nullptr;
     uint64_t* hash_out = nullptr;
+    cudaEvent_t ev[24] = {nullptr};   // begin/end per launch slot, created on first timed run
+    bool timed[12] = {false};
     void release() {
+        for (auto& e : ev) if (e) cudaEventDestroy(e);
         cudaFree(items); cudaFree(merges); cudaFree(tiles); cudaFree(verify); cudaFree(hashes); cudaFree(status); cudaFree(acc); cudaFree(hash_out);
         *this = DevicePlan{};
     }
@@ -103,6 +106,9 @@ struct ptwm_b200_plan {
     std::vector<HashExpect> hash_expect;
     std::vector<uint32_t> item_tensor;  // item id -> tensor index (for error messages)
     uint32_t launches = 0;
+    // per launch slot: 0-3 phase-0 decoders (rANS, Huffman, tANS, O1SAC), 4 scratch copies, 5-8 phase-1 decoders, 9 final merge, 10 CRC, 11 XXH64
+    uint64_t slot_bytes[12] = {0};
+    uint32_t slot_items[12] = {0};
     std::mutex mu;
     std::map<int, DevicePlan> dev;
     ~ptwm_b200_plan() {
@@ -224,8 +230,16 @@ void finish_lists(ptwm_b200_plan& pl) {
             auto& v = pl.dec[ph][cc];
             std::stable_sort(v.begin(), v.end(), [](const DecodeItem& a, const DecodeItem& b) { return a.n > b.n; });
             if (!v.empty()) pl.launches++;
+            int slot = ph * 5 + cc;
+            pl.slot_items[slot] = uint32_t(v.size());
+            for (auto& it : v) {
+                uint64_t np = it.fused ? uint64_t(kind_planes(it.kind)) : 1, eb = it.fused ? uint64_t(kind_elem_bytes(it.kind)) : 1;
+                pl.slot_bytes[slot] += uint64_t(it.src_len) + it.state_len + uint64_t(it.n) * (np - 1) + uint64_t(it.n) * eb;
+            }
         }
         auto& m = pl.merges[ph];
+        pl.slot_items[ph * 5 + 4] = uint32_t(m.size());
+        for (auto& it : m) pl.slot_bytes[ph * 5 + 4] += uint64_t(it.n) * uint64_t(kind_planes(int(it.kind))) + uint64_t(it.n) * uint64_t(kind_elem_bytes(int(it.kind)));
         pl.tiles[ph].clear();
         uint32_t tile = 0;
         for (auto& it : m) { pl.tiles[ph].push_back(tile); tile += (it.n + MERGE_TILE - 1) / MERGE_TILE; }
@@ -267,12 +281,17 @@ int64_t enqueue(ptwm_b200_plan& pl, DevicePlan& d, const Bases& bases, uint32_t 
     CUDA_TRY(cudaMemsetAsync(d.status, 0, (pl.item_tensor.size() + 1) * sizeof(uint32_t), st));
     uint32_t* status = d.status + 1;
     size_t item_base = 0, merge_base = 0, tile_base = 0;
+    const bool timing = flags & PTWM_B200_TIME_KERNELS;
+    for (bool& t : d.timed) t = false;
+    if (timing) for (auto& e : d.ev) if (!e) CUDA_TRY(cudaEventCreate(&e));
+    auto mark = [&](int slot, int end) -> cudaError_t { if (!timing) return cudaSuccess; d.timed[slot] = true; return cudaEventRecord(d.ev[2 * slot + end], st); };
     auto launch_decodes = [&](int ph) -> int64_t {
         for (int cc = 0; cc < 4; ++cc) {
             uint32_t n = uint32_t(pl.dec[ph][cc].size());
             const DecodeItem* it = d.items + item_base;
             item_base += n;
             if (!n) continue;
+            CUDA_TRY(mark(ph * 5 + cc, 0));
             switch (cc) {
                 case 0: rans_decode_kernel<<<(n + RANS_WARP_CHUNKS - 1) / RANS_WARP_CHUNKS, 32, RANS_SMEM, st>>>(it, n, bases, status); break;
                 case 1: huffman_decode_kernel<<<(n + HUF_WARP_CHUNKS - 1) / HUF_WARP_CHUNKS, 32, HUF_SMEM, st>>>(it, n, bases, status); break;
@@ -280,6 +299,7 @@ int64_t enqueue(ptwm_b200_plan& pl, DevicePlan& d, const Bases& bases, uint32_t 
                 default: o1sac_decode_kernel<<<n, 32, 0, st>>>(it, n, bases, status); break;
             }
             CUDA_TRY(cudaGetLastError());
+            CUDA_TRY(mark(ph * 5 + cc, 1));
         }
         return 0;
     };
@@ -290,7 +310,12 @@ int64_t enqueue(ptwm_b200_plan& pl, DevicePlan& d, const Bases& bases, uint32_t 
         merge_base += n; tile_base += pl.tiles[ph].size();
         if (!n) return 0;
         uint32_t tiles = pl.tiles[ph].back();
-        if (tiles) { merge_kernel<<<tiles, 256, 0, st>>>(m, tf, n, bases); CUDA_TRY(cudaGetLastError()); }
+        if (tiles) {
+            CUDA_TRY(mark(ph * 5 + 4, 0));
+            merge_kernel<<<tiles, 256, 0, st>>>(m, tf, n, bases);
+            CUDA_TRY(cudaGetLastError());
+            CUDA_TRY(mark(ph * 5 + 4, 1));
+        }
         return 0;
     };
     int64_t rc;
@@ -298,13 +323,17 @@ int64_t enqueue(ptwm_b200_plan& pl, DevicePlan& d, const Bases& bases, uint32_t 
     if ((flags & PTWM_B200_VERIFY_CRC) && !pl.verify.empty()) {
         CUDA_TRY(cudaMemsetAsync(d.acc, 0, (pl.n_acc + 1) * sizeof(uint32_t), st));
         uint64_t blocks = (pl.n_runs + 127) / 128;
+        CUDA_TRY(mark(10, 0));
         crc_planes_kernel<<<uint32_t(blocks), 128, 0, st>>>(d.verify, uint32_t(pl.verify.size()), pl.n_runs, bases, d_tabs, d.acc);
         CUDA_TRY(cudaGetLastError());
+        CUDA_TRY(mark(10, 1));
     }
     if ((flags & PTWM_B200_VERIFY_HASH) && !pl.hashes.empty()) {
         uint32_t n = uint32_t(pl.hashes.size());
+        CUDA_TRY(mark(11, 0));
         xxh64_kernel<<<(n + 7) / 8, 32, 0, st>>>(d.hashes, n, bases, d.hash_out);
         CUDA_TRY(cudaGetLastError());
+        CUDA_TRY(mark(11, 1));
     }
     return 0;
 }
@@ -599,6 +628,22 @@ int64_t ptwm_b200_plan_finish(ptwm_b200_plan* p, uint32_t flags, uint32_t device
     auto it = p->dev.find(int(device_ordinal));
     if (it == p->dev.end()) return fail(PTWM_RC_INVALID_INPUT, "plan has not run on this device");
     return evaluate(*p, it->second, flags, st);
+}
+
+int64_t ptwm_b200_plan_timings(ptwm_b200_plan* p, uint32_t device_ordinal, float* ms, uint64_t* bytes, uint32_t* items) {
+    if (!p) return fail(PTWM_RC_INVALID_INPUT, "null plan");
+    DeviceGuard guard{int(device_ordinal)};
+    std::lock_guard<std::mutex> lock(p->mu);
+    auto it = p->dev.find(int(device_ordinal));
+    if (it == p->dev.end()) return fail(PTWM_RC_INVALID_INPUT, "plan has not run on this device");
+    for (int s = 0; s < 12; ++s) {
+        float t = -1.0f;
+        if (it->second.timed[s]) CUDA_TRY(cudaEventElapsedTime(&t, it->second.ev[2 * s], it->second.ev[2 * s + 1]));
+        if (ms) ms[s] = t;
+        if (bytes) bytes[s] = p->slot_bytes[s];
+        if (items) items[s] = p->slot_items[s];
+    }
+    return 12;
 }
 
 uint32_t ptwm_b200_crc32_by_runs(const uint8_t* data, size_t len, size_t run) {
