@@ -133,7 +133,8 @@ void ptwm_b200_plan_stats(const ptwm_b200_plan* p, uint64_t* bytes_read, uint64_
 /* Decode the planned tensors.  blob_dev_ptr addresses file offset 0 of the
  * container on the device (see ptwm_b200_plan_blob_span), of which bytes
  * [blob_first, blob_first + blob_len) are resident.  stream: a cudaStream_t as
- * integer, 0 = the library's stream for the device.  Without
+ * integer, 0 = the library's stream for the device (pass cudaStreamLegacy, 1,
+ * for the legacy default stream).  Without
  * PTWM_B200_NO_SYNC the call returns after completion with all checks done
  * (ContainerReader::decode_model semantics, container.rs:1766-1780). */
 int64_t ptwm_b200_plan_run(ptwm_b200_plan* p, uint64_t blob_dev_ptr, uint64_t blob_first, uint64_t blob_len, uint64_t out_dev_ptr, uint64_t out_cap,

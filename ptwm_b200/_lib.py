@@ -11,7 +11,7 @@ import os
 import subprocess
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libptwm_b200.so")
+LIB_PATH = os.environ.get("PTWM_B200_LIB") or os.path.join(_HERE, "libptwm_b200.so")  # PTWM_B200_LIB: load another build of the same library
 _SOURCES = [os.path.join(_HERE, "csrc", f) for f in ("unity.cu", "ptwm_b200.cu", "encoder.cu", "kernels.cuh", "encode.cuh", "encode_tables.cuh",
                                                       "format.hpp", "host_common.hpp", "plan.h")] + [
     os.path.join(_HERE, "..", "include", "ptwm_b200.h")]

@@ -15,7 +15,7 @@ from typing import Mapping, Optional, Sequence
 import torch
 
 from . import _lib
-from .container import PtwmError, _check
+from .container import PtwmError, _check, stream_handle
 
 IDENTITY, HUFFMAN, RANS = 0, 1, 3
 _MENU_BIT = {IDENTITY: 1, HUFFMAN: 2, RANS: 4}
@@ -64,7 +64,7 @@ class EncodedContainer:
         """The container bytes as a CUDA uint8 tensor (a copy owned by torch)."""
         t = torch.empty(self.size, dtype=torch.uint8, device=torch.device("cuda", self.device))
         if self.size:
-            _check(_lib.lib().ptwm_b200_encoded_copy_to_device(self._e, t.data_ptr(), t.numel(), torch.cuda.current_stream(self.device).cuda_stream))
+            _check(_lib.lib().ptwm_b200_encoded_copy_to_device(self._e, t.data_ptr(), t.numel(), stream_handle(self.device)))
         return t
 
 
@@ -119,5 +119,5 @@ def compress_model(tensors: Mapping[str, torch.Tensor], config: Optional[Compres
                              int(cfg.emit_payload_hash))
     torch.cuda.current_stream(dev).synchronize()
     h = C.c_void_p()
-    _check(_lib.lib().ptwm_b200_encode_model(arr, len(names), C.byref(opt), dev, torch.cuda.current_stream(dev).cuda_stream, C.byref(h)))
+    _check(_lib.lib().ptwm_b200_encode_model(arr, len(names), C.byref(opt), dev, stream_handle(dev), C.byref(h)))
     return EncodedContainer(h, names, n_planes, dev)

@@ -57,6 +57,14 @@ def _as_u8_tensor(data) -> torch.Tensor:
     return torch.frombuffer(mv, dtype=torch.uint8)
 
 
+def stream_handle(device: int) -> int:
+    """cudaStream_t of torch's current stream as an integer the C ABI takes.
+    The legacy default stream has handle 0, which the ABI reserves for "the
+    library's own stream", so it is passed as cudaStreamLegacy (1)."""
+    s = torch.cuda.current_stream(device).cuda_stream
+    return s if s else 1
+
+
 class DecodePlan:
     """Launch plan for a subset of tensors of one container (ptwm_b200_plan)."""
 
@@ -93,7 +101,7 @@ class DecodePlan:
         ``blob_dev`` holds file bytes [blob_first, blob_first + len)."""
         dev = out.device.index if out.device.index is not None else torch.cuda.current_device()
         if stream is None:
-            stream = torch.cuda.current_stream(dev).cuda_stream
+            stream = stream_handle(dev)
         sp = scratch.data_ptr() if scratch is not None and scratch.numel() else 0
         sc = scratch.numel() if scratch is not None else 0
         _check(_lib.lib().ptwm_b200_plan_run(self._p, (blob_dev.data_ptr() - blob_first) if blob_dev.numel() else 0, blob_first, blob_dev.numel(),
@@ -101,7 +109,7 @@ class DecodePlan:
 
     def finish(self, device: int, flags: int = 0, stream: Optional[int] = None) -> None:
         if stream is None:
-            stream = torch.cuda.current_stream(device).cuda_stream
+            stream = stream_handle(device)
         _check(_lib.lib().ptwm_b200_plan_finish(self._p, flags, device, stream))
 
     def timings(self, device: int) -> dict:

@@ -143,24 +143,74 @@ __device__ __forceinline__ Epilogue make_epilogue(const Bases& bases, const Deco
     for (int j = 0; j < 3; ++j) e.partner[j] = (j < np - 1) ? rd(bases, it.partner[j]) : nullptr;
     return e;
 }
-// `pos` is the symbol index inside the chunk, `syms` holds `count` symbols.
-__device__ __forceinline__ void emit(const Epilogue& e, uint64_t pos, uint32_t count, uint64_t syms) {
-    uint64_t b[4] = {0, 0, 0, 0};
-    if (!e.fused) {
-        b[0] = syms;
-        compose_store(K_PASS, e.dst, pos, count, b);
-        return;
-    }
+// Bytes of the other planes for `count` elements at `pos` (fused lanes only).
+// Issued before the group's symbols are decoded so the loads overlap the decode.
+__device__ __forceinline__ void gather_partners(const Epilogue& e, uint64_t pos, uint32_t count, uint64_t b[4]) {
+    b[0] = b[1] = b[2] = b[3] = 0;
+    if (!e.fused) return;
     int np = kind_planes(e.kind);
     int j = 0;
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
         if (p >= np) break;
-        if (p == e.slot) b[p] = syms;
-        else { const uint8_t* q = e.partner[j++] + pos; b[p] = count == 8 ? ld8_unaligned(q) : ld_bytes(q, count); }
+        if (p == e.slot) continue;
+        const uint8_t* q = e.partner[j++] + pos;
+        b[p] = count == 8 ? ld8_unaligned(q) : ld_bytes(q, count);
     }
+}
+// `pos` is the symbol index inside the chunk, `syms` holds `count` symbols,
+// b[] the partner bytes from gather_partners.
+__device__ __forceinline__ void emit_with(const Epilogue& e, uint64_t pos, uint32_t count, uint64_t syms, uint64_t b[4]) {
+    if (!e.fused) { b[0] = syms; compose_store(K_PASS, e.dst, pos, count, b); return; }
+#pragma unroll
+    for (int p = 0; p < 4; ++p) if (p == e.slot) b[p] = syms;
     compose_store(e.kind, e.dst, pos, count, b);
 }
+__device__ __forceinline__ void emit(const Epilogue& e, uint64_t pos, uint32_t count, uint64_t syms) {
+    uint64_t b[4];
+    gather_partners(e, pos, count, b);
+    emit_with(e, pos, count, syms, b);
+}
+// The other planes' bytes of a fused lane, read as a stream of aligned 8-byte
+// words one group ahead of their use: a group of eight elements needs the
+// words w0 and w1, the word after them is requested while the group's symbols
+// are still being decoded, so its DRAM latency hides behind the decode.
+struct PartnerStream {
+    const uint64_t* q[3];    // word that holds the first byte of the current group
+    const uint64_t* lim[3];  // first word that must not be read
+    uint64_t w0[3], w1[3], w2[3];
+    uint32_t sh[3];
+    int n;                   // partners (planes - 1), 0 for a plain lane
+    __device__ __forceinline__ void start(const Epilogue& e, uint64_t pos, uint32_t chunk_n) {
+        n = e.fused ? kind_planes(e.kind) - 1 : 0;
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            if (j >= n) break;
+            uintptr_t a = reinterpret_cast<uintptr_t>(e.partner[j]) + pos;
+            q[j] = reinterpret_cast<const uint64_t*>(a & ~uintptr_t(7));
+            sh[j] = uint32_t(a & 7) * 8;
+            lim[j] = reinterpret_cast<const uint64_t*>((reinterpret_cast<uintptr_t>(e.partner[j]) + chunk_n + 7) & ~uintptr_t(7));
+            w0[j] = q[j] < lim[j] ? __ldg(q[j]) : 0;
+            w1[j] = q[j] + 1 < lim[j] ? __ldg(q[j] + 1) : 0;
+        }
+    }
+    __device__ __forceinline__ void prefetch() {
+#pragma unroll
+        for (int j = 0; j < 3; ++j) { if (j >= n) break; w2[j] = q[j] + 2 < lim[j] ? __ldg(q[j] + 2) : 0; }
+    }
+    // plane bytes of the current group into b[] (slot = the plane the lane itself decodes), then step to the next group
+    __device__ __forceinline__ void take(int slot, uint64_t b[4]) {
+        int p = 0;
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            if (j >= n) break;
+            if (p == slot) ++p;
+            b[p++] = sh[j] ? (w0[j] >> sh[j]) | (w1[j] << (64 - sh[j])) : w0[j];
+            w0[j] = w1[j]; w1[j] = w2[j]; q[j] += 1;
+        }
+    }
+};
+
 // Length of the first group so that later groups start on an 8-element
 // boundary of the destination.
 __device__ __forceinline__ uint32_t first_group(const Epilogue& e, uint64_t pos, uint32_t remaining) {
@@ -287,36 +337,45 @@ __global__ void __launch_bounds__(32) rans_decode_kernel(const DecodeItem* __res
             Epilogue ep = make_epilogue(bases, it);
             const uint8_t* st = src + my_off;
             uint32_t x = ld_u32_unaligned(st);
-            uintptr_t rp = reinterpret_cast<uintptr_t>(st) + 4;
-            const uintptr_t end = reinterpret_cast<uintptr_t>(st) + my_len;
+            // ring cursor as a 32-bit offset from the 16-byte aligned block that holds the first renorm byte
+            const uintptr_t g0 = (reinterpret_cast<uintptr_t>(st) + 4) & ~uintptr_t(15);
+            uint32_t rq = uint32_t(reinterpret_cast<uintptr_t>(st) + 4 - g0);
+            const uint32_t end_q = uint32_t(reinterpret_cast<uintptr_t>(st) + my_len - g0);
             const uintptr_t lo16 = (reinterpret_cast<uintptr_t>(bases.blob) + bases.blob_first) & ~uintptr_t(15);
             const uintptr_t hi16 = (reinterpret_cast<uintptr_t>(bases.blob) + bases.blob_end + 15) & ~uintptr_t(15);
-            uintptr_t fetched = rp & ~uintptr_t(15);
-            ring.put(fetched, fetch16(fetched, lo16, hi16)); fetched += 16;
-            ring.put(fetched, fetch16(fetched, lo16, hi16)); fetched += 16;
-            ring.put(fetched, fetch16(fetched, lo16, hi16)); fetched += 16;
-            uint4 pending = fetch16(fetched, lo16, hi16);
+            const uint8_t* rb = reinterpret_cast<const uint8_t*>(ring.base);
+#define RING_BYTE(q) rb[(((q) & 60u) << 5) | ((q) & 3u)]
+            uint32_t fq = 0;
+            ring.put(fq, fetch16(g0 + fq, lo16, hi16)); fq += 16;
+            ring.put(fq, fetch16(g0 + fq, lo16, hi16)); fq += 16;
+            ring.put(fq, fetch16(g0 + fq, lo16, hi16)); fq += 16;
+            uint4 pending = fetch16(g0 + fq, lo16, hi16);
 
             uint64_t pos = seg_start;
             uint32_t remaining = seg_len;
             uint32_t g = first_group(ep, pos, remaining);
+            PartnerStream ps;
+            bool streaming = false;
             while (remaining) {
-                if (fetched - rp < 32) { ring.put(fetched, pending); fetched += 16; pending = fetch16(fetched, lo16, hi16); }
-                uint64_t syms = 0;
+                if (fq - rq < 32) { ring.put(fq, pending); fq += 16; pending = fetch16(g0 + fq, lo16, hi16); }
+                uint64_t pb[4] = {0, 0, 0, 0};
+                if (streaming) ps.prefetch();
+                uint32_t s_lo = 0, s_hi = 0;
                 if (g == 8) {
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
+                        uint32_t nb = RING_BYTE(rq);  // next renorm byte, read before it is known to be needed
                         uint32_t idx = x & 2047u;
                         uint32_t sym = tab[idx];
                         uint32_t p = pk[sym];
                         x = (p >> 16) * (x >> 11) + idx - (p & 0xFFFFu);
-                        syms |= uint64_t(sym) << (8 * j);
+                        if (j < 4) s_lo |= sym << (8 * j); else s_hi |= sym << (8 * (j - 4));
+                        bool need = x < RANS_L;
+                        x = need ? (x << 8) | nb : x;
+                        rq += need ? 1u : 0u;
                         if (x < RANS_L) {
-                            x = (x << 8) | ring.byte(rp); ++rp;
-                            if (x < RANS_L) {
-                                x = (x << 8) | ring.byte(rp); ++rp;
-                                if (x < RANS_L) { x = (x << 8) | ring.byte(rp); ++rp; }
-                            }
+                            x = (x << 8) | RING_BYTE(rq); ++rq;
+                            if (x < RANS_L) { x = (x << 8) | RING_BYTE(rq); ++rq; }
                         }
                     }
                 } else {
@@ -325,15 +384,19 @@ __global__ void __launch_bounds__(32) rans_decode_kernel(const DecodeItem* __res
                         uint32_t sym = tab[idx];
                         uint32_t p = pk[sym];
                         x = (p >> 16) * (x >> 11) + idx - (p & 0xFFFFu);
-                        syms |= uint64_t(sym) << (8 * j);
-                        for (int r = 0; r < 3 && x < RANS_L; ++r) { x = (x << 8) | ring.byte(rp); ++rp; }
+                        if (j < 4) s_lo |= sym << (8 * j); else s_hi |= sym << (8 * (j - 4));
+                        for (int r = 0; r < 3 && x < RANS_L; ++r) { x = (x << 8) | RING_BYTE(rq); ++rq; }
                     }
                 }
-                emit(ep, pos, g, syms);
+                if (streaming) ps.take(ep.slot, pb);
+                else gather_partners(ep, pos, g, pb);  // the first group may be short and start anywhere
+                emit_with(ep, pos, g, uint64_t(s_lo) | uint64_t(s_hi) << 32, pb);
                 pos += g; remaining -= g;
                 g = remaining < 8 ? remaining : 8;
+                if (!streaming && remaining) { ps.start(ep, pos, it.n); streaming = true; }
             }
-            if (rp > end) err = ST_STREAM_UNDERRUN;  // decompress.rs:99-104
+#undef RING_BYTE
+            if (rq > end_q) err = ST_STREAM_UNDERRUN;  // decompress.rs:99-104
         }
     }
     if (err) atomicMax(&status[it.id], err);
@@ -461,6 +524,8 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
         uint64_t pos = seg_start;
         uint32_t remaining = seg_len;
         uint32_t g = remaining ? first_group(ep, pos, remaining) : 0;
+        PartnerStream ps;
+        bool streaming = false;
         auto refill = [&]() {
             // one aligned word (or the last partial one) when at most 32 bits are left
             if (cnt <= 32 && rp > start) {
@@ -474,18 +539,35 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
         };
         while (remaining) {
             if (rp - fetched < 32 && fetched > start) { fetched -= 16; ring.put(fetched, pending); pending = fetch16(fetched - 16, lo16, hi16); }
+            uint64_t pb[4] = {0, 0, 0, 0};
+            if (streaming) ps.prefetch();
             uint64_t syms = 0;
-            for (uint32_t j = 0; j < g; ++j) {
-                refill();
-                uint32_t e = table[uint32_t(cont) & mask];
-                uint32_t nb = e >> 8;
-                if (nb > cnt) { err = ST_STREAM_UNDERRUN; nb = cnt; }  // decompress.rs:176-196
-                cont >>= nb; cnt -= nb;
-                syms |= uint64_t(e & 0xFF) << (8 * j);
+            if (g == 8) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if ((j & 1) == 0) refill();  // two symbols need at most 22 bits, a refill leaves more than 32
+                    uint32_t e = table[uint32_t(cont) & mask];
+                    uint32_t nb = e >> 8;
+                    if (nb > cnt) { err = ST_STREAM_UNDERRUN; nb = cnt; }  // decompress.rs:176-196
+                    cont >>= nb; cnt -= nb;
+                    syms |= uint64_t(e & 0xFF) << (8 * j);
+                }
+            } else {
+                for (uint32_t j = 0; j < g; ++j) {
+                    refill();
+                    uint32_t e = table[uint32_t(cont) & mask];
+                    uint32_t nb = e >> 8;
+                    if (nb > cnt) { err = ST_STREAM_UNDERRUN; nb = cnt; }
+                    cont >>= nb; cnt -= nb;
+                    syms |= uint64_t(e & 0xFF) << (8 * j);
+                }
             }
-            emit(ep, pos, g, syms);
+            if (streaming) ps.take(ep.slot, pb);
+            else gather_partners(ep, pos, g, pb);
+            emit_with(ep, pos, g, syms, pb);
             pos += g; remaining -= g;
             g = remaining < 8 ? remaining : 8;
+            if (!streaming && remaining) { ps.start(ep, pos, it.n); streaming = true; }
         }
         // every stream must end with no unread byte and only zero bits left
         // (decompress.rs:140-144, bitstream.rs:184-186)

@@ -48,6 +48,10 @@ int64_t device_state(int dev, DeviceState** out) {
         CUDA_TRY(cudaFuncSetAttribute(rans_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RANS_SMEM));
         CUDA_TRY(cudaFuncSetAttribute(huffman_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, HUF_SMEM));
         CUDA_TRY(cudaFuncSetAttribute(tans_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TANS_SMEM));
+        // the decoders are limited by how many chunk tables fit in an SM: ask for the largest shared-memory carve-out
+        CUDA_TRY(cudaFuncSetAttribute(rans_decode_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        CUDA_TRY(cudaFuncSetAttribute(huffman_decode_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        CUDA_TRY(cudaFuncSetAttribute(tans_decode_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         s.attrs = true;
     }
     *out = &s;
