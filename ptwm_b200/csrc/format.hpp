@@ -92,6 +92,7 @@ struct ChunkDesc {
     // filled by classify_chunk:
     bool raw;             // bytes stored verbatim at data_off
     uint64_t data_off, data_len;  // raw bytes, or the codec blob after TAG and length prefix
+    uint8_t max_sym;      // rANS coded chunks: alphabet bound from the first blob byte (sizes the decoder's tables)
 };
 
 struct PlaneDesc {
@@ -293,7 +294,7 @@ inline std::vector<TableEntry> read_table(const uint8_t* base, size_t begin, siz
 // Frame header, tag byte and length prefix of one chunk (compressor.rs:316-321;
 // codecs/{huffman,rans,tans}.rs decode; codecs/length_prefix.rs:29-33).
 inline void classify_chunk(const uint8_t* base, uint16_t codec, ChunkDesc& ch) {
-    ch.raw = false; ch.data_off = ch.body_off; ch.data_len = ch.body_len;
+    ch.raw = false; ch.data_off = ch.body_off; ch.data_len = ch.body_len; ch.max_sym = 255;
     if (codec == C_IDENTITY) {
         ch.raw = true;
         if (ch.body_len != ch.decoded) throw FormatError("identity plane length differs from its decoded length");
@@ -315,6 +316,7 @@ inline void classify_chunk(const uint8_t* base, uint16_t codec, ChunkDesc& ch) {
     if (!ok) throw FormatError("implausible orig_len for the encoded bytes");
     if (orig != ch.decoded) throw FormatError("decoded length differs from the length the chunk declares");
     ch.data_off = ch.body_off + 5; ch.data_len = enc;
+    ch.max_sym = (codec == C_RANS && enc) ? base[ch.data_off] : 255;
 }
 
 }  // namespace detail

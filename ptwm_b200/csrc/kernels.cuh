@@ -248,17 +248,25 @@ __device__ __forceinline__ uint4 fetch16(uintptr_t a, uintptr_t lo16, uintptr_t 
 // ---- rANS ------------------------------------------------------------------
 constexpr uint32_t RANS_L = 1u << 23;
 constexpr int RANS_WARP_CHUNKS = 8;
-// shared bytes per warp: symbol table 2048 B and (freq<<16 | start) per symbol
-constexpr int RANS_SMEM_PER_CHUNK = 2048 + 1024;
 constexpr int RING_SMEM = 16 * 32 * 4;
-constexpr int RANS_SMEM = RANS_WARP_CHUNKS * RANS_SMEM_PER_CHUNK + RING_SMEM;
+// Shared memory per chunk: a rank table for slot pairs (which present symbol
+// covers slot 2k+1: 1024 bytes) and one word per present symbol
+// (symbol | freq << 8 | start << 20), `l_entries` words (alphabet bound + 2).
+// A slot pair can straddle at most one symbol boundary, so the even slot is
+// covered by that symbol or the one before it; both words are read and the
+// right one is kept.  This is 1.6 KiB per chunk for a bf16 exponent plane
+// instead of the 3 KiB of a full slot table, which is what bounds the number
+// of streams an SM holds.
+__host__ __device__ inline uint32_t rans_l_entries(uint32_t max_sym) { return (max_sym + 3 + 3) & ~3u; }
+__host__ __device__ inline uint32_t rans_smem_bytes(uint32_t l_entries) { return RANS_WARP_CHUNKS * (1024 + 4 * l_entries) + RING_SMEM; }
 
-__global__ void __launch_bounds__(32) rans_decode_kernel(const DecodeItem* __restrict__ items, uint32_t n_items, Bases bases, uint32_t* __restrict__ status) {
+__global__ void __launch_bounds__(32) rans_decode_kernel(const DecodeItem* __restrict__ items, uint32_t n_items, Bases bases, uint32_t* __restrict__ status,
+                                                         uint32_t l_entries) {
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t lane = threadIdx.x, c = lane >> 2, s = lane & 3;
-    uint8_t* symtab = smem;                                                              // [8][2048]
-    uint32_t* packed = reinterpret_cast<uint32_t*>(smem + RANS_WARP_CHUNKS * 2048);      // [8][256]
-    Ring ring{reinterpret_cast<uint32_t*>(smem + RANS_WARP_CHUNKS * RANS_SMEM_PER_CHUNK) + lane};
+    uint8_t* ranktab = smem;                                                             // [8][1024]
+    uint32_t* symlist = reinterpret_cast<uint32_t*>(smem + RANS_WARP_CHUNKS * 1024);     // [8][l_entries], entry 0 is a pad
+    Ring ring{reinterpret_cast<uint32_t*>(smem + RANS_WARP_CHUNKS * (1024 + 4 * l_entries)) + lane};
 
     const uint32_t item_idx = blockIdx.x * RANS_WARP_CHUNKS + c;
     const bool valid = item_idx < n_items;
@@ -267,14 +275,14 @@ __global__ void __launch_bounds__(32) rans_decode_kernel(const DecodeItem* __res
     const uint8_t* src = valid ? rd(bases, it.src) : nullptr;
     uint32_t err = ST_OK;
 
-    // header: [max_sym][freq u16 × (max_sym+1)][4 × u32 stream lengths]
+    // header: [max_sym][freq u16 x (max_sym+1)][4 x u32 stream lengths]
     uint32_t max_sym = 0, hdr = 0, my_off = 0, my_len = 0;
     if (valid) {
         if (it.src_len < 1) err = ST_BAD_HEADER;
         else {
             max_sym = src[0];
             hdr = 1 + 2 * (max_sym + 1);
-            if (it.src_len < hdr + 16) err = ST_BAD_HEADER;
+            if (it.src_len < hdr + 16 || max_sym + 3 > l_entries) err = ST_BAD_HEADER;
             else {
                 uint64_t total = 0;
                 uint32_t off = hdr + 16;
@@ -288,7 +296,7 @@ __global__ void __launch_bounds__(32) rans_decode_kernel(const DecodeItem* __res
         }
     }
 
-    // tables: the whole warp builds one chunk's table at a time
+    // tables: the whole warp builds one chunk's tables at a time
     for (uint32_t c2 = 0; c2 < RANS_WARP_CHUNKS; ++c2) {
         const uint32_t leader = c2 * 4;
         uintptr_t psrc = __shfl_sync(0xFFFFFFFFu, reinterpret_cast<uintptr_t>(src), leader);
@@ -297,32 +305,38 @@ __global__ void __launch_bounds__(32) rans_decode_kernel(const DecodeItem* __res
         uint32_t pvalid = __shfl_sync(0xFFFFFFFFu, uint32_t(valid), leader);
         if (!pvalid || perr) continue;
         const uint8_t* ps = reinterpret_cast<const uint8_t*>(psrc);
-        uint32_t f[8], sum = 0;
+        uint32_t f[8], sum = 0, present = 0;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             uint32_t sym = lane * 8 + k;
             f[k] = sym <= pms ? uint32_t(ps[1 + 2 * sym]) | uint32_t(ps[2 + 2 * sym]) << 8 : 0u;
             sum += f[k];
+            present += f[k] != 0;
         }
-        uint32_t incl = sum;
+        uint32_t incl = sum, rincl = present;
 #pragma unroll
-        for (int d = 1; d < 32; d <<= 1) { uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, d); if (lane >= d) incl += t; }
+        for (int d = 1; d < 32; d <<= 1) {
+            uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, d), r = __shfl_up_sync(0xFFFFFFFFu, rincl, d);
+            if (lane >= d) { incl += t; rincl += r; }
+        }
         uint32_t total = __shfl_sync(0xFFFFFFFFu, incl, 31);
         bool bad = total != 2048;  // decompress.rs:49-55
         if (bad) { if (c == c2) err = ST_BAD_HEADER; continue; }
-        uint32_t start = incl - sum;
-        uint8_t* tab = symtab + c2 * 2048;
-        uint32_t* pk = packed + c2 * 256;
+        uint32_t start = incl - sum, rank = rincl - present;
+        uint8_t* tab = ranktab + c2 * 1024;
+        uint32_t* lst = symlist + c2 * l_entries;
+        if (lane == 0) lst[0] = 0;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             uint32_t sym = lane * 8 + k, fr = f[k];
-            pk[sym] = (fr << 16) | start;
-            uint32_t a = start, e = start + fr;
-            while (a < e && (a & 3)) tab[a++] = uint8_t(sym);
-            uint32_t rep = sym * 0x01010101u;
+            if (!fr) continue;
+            lst[rank + 1] = sym | (fr << 8) | (start << 20);
+            uint32_t a = start >> 1, e = (start + fr) >> 1;  // pairs whose odd slot lies in [start, start + fr)
+            while (a < e && (a & 3)) tab[a++] = uint8_t(rank);
+            uint32_t rep = rank * 0x01010101u;
             while (a + 4 <= e) { *reinterpret_cast<uint32_t*>(tab + a) = rep; a += 4; }
-            while (a < e) tab[a++] = uint8_t(sym);
-            start = e;
+            while (a < e) tab[a++] = uint8_t(rank);
+            start += fr; ++rank;
         }
     }
     __syncwarp();
@@ -332,8 +346,8 @@ __global__ void __launch_bounds__(32) rans_decode_kernel(const DecodeItem* __res
     if (valid && !err && seg_len > 0) {
         if (my_len < 4) err = ST_STREAM_UNDERRUN;  // decompress.rs:82-86
         else {
-            const uint8_t* tab = symtab + c * 2048;
-            const uint32_t* pk = packed + c * 256;
+            const uint8_t* tab = ranktab + c * 1024;
+            const uint32_t* lst = symlist + c * l_entries;
             Epilogue ep = make_epilogue(bases, it);
             const uint8_t* st = src + my_off;
             uint32_t x = ld_u32_unaligned(st);
@@ -366,9 +380,11 @@ __global__ void __launch_bounds__(32) rans_decode_kernel(const DecodeItem* __res
                     for (int j = 0; j < 8; ++j) {
                         uint32_t nb = RING_BYTE(rq);  // next renorm byte, read before it is known to be needed
                         uint32_t idx = x & 2047u;
-                        uint32_t sym = tab[idx];
-                        uint32_t p = pk[sym];
-                        x = (p >> 16) * (x >> 11) + idx - (p & 0xFFFFu);
+                        uint32_t r = tab[idx >> 1];
+                        uint32_t ea = lst[r + 1], eb = lst[r];
+                        uint32_t e = idx < (ea >> 20) ? eb : ea;
+                        uint32_t sym = e & 0xFFu;
+                        x = ((e >> 8) & 0xFFFu) * (x >> 11) + idx - (e >> 20);
                         if (j < 4) s_lo |= sym << (8 * j); else s_hi |= sym << (8 * (j - 4));
                         bool need = x < RANS_L;
                         x = need ? (x << 8) | nb : x;
@@ -381,9 +397,11 @@ __global__ void __launch_bounds__(32) rans_decode_kernel(const DecodeItem* __res
                 } else {
                     for (uint32_t j = 0; j < g; ++j) {
                         uint32_t idx = x & 2047u;
-                        uint32_t sym = tab[idx];
-                        uint32_t p = pk[sym];
-                        x = (p >> 16) * (x >> 11) + idx - (p & 0xFFFFu);
+                        uint32_t r = tab[idx >> 1];
+                        uint32_t ea = lst[r + 1], eb = lst[r];
+                        uint32_t e = idx < (ea >> 20) ? eb : ea;
+                        uint32_t sym = e & 0xFFu;
+                        x = ((e >> 8) & 0xFFFu) * (x >> 11) + idx - (e >> 20);
                         if (j < 4) s_lo |= sym << (8 * j); else s_hi |= sym << (8 * (j - 4));
                         for (int r = 0; r < 3 && x < RANS_L; ++r) { x = (x << 8) | RING_BYTE(rq); ++rq; }
                     }

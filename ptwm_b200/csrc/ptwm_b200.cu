@@ -45,7 +45,7 @@ int64_t device_state(int dev, DeviceState** out) {
         CUDA_TRY(cudaMemcpy(s.d_tabs, &crc_tables(), sizeof(CrcTables), cudaMemcpyHostToDevice));
     }
     if (!s.attrs) {
-        CUDA_TRY(cudaFuncSetAttribute(rans_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RANS_SMEM));
+        CUDA_TRY(cudaFuncSetAttribute(rans_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(rans_smem_bytes(rans_l_entries(255)))));
         CUDA_TRY(cudaFuncSetAttribute(huffman_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, HUF_SMEM));
         CUDA_TRY(cudaFuncSetAttribute(tans_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TANS_SMEM));
         // the decoders are limited by how many chunk tables fit in an SM: ask for the largest shared-memory carve-out
@@ -111,6 +111,7 @@ struct ptwm_b200_plan {
     std::vector<uint32_t> item_tensor;  // item id -> tensor index (for error messages)
     uint32_t launches = 0;
     // per launch slot: 0-3 phase-0 decoders (rANS, Huffman, tANS, O1SAC), 4 scratch copies, 5-8 phase-1 decoders, 9 final merge, 10 CRC, 11 XXH64
+    uint32_t rans_max_sym[2] = {0, 0};  // per phase: largest alphabet bound among the rANS chunks (sizes the kernel's shared memory)
     uint64_t slot_bytes[12] = {0};
     uint32_t slot_items[12] = {0};
     std::mutex mu;
@@ -147,6 +148,7 @@ void plan_tensor(ptwm_b200_plan& pl, uint32_t ti, const TensorDesc& t, uint64_t 
         it.src = make_ref(SP_BLOB, ch.data_off); it.src_len = uint32_t(ch.data_len); it.n = ch.decoded; it.id = new_id();
         it.partner[0] = it.partner[1] = it.partner[2] = REF_NONE; it.state = REF_NONE; it.work = REF_NONE;
         span(ch.data_off, ch.data_len);
+        it.row_len = ch.max_sym;  // rANS: alphabet bound (row_len is only read by Order1ScaleAC)
         if (p.codec == C_O1SAC) {
             it.state = make_ref(SP_BLOB, ch.state_off); it.state_len = uint32_t(ch.state_len); it.state_version = ch.state_version;
             it.row_len = uint32_t(p.row_len);
@@ -236,6 +238,7 @@ void finish_lists(ptwm_b200_plan& pl) {
             if (!v.empty()) pl.launches++;
             int slot = ph * 5 + cc;
             pl.slot_items[slot] = uint32_t(v.size());
+            if (cc == 0) for (auto& it : v) pl.rans_max_sym[ph] = std::max(pl.rans_max_sym[ph], it.row_len);
             for (auto& it : v) {
                 uint64_t np = it.fused ? uint64_t(kind_planes(it.kind)) : 1, eb = it.fused ? uint64_t(kind_elem_bytes(it.kind)) : 1;
                 pl.slot_bytes[slot] += uint64_t(it.src_len) + it.state_len + uint64_t(it.n) * (np - 1) + uint64_t(it.n) * eb;
@@ -297,7 +300,11 @@ int64_t enqueue(ptwm_b200_plan& pl, DevicePlan& d, const Bases& bases, uint32_t 
             if (!n) continue;
             CUDA_TRY(mark(ph * 5 + cc, 0));
             switch (cc) {
-                case 0: rans_decode_kernel<<<(n + RANS_WARP_CHUNKS - 1) / RANS_WARP_CHUNKS, 32, RANS_SMEM, st>>>(it, n, bases, status); break;
+                case 0: {
+                    uint32_t le = rans_l_entries(pl.rans_max_sym[ph]);
+                    rans_decode_kernel<<<(n + RANS_WARP_CHUNKS - 1) / RANS_WARP_CHUNKS, 32, rans_smem_bytes(le), st>>>(it, n, bases, status, le);
+                    break;
+                }
                 case 1: huffman_decode_kernel<<<(n + HUF_WARP_CHUNKS - 1) / HUF_WARP_CHUNKS, 32, HUF_SMEM, st>>>(it, n, bases, status); break;
                 case 2: tans_decode_kernel<<<(n + TANS_WARP_CHUNKS - 1) / TANS_WARP_CHUNKS, 32, TANS_SMEM, st>>>(it, n, bases, status); break;
                 default: o1sac_decode_kernel<<<n, 32, 0, st>>>(it, n, bases, status); break;
@@ -405,8 +412,8 @@ int64_t decode_plane_cuda(uint8_t sfv, const uint8_t* state, size_t state_len, c
     if (rc < 0) return rc;
     cudaStream_t st = ds->stream;
     // the tag and length prefix decide what runs: read them back (5 bytes)
-    uint8_t head[5] = {0, 0, 0, 0, 0};
-    if (in_len) CUDA_TRY(cudaMemcpy(head, reinterpret_cast<const void*>(in_dev), std::min<size_t>(in_len, 5), cudaMemcpyDeviceToHost));
+    uint8_t head[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (in_len) CUDA_TRY(cudaMemcpy(head, reinterpret_cast<const void*>(in_dev), std::min<size_t>(in_len, 8), cudaMemcpyDeviceToHost));
     ChunkDesc ch{};
     ch.body_off = 0; ch.body_len = in_len;
     uint64_t decoded;
@@ -421,7 +428,7 @@ int64_t decode_plane_cuda(uint8_t sfv, const uint8_t* state, size_t state_len, c
         }
         if (decoded > out_cap) return fail(PTWM_RC_BUFFER_TOO_SMALL, "output buffer smaller than the decoded plane");
         ch.decoded = uint32_t(decoded);
-        detail::classify_chunk(head, uint16_t(codec), ch);  // only reads head[0..5)
+        detail::classify_chunk(head, uint16_t(codec), ch);  // only reads head[0..6)
         if (codec == C_O1SAC) check_o1sac(state, state_len, sfv, in_len, decoded, 0);
     } catch (const FormatError& e) { return fail(PTWM_RC_INVALID_INPUT, e.what()); }
     if (!decoded) return 0;
@@ -451,7 +458,7 @@ int64_t decode_plane_cuda(uint8_t sfv, const uint8_t* state, size_t state_len, c
     const DecodeItem* d_it = reinterpret_cast<const DecodeItem*>(scratch + 64);
     uint32_t* d_status = reinterpret_cast<uint32_t*>(scratch);
     switch (codec) {
-        case C_RANS: rans_decode_kernel<<<1, 32, RANS_SMEM, st>>>(d_it, 1, bases, d_status); break;
+        case C_RANS: rans_decode_kernel<<<1, 32, rans_smem_bytes(rans_l_entries(255)), st>>>(d_it, 1, bases, d_status, rans_l_entries(255)); break;
         case C_HUFFMAN: huffman_decode_kernel<<<1, 32, HUF_SMEM, st>>>(d_it, 1, bases, d_status); break;
         case C_TANS: tans_decode_kernel<<<1, 32, TANS_SMEM, st>>>(d_it, 1, bases, d_status); break;
         default: o1sac_decode_kernel<<<1, 32, 0, st>>>(d_it, 1, bases, d_status); break;
