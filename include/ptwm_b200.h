@@ -188,6 +188,32 @@ int64_t ptwm_b200_encoded_copy_to_device(const ptwm_b200_encoded* e, uint64_t ds
 int32_t ptwm_b200_encoded_plane_codec(const ptwm_b200_encoded* e, size_t tensor, size_t plane);
 void ptwm_b200_encoded_free(ptwm_b200_encoded* e);
 
+/* ---- 4. decode without allocating ----------------------------------------- */
+
+/* No counterpart in the reference.  Same work and same arguments as
+ * ptwm_hardware_backend_v1_dispatch_decode_cuda (one plane payload, device to
+ * device, returns the decoded byte count), for callers that may not allocate
+ * device memory: a loader that runs after the serving engine has handed all of
+ * HBM to its own pool, or inside a sandbox that accounts for every allocation,
+ * cannot afford the cudaMalloc the regular entry point does for its per-call
+ * scratch.  Here that scratch is a fixed 64 KiB array inside the library's
+ * device image (every GPU that loads the library holds it until the process
+ * exits), and the call makes no cudaMalloc / cudaFree and creates no stream:
+ * `stream` must be given (1 = the legacy default stream).
+ *
+ * - Limit: identity / huffman / rans / tans payloads of any size fit; an
+ *   Order1ScaleAC state fits up to 62 context rows, a larger one is refused with
+ *   PTWM_RC_BUFFER_TOO_SMALL and a message naming the limit.
+ * - The first call on a device looks the array's address up
+ *   (cudaGetSymbolAddress) and raises the kernels' shared-memory limit; make that
+ *   first call before any stream capture begins.
+ * - All calls share the one array.  Its status word is cleared at the start of
+ *   each call; two calls that overlap on the same GPU (different streams or
+ *   threads) race on it and must be serialised by the caller. */
+int64_t ptwm_b200_decode_plane_noalloc(uint8_t state_format_version, const uint8_t* state_ptr, size_t state_len, const uint8_t* codec_id_ptr,
+                                       size_t codec_id_len, uint64_t in_dev_ptr, size_t in_len, uint64_t out_dev_ptr, size_t out_cap,
+                                       uint32_t device_ordinal, uint64_t stream);
+
 /* Per-launch figures of the last finished run made with PTWM_B200_TIME_KERNELS.
  * Twelve slots: 0-3 first-pass decoders (rANS, Huffman, tANS, Order1ScaleAC),
  * 4 copies to scratch, 5-8 second-pass decoders (fused with the merge where a

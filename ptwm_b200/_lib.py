@@ -12,7 +12,7 @@ import subprocess
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("PTWM_B200_LIB") or os.path.join(_HERE, "libptwm_b200.so")  # PTWM_B200_LIB: load another build of the same library
-_SOURCES = [os.path.join(_HERE, "csrc", f) for f in ("unity.cu", "ptwm_b200.cu", "encoder.cu", "kernels.cuh", "encode.cuh", "encode_tables.cuh",
+_SOURCES = [os.path.join(_HERE, "csrc", f) for f in ("unity.cu", "ptwm_b200.cu", "encoder.cu", "kernels.cuh", "encode.cuh", "encode_tables.cuh", "noalloc.cu",
                                                       "format.hpp", "host_common.hpp", "plan.h")] + [
     os.path.join(_HERE, "..", "include", "ptwm_b200.h")]
 
@@ -77,6 +77,8 @@ _SIGNATURES = {
                                        C.c_uint32, C.c_uint64]),
     "ptwm_b200_plan_finish": (C.c_int64, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint64]),
     "ptwm_b200_plan_timings": (C.c_int64, [C.c_void_p, C.c_uint32, C.POINTER(C.c_float), C.POINTER(C.c_uint64), C.POINTER(C.c_uint32)]),
+    "ptwm_b200_decode_plane_noalloc": (C.c_int64, [C.c_uint8, C.c_void_p, C.c_size_t, C.c_char_p, C.c_size_t, C.c_uint64, C.c_size_t, C.c_uint64,
+                                                   C.c_size_t, C.c_uint32, C.c_uint64]),
     "ptwm_b200_crc32_by_runs": (C.c_uint32, [C.c_char_p, C.c_size_t, C.c_size_t]),
     "ptwm_hardware_backend_v1_cuda_stream_handle": (C.c_uint64, [C.c_uint32]),
     "ptwm_plane_codec_v1_cuda_stream_handle": (C.c_uint64, [C.c_uint32]),

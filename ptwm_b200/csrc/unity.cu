@@ -2,3 +2,4 @@
 // decode and encode hosts are compiled together.
 #include "ptwm_b200.cu"
 #include "encoder.cu"
+#include "noalloc.cu"
