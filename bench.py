@@ -181,7 +181,7 @@ def run_reference(args):
             "config": workload_config(args, raw_bytes=raw, compressed=len(blob)),
             "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line))
+    emit_json(line)
 
 
 def workload_config(args, raw_bytes, compressed):
@@ -335,12 +335,25 @@ def run_ours(args):
             threads = oracle.num_procs()
             sec, dec = time_cpu_decode(blob, expect, threads, repeats=3)
             line["cpu_baseline"] = {"value": dec / sec / 1e9, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample}
-        print(json.dumps(line))
+        emit_json(line)
     if world > 1:
         dist.destroy_process_group()
 
 
+_JSON_OUT = None
+
+
+def emit_json(line: dict) -> None:
+    """The one JSON line goes to the real stdout; everything else that writes to
+    file descriptor 1 (NCCL prints its version banner there) is sent to stderr."""
+    _JSON_OUT.write(json.dumps(line) + "\n")
+    _JSON_OUT.flush()
+
+
 def main():
+    global _JSON_OUT
+    _JSON_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
