@@ -93,6 +93,7 @@ struct ChunkDesc {
     bool raw;             // bytes stored verbatim at data_off
     uint64_t data_off, data_len;  // raw bytes, or the codec blob after TAG and length prefix
     uint8_t max_sym;      // rANS coded chunks: alphabet bound from the first blob byte (sizes the decoder's tables)
+    uint16_t distinct;    // rANS coded chunks: symbols with a non-zero frequency (picks the decoder variant); 256 when unknown
 };
 
 struct PlaneDesc {
@@ -294,7 +295,7 @@ inline std::vector<TableEntry> read_table(const uint8_t* base, size_t begin, siz
 // Frame header, tag byte and length prefix of one chunk (compressor.rs:316-321;
 // codecs/{huffman,rans,tans}.rs decode; codecs/length_prefix.rs:29-33).
 inline void classify_chunk(const uint8_t* base, uint16_t codec, ChunkDesc& ch) {
-    ch.raw = false; ch.data_off = ch.body_off; ch.data_len = ch.body_len; ch.max_sym = 255;
+    ch.raw = false; ch.data_off = ch.body_off; ch.data_len = ch.body_len; ch.max_sym = 255; ch.distinct = 256;
     if (codec == C_IDENTITY) {
         ch.raw = true;
         if (ch.body_len != ch.decoded) throw FormatError("identity plane length differs from its decoded length");
@@ -317,6 +318,13 @@ inline void classify_chunk(const uint8_t* base, uint16_t codec, ChunkDesc& ch) {
     if (orig != ch.decoded) throw FormatError("decoded length differs from the length the chunk declares");
     ch.data_off = ch.body_off + 5; ch.data_len = enc;
     ch.max_sym = (codec == C_RANS && enc) ? base[ch.data_off] : 255;
+    if (codec == C_RANS && enc >= 1 + 2 * (uint64_t(ch.max_sym) + 1)) {
+        // frequency table: u16 per symbol after the alphabet bound (rans/decompress.rs:36-47)
+        const uint8_t* f = base + ch.data_off + 1;
+        uint32_t d = 0;
+        for (uint32_t k = 0; k <= ch.max_sym; ++k) d += (f[2 * k] | f[2 * k + 1]) != 0;
+        ch.distinct = uint16_t(d);
+    }
 }
 
 }  // namespace detail

@@ -56,6 +56,15 @@ __device__ __forceinline__ uint64_t ld_bytes(const uint8_t* p, uint32_t count) {
 __device__ __forceinline__ uint32_t revert16x2(uint32_t r) {  // split/dtype16.rs:20-25
     return ((r << 8) & 0x80008000u) | ((r >> 1) & 0x7F807F80u) | (r & 0x007F007Fu);
 }
+// Four 16-bit elements from four bytes of the low plane ([S M7]) and four of
+// the high plane (E8): the bit reorder done on the packed planes, then the
+// interleave.  Same result as revert16x2 on the interleaved words.
+__device__ __forceinline__ void compose16x4(uint32_t lo, uint32_t hi, uint32_t& v0, uint32_t& v1) {
+    uint32_t oh = (lo & 0x80808080u) | ((hi >> 1) & 0x7F7F7F7Fu);
+    uint32_t ol = ((hi << 7) & 0x80808080u) | (lo & 0x7F7F7F7Fu);
+    v0 = __byte_perm(ol, oh, 0x5140);
+    v1 = __byte_perm(ol, oh, 0x7362);
+}
 __device__ __forceinline__ uint32_t revert32(uint32_t r) {  // transforms/fusion.rs:287-292
     return ((r << 8) & 0x80000000u) | ((r >> 1) & 0x7F800000u) | (r & 0x007FFFFFu);
 }
@@ -87,10 +96,8 @@ __device__ __forceinline__ void compose_store(int kind, uint8_t* dst, uint64_t p
         case K_M16: {
             uint32_t l0 = uint32_t(b[0]), l1 = uint32_t(b[0] >> 32), h0 = uint32_t(b[1]), h1 = uint32_t(b[1] >> 32);
             uint4 v;
-            v.x = revert16x2(__byte_perm(l0, h0, 0x5140));
-            v.y = revert16x2(__byte_perm(l0, h0, 0x7362));
-            v.z = revert16x2(__byte_perm(l1, h1, 0x5140));
-            v.w = revert16x2(__byte_perm(l1, h1, 0x7362));
+            compose16x4(l0, h0, v.x, v.y);
+            compose16x4(l1, h1, v.z, v.w);
             uint8_t* p = dst + pos * 2;
             if (count == 8 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) *reinterpret_cast<uint4*>(p) = v;
             else {
@@ -249,24 +256,155 @@ __device__ __forceinline__ uint4 fetch16(uintptr_t a, uintptr_t lo16, uintptr_t 
 constexpr uint32_t RANS_L = 1u << 23;
 constexpr int RANS_WARP_CHUNKS = 8;
 constexpr int RING_SMEM = 16 * 32 * 4;
-// Shared memory per chunk: a rank table for slot pairs (which present symbol
-// covers slot 2k+1: 1024 bytes) and one word per present symbol
-// (symbol | freq << 8 | start << 20), `l_entries` words (alphabet bound + 2).
-// A slot pair can straddle at most one symbol boundary, so the even slot is
-// covered by that symbol or the one before it; both words are read and the
-// right one is kept.  This is 1.6 KiB per chunk for a bf16 exponent plane
-// instead of the 3 KiB of a full slot table, which is what bounds the number
-// of streams an SM holds.
+// How many distinct symbols a chunk may hold for the kernel that keeps a copy
+// of the symbol list per lane (two pad entries come on top).
+constexpr uint32_t RANS_NARROW_SYMBOLS = 38;
+// Shared memory per chunk:
+//  * a rank table over the 2048 slots: 128 words of (16-bit boundary bitmap,
+//    boundaries before the word << 16).  Bit i of a bitmap is set when slot
+//    16 w + i is the first slot of a symbol, so the symbol covering a slot is
+//    number count + popc(bits up to the slot) among the present symbols: 512
+//    bytes instead of a byte per slot, and shared memory per chunk is what
+//    bounds the number of streams an SM keeps in flight;
+//  * one word per present symbol (symbol | freq << 8 | start << 20), entry 0 a
+//    pad so that the count above indexes it directly.  Two layouts:
+//    shared by the four lanes of a chunk, `l_entries` words per chunk (alphabet
+//    bound + 2), any alphabet; or one copy per lane (PER_LANE), entry k of lane
+//    l in word k * 32 + l, a bank of its own, so the read is conflict free.
+//    `l_entries` is then the number of rows and bounds the distinct symbols of
+//    a chunk; the host sends only chunks that fit.
+constexpr int RANS_RANK_BYTES = 512;
 __host__ __device__ inline uint32_t rans_l_entries(uint32_t max_sym) { return (max_sym + 3 + 3) & ~3u; }
-__host__ __device__ inline uint32_t rans_smem_bytes(uint32_t l_entries) { return RANS_WARP_CHUNKS * (1024 + 4 * l_entries) + RING_SMEM; }
+__host__ __device__ inline uint32_t rans_smem_bytes(uint32_t l_entries, bool per_lane = false) {
+    return RANS_WARP_CHUNKS * RANS_RANK_BYTES + (per_lane ? 128 * l_entries : RANS_WARP_CHUNKS * 4 * l_entries) + RING_SMEM;
+}
 
-__global__ void __launch_bounds__(32) rans_decode_kernel(const DecodeItem* __restrict__ items, uint32_t n_items, Bases bases, uint32_t* __restrict__ status,
-                                                         uint32_t l_entries) {
+// Ring addressing: byte q of a lane's ring lives in word (q >> 2) & 15 of the
+// [word][lane] array, `rw` points at the lane's column.
+__device__ __forceinline__ uint32_t ring_byte(const uint32_t* rw, uint32_t q) {
+    return reinterpret_cast<const uint8_t*>(rw)[((q & 60u) << 5) | (q & 3u)];
+}
+// The eight ring bytes from q on, big-endian: byte q is the top byte of `wh`.
+__device__ __forceinline__ void ring_window_be(const uint32_t* rw, uint32_t q, uint32_t& wh, uint32_t& wl) {
+    uint32_t k = q >> 2;
+    uint32_t w0 = rw[(k & 15u) << 5], w1 = rw[((k + 1) & 15u) << 5], w2 = rw[((k + 2) & 15u) << 5];
+    uint32_t sel = 0x0123u + 0x1111u * (q & 3u);
+    wh = __byte_perm(w0, w1, sel);
+    wl = __byte_perm(w1, w2, sel);
+}
+// One symbol (decompress.rs:118-139): slot -> number of the covering symbol ->
+// (symbol | freq << 8 | start << 20), state update.  `e` is returned whole; its
+// low byte is the symbol.  LS = distance in words between list entries.
+template <int LS>
+__device__ __forceinline__ uint32_t rans_lookup(const uint32_t* tab, const uint32_t* lst, uint32_t& x) {
+    uint32_t idx = x & 2047u;
+    uint32_t w = tab[idx >> 4];
+    uint32_t k = (w >> 16) + __popc((w << 16) << (~idx & 15u));  // boundaries at or below the slot
+    uint32_t e = lst[k * LS];
+    x = ((e >> 8) & 0xFFFu) * (x >> 11) + (idx - (e >> 20));
+    return e;
+}
+// Up to eight symbols, renormalising a byte at a time straight from the ring.
+template <int LS>
+__device__ __forceinline__ void rans_short_group(const uint32_t* tab, const uint32_t* lst, const uint32_t* rw, uint32_t& x, uint32_t& rq, uint32_t g,
+                                                 uint32_t& s_lo, uint32_t& s_hi) {
+    s_lo = 0; s_hi = 0;
+    for (uint32_t j = 0; j < g; ++j) {
+        uint32_t sym = rans_lookup<LS>(tab, lst, x) & 0xFFu;
+        if (j < 4) s_lo |= sym << (8 * j); else s_hi |= sym << (8 * (j - 4));
+        for (int k = 0; k < 3 && x < RANS_L; ++k) { x = (x << 8) | ring_byte(rw, rq); ++rq; }
+    }
+}
+// Exactly eight symbols, without a branch per symbol.  The next eight stream
+// bytes sit big-endian in two registers behind the state; renormalising by
+// 0..3 bytes (the count follows from the leading zeros of the state) is a
+// funnel shift of state and window.  Eight bytes cover a group unless its
+// symbols average more than one byte each (frequencies below 8 in a row); the
+// total is checked once per group and such a group is decoded again byte-wise.
+template <int LS>
+__device__ __forceinline__ void rans_group8(const uint32_t* tab, const uint32_t* lst, const uint32_t* rw, uint32_t& x, uint32_t& rq, uint32_t& s_lo,
+                                            uint32_t& s_hi) {
+    uint32_t wh, wl, used = 0;
+    const uint32_t x0 = x;
+    ring_window_be(rw, rq, wh, wl);
+    s_lo = 0; s_hi = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        uint32_t e = rans_lookup<LS>(tab, lst, x);
+        const uint32_t ins = (0x3210u & ~(0xFu << (4 * (j & 3)))) | (4u << (4 * (j & 3)));  // low byte of e into byte j & 3
+        if (j < 4) s_lo = __byte_perm(s_lo, e, ins); else s_hi = __byte_perm(s_hi, e, ins);
+        // bytes until x >= 2^23, at most three: 0 for clz <= 8, 1 for 9..16, 2 for 17..24, 3 above
+        uint32_t sh = uint32_t(max(int(__clz(x)) - 1, 0)) & 0x18u;
+        x = __funnelshift_l(wh, x, sh);
+        wh = __funnelshift_l(wl, wh, sh);
+        wl <<= sh;
+        used += sh;
+    }
+    if (used > 64) {
+        x = x0;
+        rans_short_group<LS>(tab, lst, rw, x, rq, 8, s_lo, s_hi);
+    } else {
+        rq += used >> 3;
+    }
+}
+
+// 256-bit global accesses (sm_100): a lane that walks its own stream touches
+// one 32-byte sector per instruction instead of half of one, which halves the
+// load/store-pipe cost of these scattered accesses.
+struct Block32 { uint32_t w[8]; };
+__device__ __forceinline__ Block32 ldg256(const void* p) {
+    Block32 b;
+    asm("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+        : "=r"(b.w[0]), "=r"(b.w[1]), "=r"(b.w[2]), "=r"(b.w[3]), "=r"(b.w[4]), "=r"(b.w[5]), "=r"(b.w[6]), "=r"(b.w[7])
+        : "l"(p));
+    return b;
+}
+__device__ __forceinline__ void stg256(void* p, uint4 a, uint4 b) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+                 : "memory");
+}
+// Aligned 32-byte block at `a`; bytes outside [lo, hi) read as zero and are not touched.
+__device__ __forceinline__ Block32 load_block_guarded(uintptr_t a, uintptr_t lo, uintptr_t hi) {
+    if (a >= lo && a + 32 <= hi) return ldg256(reinterpret_cast<const void*>(a));
+    Block32 b;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        uint32_t v = 0;
+        for (int i = 0; i < 4; ++i) {
+            uintptr_t q = a + 4 * k + i;
+            if (q >= lo && q < hi) v |= uint32_t(__ldg(reinterpret_cast<const uint8_t*>(q))) << (8 * i);
+        }
+        b.w[k] = v;
+    }
+    return b;
+}
+// The 32 bytes that start `off` (0..31) bytes into the 64 bytes (cur, nxt), as eight words.
+__device__ __forceinline__ void extract32(const Block32& cur, const Block32& nxt, uint32_t off, uint32_t out[8]) {
+    uint32_t a[16], b[12], c[10], d[9];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { a[i] = cur.w[i]; a[8 + i] = nxt.w[i]; }
+    const bool j4 = off & 16, j2 = off & 8, j1 = off & 4;
+#pragma unroll
+    for (int i = 0; i < 12; ++i) b[i] = j4 ? a[i + 4] : a[i];
+#pragma unroll
+    for (int i = 0; i < 10; ++i) c[i] = j2 ? b[i + 2] : b[i];
+#pragma unroll
+    for (int i = 0; i < 9; ++i) d[i] = j1 ? c[i + 1] : c[i];
+    const uint32_t sel = 0x3210u + 0x1111u * (off & 3u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = __byte_perm(d[i], d[i + 1], sel);
+}
+
+template <bool PER_LANE>
+__global__ void __launch_bounds__(32, 24) rans_decode_kernel_t(const DecodeItem* __restrict__ items, uint32_t n_items, Bases bases, uint32_t* __restrict__ status,
+                                                           uint32_t l_entries) {
+    constexpr int LS = PER_LANE ? 32 : 1;
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t lane = threadIdx.x, c = lane >> 2, s = lane & 3;
-    uint8_t* ranktab = smem;                                                             // [8][1024]
-    uint32_t* symlist = reinterpret_cast<uint32_t*>(smem + RANS_WARP_CHUNKS * 1024);     // [8][l_entries], entry 0 is a pad
-    Ring ring{reinterpret_cast<uint32_t*>(smem + RANS_WARP_CHUNKS * (1024 + 4 * l_entries)) + lane};
+    uint32_t* ranktab = reinterpret_cast<uint32_t*>(smem);                                       // [8][128]
+    uint32_t* symlist = reinterpret_cast<uint32_t*>(smem + RANS_WARP_CHUNKS * RANS_RANK_BYTES);  // entry 0 of every list is a pad
+    const uint32_t list_bytes = PER_LANE ? 128 * l_entries : RANS_WARP_CHUNKS * 4 * l_entries;
+    Ring ring{reinterpret_cast<uint32_t*>(smem + RANS_WARP_CHUNKS * RANS_RANK_BYTES + list_bytes) + lane};
 
     const uint32_t item_idx = blockIdx.x * RANS_WARP_CHUNKS + c;
     const bool valid = item_idx < n_items;
@@ -282,7 +420,7 @@ __global__ void __launch_bounds__(32) rans_decode_kernel(const DecodeItem* __res
         else {
             max_sym = src[0];
             hdr = 1 + 2 * (max_sym + 1);
-            if (it.src_len < hdr + 16 || max_sym + 3 > l_entries) err = ST_BAD_HEADER;
+            if (it.src_len < hdr + 16 || (!PER_LANE && max_sym + 3 > l_entries)) err = ST_BAD_HEADER;
             else {
                 uint64_t total = 0;
                 uint32_t off = hdr + 16;
@@ -319,25 +457,43 @@ __global__ void __launch_bounds__(32) rans_decode_kernel(const DecodeItem* __res
             uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, d), r = __shfl_up_sync(0xFFFFFFFFu, rincl, d);
             if (lane >= d) { incl += t; rincl += r; }
         }
-        uint32_t total = __shfl_sync(0xFFFFFFFFu, incl, 31);
+        uint32_t total = __shfl_sync(0xFFFFFFFFu, incl, 31), distinct = __shfl_sync(0xFFFFFFFFu, rincl, 31);
         bool bad = total != 2048;  // decompress.rs:49-55
+        if (PER_LANE && distinct + 2 > l_entries) bad = true;  // the host only sends chunks that fit; a blob that differs from the planned one may not
         if (bad) { if (c == c2) err = ST_BAD_HEADER; continue; }
         uint32_t start = incl - sum, rank = rincl - present;
-        uint8_t* tab = ranktab + c2 * 1024;
-        uint32_t* lst = symlist + c2 * l_entries;
-        if (lane == 0) lst[0] = 0;
+        uint32_t* tab = ranktab + c2 * 128;
+        uint32_t* lst = PER_LANE ? symlist + c2 * 4 : symlist + c2 * l_entries;
+        if (lane == 0) {
+            if (PER_LANE) *reinterpret_cast<uint4*>(lst) = make_uint4(0, 0, 0, 0); else lst[0] = 0;
+        }
+        *reinterpret_cast<uint4*>(tab + 4 * lane) = make_uint4(0, 0, 0, 0);
+        __syncwarp();
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             uint32_t sym = lane * 8 + k, fr = f[k];
             if (!fr) continue;
-            lst[rank + 1] = sym | (fr << 8) | (start << 20);
-            uint32_t a = start >> 1, e = (start + fr) >> 1;  // pairs whose odd slot lies in [start, start + fr)
-            while (a < e && (a & 3)) tab[a++] = uint8_t(rank);
-            uint32_t rep = rank * 0x01010101u;
-            while (a + 4 <= e) { *reinterpret_cast<uint32_t*>(tab + a) = rep; a += 4; }
-            while (a < e) tab[a++] = uint8_t(rank);
+            uint32_t entry = sym | (fr << 8) | (start << 20);
+            if (PER_LANE) *reinterpret_cast<uint4*>(lst + (rank + 1) * 32) = make_uint4(entry, entry, entry, entry);  // the four lanes of the chunk
+            else lst[rank + 1] = entry;
+            atomicOr(&tab[start >> 4], 1u << (start & 15));
             start += fr; ++rank;
         }
+        __syncwarp();
+        // boundaries before each word: lane l owns words 4l .. 4l+3
+        uint4 bm = *reinterpret_cast<uint4*>(tab + 4 * lane);
+        uint32_t p0 = __popc(bm.x), p1 = __popc(bm.y), p2 = __popc(bm.z), p3 = __popc(bm.w), scan = p0 + p1 + p2 + p3;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            uint32_t t = __shfl_up_sync(0xFFFFFFFFu, scan, d);
+            if (lane >= d) scan += t;
+        }
+        uint32_t before = scan - (p0 + p1 + p2 + p3);
+        bm.x |= before << 16; before += p0;
+        bm.y |= before << 16; before += p1;
+        bm.z |= before << 16; before += p2;
+        bm.w |= before << 16;
+        *reinterpret_cast<uint4*>(tab + 4 * lane) = bm;
     }
     __syncwarp();
 
@@ -346,8 +502,9 @@ __global__ void __launch_bounds__(32) rans_decode_kernel(const DecodeItem* __res
     if (valid && !err && seg_len > 0) {
         if (my_len < 4) err = ST_STREAM_UNDERRUN;  // decompress.rs:82-86
         else {
-            const uint8_t* tab = ranktab + c * 1024;
-            const uint32_t* lst = symlist + c * l_entries;
+            const uint32_t* tab = ranktab + c * 128;
+            const uint32_t* lst = PER_LANE ? symlist + lane : symlist + c * l_entries;
+            const uint32_t* rw = ring.base;
             Epilogue ep = make_epilogue(bases, it);
             const uint8_t* st = src + my_off;
             uint32_t x = ld_u32_unaligned(st);
@@ -357,63 +514,113 @@ __global__ void __launch_bounds__(32) rans_decode_kernel(const DecodeItem* __res
             const uint32_t end_q = uint32_t(reinterpret_cast<uintptr_t>(st) + my_len - g0);
             const uintptr_t lo16 = (reinterpret_cast<uintptr_t>(bases.blob) + bases.blob_first) & ~uintptr_t(15);
             const uintptr_t hi16 = (reinterpret_cast<uintptr_t>(bases.blob) + bases.blob_end + 15) & ~uintptr_t(15);
-            const uint8_t* rb = reinterpret_cast<const uint8_t*>(ring.base);
-#define RING_BYTE(q) rb[(((q) & 60u) << 5) | ((q) & 3u)]
             uint32_t fq = 0;
             ring.put(fq, fetch16(g0 + fq, lo16, hi16)); fq += 16;
             ring.put(fq, fetch16(g0 + fq, lo16, hi16)); fq += 16;
             ring.put(fq, fetch16(g0 + fq, lo16, hi16)); fq += 16;
             uint4 pending = fetch16(g0 + fq, lo16, hi16);
-
-            uint64_t pos = seg_start;
-            uint32_t remaining = seg_len;
-            uint32_t g = first_group(ep, pos, remaining);
-            PartnerStream ps;
-            bool streaming = false;
-            while (remaining) {
-                if (fq - rq < 32) { ring.put(fq, pending); fq += 16; pending = fetch16(g0 + fq, lo16, hi16); }
-                uint64_t pb[4] = {0, 0, 0, 0};
-                if (streaming) ps.prefetch();
-                uint32_t s_lo = 0, s_hi = 0;
-                if (g == 8) {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        uint32_t nb = RING_BYTE(rq);  // next renorm byte, read before it is known to be needed
-                        uint32_t idx = x & 2047u;
-                        uint32_t r = tab[idx >> 1];
-                        uint32_t ea = lst[r + 1], eb = lst[r];
-                        uint32_t e = idx < (ea >> 20) ? eb : ea;
-                        uint32_t sym = e & 0xFFu;
-                        x = ((e >> 8) & 0xFFFu) * (x >> 11) + idx - (e >> 20);
-                        if (j < 4) s_lo |= sym << (8 * j); else s_hi |= sym << (8 * (j - 4));
-                        bool need = x < RANS_L;
-                        x = need ? (x << 8) | nb : x;
-                        rq += need ? 1u : 0u;
-                        if (x < RANS_L) {
-                            x = (x << 8) | RING_BYTE(rq); ++rq;
-                            if (x < RANS_L) { x = (x << 8) | RING_BYTE(rq); ++rq; }
-                        }
-                    }
-                } else {
-                    for (uint32_t j = 0; j < g; ++j) {
-                        uint32_t idx = x & 2047u;
-                        uint32_t r = tab[idx >> 1];
-                        uint32_t ea = lst[r + 1], eb = lst[r];
-                        uint32_t e = idx < (ea >> 20) ? eb : ea;
-                        uint32_t sym = e & 0xFFu;
-                        x = ((e >> 8) & 0xFFFu) * (x >> 11) + idx - (e >> 20);
-                        if (j < 4) s_lo |= sym << (8 * j); else s_hi |= sym << (8 * (j - 4));
-                        for (int r = 0; r < 3 && x < RANS_L; ++r) { x = (x << 8) | RING_BYTE(rq); ++rq; }
-                    }
+            // A group consumes at most 24 bytes; 32 valid bytes at its start always suffice.
+            // The lanes of a warp drain their rings at similar rates: when any active lane runs low,
+            // every lane with room for a block takes one, so the refill code runs once per several groups.
+            auto top_up = [&]() {
+                if (__any_sync(__activemask(), fq - rq < 32)) {
+                    if (fq - rq <= 48) { ring.put(fq, pending); fq += 16; pending = fetch16(g0 + fq, lo16, hi16); }
                 }
-                if (streaming) ps.take(ep.slot, pb);
-                else gather_partners(ep, pos, g, pb);  // the first group may be short and start anywhere
-                emit_with(ep, pos, g, uint64_t(s_lo) | uint64_t(s_hi) << 32, pb);
-                pos += g; remaining -= g;
-                g = remaining < 8 ? remaining : 8;
-                if (!streaming && remaining) { ps.start(ep, pos, it.n); streaming = true; }
+            };
+
+            uint32_t pos = seg_start, remaining = seg_len;
+            // head: a short group up to the next 8-element boundary of the destination
+            {
+                uint32_t g = first_group(ep, pos, remaining);
+                if (g < 8 || remaining < 16) {
+                    uint32_t s_lo, s_hi;
+                    top_up();
+                    rans_short_group<LS>(tab, lst, rw, x, rq, g, s_lo, s_hi);
+                    emit(ep, pos, g, uint64_t(s_lo) | uint64_t(s_hi) << 32);
+                    pos += g; remaining -= g;
+                }
             }
-#undef RING_BYTE
+            const int mode = !ep.fused ? 0 : ep.kind == K_M16 ? 1 + ep.slot : 3;
+            if (mode == 0) {
+                // plain lane: eight symbols are eight bytes of the plane
+                uint8_t* out = ep.dst + pos;
+                uint32_t nfast = (reinterpret_cast<uintptr_t>(out) & 7) == 0 ? remaining >> 3 : 0;
+                for (uint32_t i = 0; i < nfast; ++i) {
+                    uint32_t s_lo, s_hi;
+                    top_up();
+                    rans_group8<LS>(tab, lst, rw, x, rq, s_lo, s_hi);
+                    *reinterpret_cast<uint2*>(out) = make_uint2(s_lo, s_hi);
+                    out += 8;
+                }
+                pos += nfast * 8; remaining -= nfast * 8;
+            } else if (mode == 1 || mode == 2) {
+                // 16-bit elements, one partner plane.  Rounds of 32 elements: the partner bytes come as
+                // aligned 32-byte blocks two rounds ahead of their use (cur, nxt, and one in flight), the
+                // composed elements leave as two 32-byte stores.  Blocks that are not wholly inside the
+                // partner's chunk are never read whole, so nothing outside the caller's buffers is touched.
+                if (remaining >= 8 && ((reinterpret_cast<uintptr_t>(ep.dst) + size_t(pos) * 2) & 31) != 0) {
+                    uint32_t s_lo, s_hi;  // one more group of eight brings the destination to a 32-byte boundary
+                    top_up();
+                    rans_group8<LS>(tab, lst, rw, x, rq, s_lo, s_hi);
+                    emit(ep, pos, 8, uint64_t(s_lo) | uint64_t(s_hi) << 32);
+                    pos += 8; remaining -= 8;
+                }
+                const uintptr_t p_lo = reinterpret_cast<uintptr_t>(ep.partner[0]), p_hi = p_lo + it.n;
+                const uintptr_t pa = p_lo + pos;
+                uintptr_t q = pa & ~uintptr_t(31);
+                uint8_t* out = ep.dst + size_t(pos) * 2;
+                // round r reads the block at q + 32 (r + 2): it must end inside the chunk
+                uint32_t rounds = 0;
+                if ((reinterpret_cast<uintptr_t>(out) & 31) == 0 && q + 96 <= p_hi) {
+                    rounds = uint32_t((p_hi - q - 96) >> 5) + 1;
+                    if (rounds > (remaining >> 5)) rounds = remaining >> 5;
+                }
+                if (rounds) {
+                    const uint32_t off = uint32_t(pa & 31);
+                    Block32 cur = load_block_guarded(q, p_lo, p_hi), nxt = ldg256(reinterpret_cast<const void*>(q + 32));
+                    for (uint32_t r = 0; r < rounds; ++r) {
+                        const Block32 ahead = ldg256(reinterpret_cast<const void*>(q + 64));
+                        uint32_t pw[8];
+                        uint4 v[4];
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            uint32_t s_lo, s_hi;
+                            top_up();
+                            rans_group8<LS>(tab, lst, rw, x, rq, s_lo, s_hi);
+                            if (g == 0) extract32(cur, nxt, off, pw);
+                            if (mode == 1) { compose16x4(s_lo, pw[2 * g], v[g].x, v[g].y); compose16x4(s_hi, pw[2 * g + 1], v[g].z, v[g].w); }
+                            else { compose16x4(pw[2 * g], s_lo, v[g].x, v[g].y); compose16x4(pw[2 * g + 1], s_hi, v[g].z, v[g].w); }
+                        }
+                        stg256(out, v[0], v[1]);
+                        stg256(out + 32, v[2], v[3]);
+                        out += 64; q += 32;
+                        cur = nxt; nxt = ahead;
+                    }
+                    pos += rounds * 32; remaining -= rounds * 32;
+                }
+            } else {
+                // other fused kinds: partner words streamed one group ahead
+                PartnerStream ps;
+                if (remaining >= 8) ps.start(ep, pos, it.n);
+                while (remaining >= 8) {
+                    uint32_t s_lo, s_hi;
+                    uint64_t pb[4] = {0, 0, 0, 0};
+                    top_up();
+                    ps.prefetch();
+                    rans_group8<LS>(tab, lst, rw, x, rq, s_lo, s_hi);
+                    ps.take(ep.slot, pb);
+                    emit_with(ep, pos, 8, uint64_t(s_lo) | uint64_t(s_hi) << 32, pb);
+                    pos += 8; remaining -= 8;
+                }
+            }
+            // tail: whatever the fast loops left
+            while (remaining) {
+                uint32_t g = remaining < 8 ? remaining : 8, s_lo, s_hi;
+                top_up();
+                rans_short_group<LS>(tab, lst, rw, x, rq, g, s_lo, s_hi);
+                emit(ep, pos, g, uint64_t(s_lo) | uint64_t(s_hi) << 32);
+                pos += g; remaining -= g;
+            }
             if (rq > end_q) err = ST_STREAM_UNDERRUN;  // decompress.rs:99-104
         }
     }

@@ -32,7 +32,7 @@ int64_t noalloc_scratch_for(int device, uint8_t** out) {
         cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
         if (e != cudaSuccess) return fail(PTWM_RC_CUDA, std::string("cudaGetSymbolAddress(g_noalloc_scratch): ") + cudaGetErrorString(e));
         // the decoders need more dynamic shared memory than the default limit; an attribute, not an allocation
-        CUDA_TRY(cudaFuncSetAttribute(rans_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(rans_smem_bytes(rans_l_entries(255)))));
+        CUDA_TRY(cudaFuncSetAttribute(rans_decode_kernel_t<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(rans_smem_bytes(rans_l_entries(255)))));
         CUDA_TRY(cudaFuncSetAttribute(huffman_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, HUF_SMEM));
         CUDA_TRY(cudaFuncSetAttribute(tans_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TANS_SMEM));
         it = g_noalloc_ptr.emplace(device, static_cast<uint8_t*>(p)).first;
@@ -108,7 +108,7 @@ extern "C" int64_t ptwm_b200_decode_plane_noalloc(uint8_t state_format_version, 
     const DecodeItem* d_it = reinterpret_cast<const DecodeItem*>(scratch + 64);
     uint32_t* d_status = reinterpret_cast<uint32_t*>(scratch);
     switch (codec) {
-        case C_RANS: rans_decode_kernel<<<1, 32, rans_smem_bytes(rans_l_entries(255)), st>>>(d_it, 1, bases, d_status, rans_l_entries(255)); break;
+        case C_RANS: rans_decode_kernel_t<false><<<1, 32, rans_smem_bytes(rans_l_entries(255)), st>>>(d_it, 1, bases, d_status, rans_l_entries(255)); break;
         case C_HUFFMAN: huffman_decode_kernel<<<1, 32, HUF_SMEM, st>>>(d_it, 1, bases, d_status); break;
         case C_TANS: tans_decode_kernel<<<1, 32, TANS_SMEM, st>>>(d_it, 1, bases, d_status); break;
         default: o1sac_decode_kernel<<<1, 32, 0, st>>>(d_it, 1, bases, d_status); break;

@@ -45,11 +45,13 @@ int64_t device_state(int dev, DeviceState** out) {
         CUDA_TRY(cudaMemcpy(s.d_tabs, &crc_tables(), sizeof(CrcTables), cudaMemcpyHostToDevice));
     }
     if (!s.attrs) {
-        CUDA_TRY(cudaFuncSetAttribute(rans_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(rans_smem_bytes(rans_l_entries(255)))));
+        CUDA_TRY(cudaFuncSetAttribute(rans_decode_kernel_t<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(rans_smem_bytes(rans_l_entries(255)))));
+        CUDA_TRY(cudaFuncSetAttribute(rans_decode_kernel_t<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(rans_smem_bytes(RANS_NARROW_SYMBOLS + 2, true))));
+        CUDA_TRY(cudaFuncSetAttribute(rans_decode_kernel_t<true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         CUDA_TRY(cudaFuncSetAttribute(huffman_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, HUF_SMEM));
         CUDA_TRY(cudaFuncSetAttribute(tans_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TANS_SMEM));
         // the decoders are limited by how many chunk tables fit in an SM: ask for the largest shared-memory carve-out
-        CUDA_TRY(cudaFuncSetAttribute(rans_decode_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        CUDA_TRY(cudaFuncSetAttribute(rans_decode_kernel_t<false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         CUDA_TRY(cudaFuncSetAttribute(huffman_decode_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         CUDA_TRY(cudaFuncSetAttribute(tans_decode_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         s.attrs = true;
@@ -111,7 +113,9 @@ struct ptwm_b200_plan {
     std::vector<uint32_t> item_tensor;  // item id -> tensor index (for error messages)
     uint32_t launches = 0;
     // per launch slot: 0-3 phase-0 decoders (rANS, Huffman, tANS, O1SAC), 4 scratch copies, 5-8 phase-1 decoders, 9 final merge, 10 CRC, 11 XXH64
-    uint32_t rans_max_sym[2] = {0, 0};  // per phase: largest alphabet bound among the rANS chunks (sizes the kernel's shared memory)
+    // rANS chunks per phase: the first `rans_narrow` items hold few distinct symbols and go to the kernel with a symbol
+    // list per lane (`rans_rows` rows); the rest go to the general kernel, sized by the largest alphabet bound among them.
+    uint32_t rans_max_sym[2] = {0, 0}, rans_narrow[2] = {0, 0}, rans_rows[2] = {0, 0};
     uint64_t slot_bytes[12] = {0};
     uint32_t slot_items[12] = {0};
     std::mutex mu;
@@ -148,7 +152,7 @@ void plan_tensor(ptwm_b200_plan& pl, uint32_t ti, const TensorDesc& t, uint64_t 
         it.src = make_ref(SP_BLOB, ch.data_off); it.src_len = uint32_t(ch.data_len); it.n = ch.decoded; it.id = new_id();
         it.partner[0] = it.partner[1] = it.partner[2] = REF_NONE; it.state = REF_NONE; it.work = REF_NONE;
         span(ch.data_off, ch.data_len);
-        it.row_len = ch.max_sym;  // rANS: alphabet bound (row_len is only read by Order1ScaleAC)
+        it.row_len = uint32_t(ch.max_sym) | uint32_t(ch.distinct) << 16;  // rANS: alphabet bound and distinct symbols, for the planner only (the kernels read row_len for Order1ScaleAC)
         if (p.codec == C_O1SAC) {
             it.state = make_ref(SP_BLOB, ch.state_off); it.state_len = uint32_t(ch.state_len); it.state_version = ch.state_version;
             it.row_len = uint32_t(p.row_len);
@@ -234,11 +238,23 @@ void finish_lists(ptwm_b200_plan& pl) {
     for (int ph = 0; ph < 2; ++ph) {
         for (int cc = 0; cc < 4; ++cc) {
             auto& v = pl.dec[ph][cc];
-            std::stable_sort(v.begin(), v.end(), [](const DecodeItem& a, const DecodeItem& b) { return a.n > b.n; });
+            auto narrow = [cc](const DecodeItem& a) { return cc == 0 && (a.row_len >> 16) <= RANS_NARROW_SYMBOLS; };
+            std::stable_sort(v.begin(), v.end(), [&](const DecodeItem& a, const DecodeItem& b) {
+                bool na = narrow(a), nb = narrow(b);
+                return na != nb ? na : a.n > b.n;
+            });
             if (!v.empty()) pl.launches++;
             int slot = ph * 5 + cc;
             pl.slot_items[slot] = uint32_t(v.size());
-            if (cc == 0) for (auto& it : v) pl.rans_max_sym[ph] = std::max(pl.rans_max_sym[ph], it.row_len);
+            if (cc == 0) {
+                uint32_t most = 0;
+                for (auto& it : v) {
+                    if (narrow(it)) { pl.rans_narrow[ph]++; most = std::max(most, it.row_len >> 16); }
+                    else pl.rans_max_sym[ph] = std::max(pl.rans_max_sym[ph], it.row_len & 0xFFu);
+                }
+                pl.rans_rows[ph] = most + 2;
+                if (pl.rans_narrow[ph] && pl.rans_narrow[ph] < v.size()) pl.launches++;
+            }
             for (auto& it : v) {
                 uint64_t np = it.fused ? uint64_t(kind_planes(it.kind)) : 1, eb = it.fused ? uint64_t(kind_elem_bytes(it.kind)) : 1;
                 pl.slot_bytes[slot] += uint64_t(it.src_len) + it.state_len + uint64_t(it.n) * (np - 1) + uint64_t(it.n) * eb;
@@ -301,8 +317,16 @@ int64_t enqueue(ptwm_b200_plan& pl, DevicePlan& d, const Bases& bases, uint32_t 
             CUDA_TRY(mark(ph * 5 + cc, 0));
             switch (cc) {
                 case 0: {
-                    uint32_t le = rans_l_entries(pl.rans_max_sym[ph]);
-                    rans_decode_kernel<<<(n + RANS_WARP_CHUNKS - 1) / RANS_WARP_CHUNKS, 32, rans_smem_bytes(le), st>>>(it, n, bases, status, le);
+                    const uint32_t nn = pl.rans_narrow[ph], nw = n - nn;
+                    if (nn) {
+                        const uint32_t rows = pl.rans_rows[ph];
+                        rans_decode_kernel_t<true><<<(nn + RANS_WARP_CHUNKS - 1) / RANS_WARP_CHUNKS, 32, rans_smem_bytes(rows, true), st>>>(it, nn, bases, status, rows);
+                        CUDA_TRY(cudaGetLastError());
+                    }
+                    if (nw) {
+                        const uint32_t le = rans_l_entries(pl.rans_max_sym[ph]);
+                        rans_decode_kernel_t<false><<<(nw + RANS_WARP_CHUNKS - 1) / RANS_WARP_CHUNKS, 32, rans_smem_bytes(le), st>>>(it + nn, nw, bases, status, le);
+                    }
                     break;
                 }
                 case 1: huffman_decode_kernel<<<(n + HUF_WARP_CHUNKS - 1) / HUF_WARP_CHUNKS, 32, HUF_SMEM, st>>>(it, n, bases, status); break;
@@ -458,7 +482,7 @@ int64_t decode_plane_cuda(uint8_t sfv, const uint8_t* state, size_t state_len, c
     const DecodeItem* d_it = reinterpret_cast<const DecodeItem*>(scratch + 64);
     uint32_t* d_status = reinterpret_cast<uint32_t*>(scratch);
     switch (codec) {
-        case C_RANS: rans_decode_kernel<<<1, 32, rans_smem_bytes(rans_l_entries(255)), st>>>(d_it, 1, bases, d_status, rans_l_entries(255)); break;
+        case C_RANS: rans_decode_kernel_t<false><<<1, 32, rans_smem_bytes(rans_l_entries(255)), st>>>(d_it, 1, bases, d_status, rans_l_entries(255)); break;
         case C_HUFFMAN: huffman_decode_kernel<<<1, 32, HUF_SMEM, st>>>(d_it, 1, bases, d_status); break;
         case C_TANS: tans_decode_kernel<<<1, 32, TANS_SMEM, st>>>(d_it, 1, bases, d_status); break;
         default: o1sac_decode_kernel<<<1, 32, 0, st>>>(d_it, 1, bases, d_status); break;
