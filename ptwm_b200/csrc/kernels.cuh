@@ -232,6 +232,147 @@ __device__ __forceinline__ void split_four_dev(uint32_t n, uint32_t s, uint32_t&
     start = s * base + (s < rem ? s : rem);
 }
 
+// 256-bit global accesses (sm_100): a lane that walks its own stream touches
+// one 32-byte sector per instruction instead of half of one, which halves the
+// load/store-pipe cost of these scattered accesses.
+struct Block32 { uint32_t w[8]; };
+__device__ __forceinline__ Block32 ldg256(const void* p) {
+    Block32 b;
+    asm("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+        : "=r"(b.w[0]), "=r"(b.w[1]), "=r"(b.w[2]), "=r"(b.w[3]), "=r"(b.w[4]), "=r"(b.w[5]), "=r"(b.w[6]), "=r"(b.w[7])
+        : "l"(p));
+    return b;
+}
+__device__ __forceinline__ void stg256(void* p, uint4 a, uint4 b) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+                 : "memory");
+}
+// Aligned 32-byte block at `a`; bytes outside [lo, hi) read as zero and are not touched.
+__device__ __forceinline__ Block32 load_block_guarded(uintptr_t a, uintptr_t lo, uintptr_t hi) {
+    if (a >= lo && a + 32 <= hi) return ldg256(reinterpret_cast<const void*>(a));
+    Block32 b;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        uint32_t v = 0;
+        for (int i = 0; i < 4; ++i) {
+            uintptr_t q = a + 4 * k + i;
+            if (q >= lo && q < hi) v |= uint32_t(__ldg(reinterpret_cast<const uint8_t*>(q))) << (8 * i);
+        }
+        b.w[k] = v;
+    }
+    return b;
+}
+// The 32 bytes that start `off` (0..31) bytes into the 64 bytes (cur, nxt), as eight words.
+__device__ __forceinline__ void extract32(const Block32& cur, const Block32& nxt, uint32_t off, uint32_t out[8]) {
+    uint32_t a[16], b[12], c[10], d[9];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { a[i] = cur.w[i]; a[8 + i] = nxt.w[i]; }
+    const bool j4 = off & 16, j2 = off & 8, j1 = off & 4;
+#pragma unroll
+    for (int i = 0; i < 12; ++i) b[i] = j4 ? a[i + 4] : a[i];
+#pragma unroll
+    for (int i = 0; i < 10; ++i) c[i] = j2 ? b[i + 2] : b[i];
+#pragma unroll
+    for (int i = 0; i < 9; ++i) d[i] = j1 ? c[i + 1] : c[i];
+    const uint32_t sel = 0x3210u + 0x1111u * (off & 3u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = __byte_perm(d[i], d[i + 1], sel);
+}
+
+// ---- fast output loops of a decoding lane -----------------------------------
+// `dec8(s_lo, s_hi)` decodes the lane's next eight symbols (symbol j in byte
+// j & 3 of s_lo for j < 4, of s_hi above); the loops below place them.
+//
+// Fused lane, 16-bit elements, one partner plane.  Rounds of 32 elements: the
+// partner bytes come as aligned 32-byte blocks two rounds ahead of their use
+// (cur, nxt, and one in flight), the composed elements leave as two 32-byte
+// stores.  Blocks that are not wholly inside the partner's chunk are never read
+// whole, so nothing outside the caller's buffers is touched.  What does not
+// fill a round is left to the caller.
+template <class Dec8>
+__device__ __forceinline__ void fused16_rounds(const Epilogue& ep, uint32_t chunk_n, uint32_t& pos, uint32_t& remaining, Dec8&& dec8) {
+    if (remaining >= 8 && ((reinterpret_cast<uintptr_t>(ep.dst) + size_t(pos) * 2) & 31) != 0) {
+        uint32_t s_lo, s_hi;  // one more group of eight brings the destination to a 32-byte boundary
+        dec8(s_lo, s_hi);
+        emit(ep, pos, 8, uint64_t(s_lo) | uint64_t(s_hi) << 32);
+        pos += 8; remaining -= 8;
+    }
+    const uintptr_t p_lo = reinterpret_cast<uintptr_t>(ep.partner[0]), p_hi = p_lo + chunk_n;
+    const uintptr_t pa = p_lo + pos;
+    uintptr_t q = pa & ~uintptr_t(31);
+    uint8_t* out = ep.dst + size_t(pos) * 2;
+    // round r reads the block at q + 32 (r + 2): it must end inside the chunk
+    uint32_t rounds = 0;
+    if ((reinterpret_cast<uintptr_t>(out) & 31) == 0 && q + 96 <= p_hi) {
+        rounds = uint32_t((p_hi - q - 96) >> 5) + 1;
+        if (rounds > (remaining >> 5)) rounds = remaining >> 5;
+    }
+    if (!rounds) return;
+    const uint32_t off = uint32_t(pa & 31);
+    const bool low_plane = ep.slot == 0;  // the lane decodes the low bytes, the partner holds the high bytes
+    Block32 cur = load_block_guarded(q, p_lo, p_hi), nxt = ldg256(reinterpret_cast<const void*>(q + 32));
+    for (uint32_t r = 0; r < rounds; ++r) {
+        const Block32 ahead = ldg256(reinterpret_cast<const void*>(q + 64));
+        uint32_t pw[8];
+        uint4 v[4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            uint32_t s_lo, s_hi;
+            dec8(s_lo, s_hi);
+            if (g == 0) extract32(cur, nxt, off, pw);
+            if (low_plane) { compose16x4(s_lo, pw[2 * g], v[g].x, v[g].y); compose16x4(s_hi, pw[2 * g + 1], v[g].z, v[g].w); }
+            else { compose16x4(pw[2 * g], s_lo, v[g].x, v[g].y); compose16x4(pw[2 * g + 1], s_hi, v[g].z, v[g].w); }
+        }
+        stg256(out, v[0], v[1]);
+        stg256(out + 32, v[2], v[3]);
+        out += 64; q += 32;
+        cur = nxt; nxt = ahead;
+    }
+    pos += rounds * 32; remaining -= rounds * 32;
+}
+// Plain lane: eight symbols are eight bytes of the plane; 32 bytes per store.
+template <class Dec8>
+__device__ __forceinline__ void plain_rounds(const Epilogue& ep, uint32_t& pos, uint32_t& remaining, Dec8&& dec8) {
+    uint8_t* out = ep.dst + pos;
+    if (reinterpret_cast<uintptr_t>(out) & 7) return;
+    while (remaining >= 8 && (reinterpret_cast<uintptr_t>(out) & 31) != 0) {
+        uint32_t s_lo, s_hi;
+        dec8(s_lo, s_hi);
+        *reinterpret_cast<uint2*>(out) = make_uint2(s_lo, s_hi);
+        out += 8; pos += 8; remaining -= 8;
+    }
+    const uint32_t rounds = remaining >> 5;
+    for (uint32_t r = 0; r < rounds; ++r) {
+        uint4 a, b;
+        dec8(a.x, a.y); dec8(a.z, a.w); dec8(b.x, b.y); dec8(b.z, b.w);
+        stg256(out, a, b);
+        out += 32;
+    }
+    pos += rounds * 32; remaining -= rounds * 32;
+}
+// Other fused kinds: partner words streamed one group ahead, 128-bit stores.
+template <class Dec8>
+__device__ __forceinline__ void fused_groups(const Epilogue& ep, uint32_t chunk_n, uint32_t& pos, uint32_t& remaining, Dec8&& dec8) {
+    if (remaining < 8) return;
+    PartnerStream ps;
+    ps.start(ep, pos, chunk_n);
+    while (remaining >= 8) {
+        uint32_t s_lo, s_hi;
+        uint64_t pb[4] = {0, 0, 0, 0};
+        ps.prefetch();
+        dec8(s_lo, s_hi);
+        ps.take(ep.slot, pb);
+        emit_with(ep, pos, 8, uint64_t(s_lo) | uint64_t(s_hi) << 32, pb);
+        pos += 8; remaining -= 8;
+    }
+}
+template <class Dec8>
+__device__ __forceinline__ void fast_groups(const Epilogue& ep, uint32_t chunk_n, uint32_t& pos, uint32_t& remaining, Dec8&& dec8) {
+    if (!ep.fused) plain_rounds(ep, pos, remaining, dec8);
+    else if (ep.kind == K_M16) fused16_rounds(ep, chunk_n, pos, remaining, dec8);
+    else fused_groups(ep, chunk_n, pos, remaining, dec8);
+}
+
 // ---- per-lane byte window over a stream ------------------------------------
 // A lane reads its stream one byte (rANS, forward) or one aligned word
 // (Huffman, backward) at a time.  Global memory is fetched in aligned 16-byte
@@ -346,53 +487,6 @@ __device__ __forceinline__ void rans_group8(const uint32_t* tab, const uint32_t*
     } else {
         rq += used >> 3;
     }
-}
-
-// 256-bit global accesses (sm_100): a lane that walks its own stream touches
-// one 32-byte sector per instruction instead of half of one, which halves the
-// load/store-pipe cost of these scattered accesses.
-struct Block32 { uint32_t w[8]; };
-__device__ __forceinline__ Block32 ldg256(const void* p) {
-    Block32 b;
-    asm("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-        : "=r"(b.w[0]), "=r"(b.w[1]), "=r"(b.w[2]), "=r"(b.w[3]), "=r"(b.w[4]), "=r"(b.w[5]), "=r"(b.w[6]), "=r"(b.w[7])
-        : "l"(p));
-    return b;
-}
-__device__ __forceinline__ void stg256(void* p, uint4 a, uint4 b) {
-    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
-                 : "memory");
-}
-// Aligned 32-byte block at `a`; bytes outside [lo, hi) read as zero and are not touched.
-__device__ __forceinline__ Block32 load_block_guarded(uintptr_t a, uintptr_t lo, uintptr_t hi) {
-    if (a >= lo && a + 32 <= hi) return ldg256(reinterpret_cast<const void*>(a));
-    Block32 b;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        uint32_t v = 0;
-        for (int i = 0; i < 4; ++i) {
-            uintptr_t q = a + 4 * k + i;
-            if (q >= lo && q < hi) v |= uint32_t(__ldg(reinterpret_cast<const uint8_t*>(q))) << (8 * i);
-        }
-        b.w[k] = v;
-    }
-    return b;
-}
-// The 32 bytes that start `off` (0..31) bytes into the 64 bytes (cur, nxt), as eight words.
-__device__ __forceinline__ void extract32(const Block32& cur, const Block32& nxt, uint32_t off, uint32_t out[8]) {
-    uint32_t a[16], b[12], c[10], d[9];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { a[i] = cur.w[i]; a[8 + i] = nxt.w[i]; }
-    const bool j4 = off & 16, j2 = off & 8, j1 = off & 4;
-#pragma unroll
-    for (int i = 0; i < 12; ++i) b[i] = j4 ? a[i + 4] : a[i];
-#pragma unroll
-    for (int i = 0; i < 10; ++i) c[i] = j2 ? b[i + 2] : b[i];
-#pragma unroll
-    for (int i = 0; i < 9; ++i) d[i] = j1 ? c[i + 1] : c[i];
-    const uint32_t sel = 0x3210u + 0x1111u * (off & 3u);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) out[i] = __byte_perm(d[i], d[i + 1], sel);
 }
 
 template <bool PER_LANE>
@@ -540,79 +634,10 @@ __global__ void __launch_bounds__(32, 24) rans_decode_kernel_t(const DecodeItem*
                     pos += g; remaining -= g;
                 }
             }
-            const int mode = !ep.fused ? 0 : ep.kind == K_M16 ? 1 + ep.slot : 3;
-            if (mode == 0) {
-                // plain lane: eight symbols are eight bytes of the plane
-                uint8_t* out = ep.dst + pos;
-                uint32_t nfast = (reinterpret_cast<uintptr_t>(out) & 7) == 0 ? remaining >> 3 : 0;
-                for (uint32_t i = 0; i < nfast; ++i) {
-                    uint32_t s_lo, s_hi;
-                    top_up();
-                    rans_group8<LS>(tab, lst, rw, x, rq, s_lo, s_hi);
-                    *reinterpret_cast<uint2*>(out) = make_uint2(s_lo, s_hi);
-                    out += 8;
-                }
-                pos += nfast * 8; remaining -= nfast * 8;
-            } else if (mode == 1 || mode == 2) {
-                // 16-bit elements, one partner plane.  Rounds of 32 elements: the partner bytes come as
-                // aligned 32-byte blocks two rounds ahead of their use (cur, nxt, and one in flight), the
-                // composed elements leave as two 32-byte stores.  Blocks that are not wholly inside the
-                // partner's chunk are never read whole, so nothing outside the caller's buffers is touched.
-                if (remaining >= 8 && ((reinterpret_cast<uintptr_t>(ep.dst) + size_t(pos) * 2) & 31) != 0) {
-                    uint32_t s_lo, s_hi;  // one more group of eight brings the destination to a 32-byte boundary
-                    top_up();
-                    rans_group8<LS>(tab, lst, rw, x, rq, s_lo, s_hi);
-                    emit(ep, pos, 8, uint64_t(s_lo) | uint64_t(s_hi) << 32);
-                    pos += 8; remaining -= 8;
-                }
-                const uintptr_t p_lo = reinterpret_cast<uintptr_t>(ep.partner[0]), p_hi = p_lo + it.n;
-                const uintptr_t pa = p_lo + pos;
-                uintptr_t q = pa & ~uintptr_t(31);
-                uint8_t* out = ep.dst + size_t(pos) * 2;
-                // round r reads the block at q + 32 (r + 2): it must end inside the chunk
-                uint32_t rounds = 0;
-                if ((reinterpret_cast<uintptr_t>(out) & 31) == 0 && q + 96 <= p_hi) {
-                    rounds = uint32_t((p_hi - q - 96) >> 5) + 1;
-                    if (rounds > (remaining >> 5)) rounds = remaining >> 5;
-                }
-                if (rounds) {
-                    const uint32_t off = uint32_t(pa & 31);
-                    Block32 cur = load_block_guarded(q, p_lo, p_hi), nxt = ldg256(reinterpret_cast<const void*>(q + 32));
-                    for (uint32_t r = 0; r < rounds; ++r) {
-                        const Block32 ahead = ldg256(reinterpret_cast<const void*>(q + 64));
-                        uint32_t pw[8];
-                        uint4 v[4];
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            uint32_t s_lo, s_hi;
-                            top_up();
-                            rans_group8<LS>(tab, lst, rw, x, rq, s_lo, s_hi);
-                            if (g == 0) extract32(cur, nxt, off, pw);
-                            if (mode == 1) { compose16x4(s_lo, pw[2 * g], v[g].x, v[g].y); compose16x4(s_hi, pw[2 * g + 1], v[g].z, v[g].w); }
-                            else { compose16x4(pw[2 * g], s_lo, v[g].x, v[g].y); compose16x4(pw[2 * g + 1], s_hi, v[g].z, v[g].w); }
-                        }
-                        stg256(out, v[0], v[1]);
-                        stg256(out + 32, v[2], v[3]);
-                        out += 64; q += 32;
-                        cur = nxt; nxt = ahead;
-                    }
-                    pos += rounds * 32; remaining -= rounds * 32;
-                }
-            } else {
-                // other fused kinds: partner words streamed one group ahead
-                PartnerStream ps;
-                if (remaining >= 8) ps.start(ep, pos, it.n);
-                while (remaining >= 8) {
-                    uint32_t s_lo, s_hi;
-                    uint64_t pb[4] = {0, 0, 0, 0};
-                    top_up();
-                    ps.prefetch();
-                    rans_group8<LS>(tab, lst, rw, x, rq, s_lo, s_hi);
-                    ps.take(ep.slot, pb);
-                    emit_with(ep, pos, 8, uint64_t(s_lo) | uint64_t(s_hi) << 32, pb);
-                    pos += 8; remaining -= 8;
-                }
-            }
+            fast_groups(ep, it.n, pos, remaining, [&](uint32_t& s_lo, uint32_t& s_hi) {
+                top_up();
+                rans_group8<LS>(tab, lst, rw, x, rq, s_lo, s_hi);
+            });
             // tail: whatever the fast loops left
             while (remaining) {
                 uint32_t g = remaining < 8 ? remaining : 8, s_lo, s_hi;
@@ -746,13 +771,16 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
         // byte steps until the read position is word aligned
         while ((rp & 3) && rp > start) { --rp; cont |= uint64_t(ring.byte(rp)) << cnt; cnt += 8; }
         const uint32_t mask = (1u << max_bits) - 1;
-        uint64_t pos = seg_start;
-        uint32_t remaining = seg_len;
-        uint32_t g = remaining ? first_group(ep, pos, remaining) : 0;
-        PartnerStream ps;
-        bool streaming = false;
-        auto refill = [&]() {
-            // one aligned word (or the last partial one) when at most 32 bits are left
+        uint32_t pos = seg_start, remaining = seg_len;
+        // The lanes of a warp drain at similar rates: when any active lane runs low, every lane with room refills,
+        // so the refill code runs once per several groups instead of (for some lane) in every one.
+        auto ring_top_up = [&]() {
+            if (__any_sync(__activemask(), rp - fetched < 32 && fetched > start)) {
+                if (rp - fetched <= 48 && fetched > start) { fetched -= 16; ring.put(fetched, pending); pending = fetch16(fetched - 16, lo16, hi16); }
+            }
+        };
+        // one aligned word (or the last partial one) into the bit container when it holds at most 32 bits
+        auto take_word = [&]() {
             if (cnt <= 32 && rp > start) {
                 uint32_t w = __byte_perm(ring.word(rp - 4), 0, 0x0123);  // byte rp-1 becomes the lowest
                 uint32_t take = rp - start >= 4 ? 4u : uint32_t(rp - start);
@@ -762,38 +790,43 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
                 rp -= take;
             }
         };
-        while (remaining) {
-            if (rp - fetched < 32 && fetched > start) { fetched -= 16; ring.put(fetched, pending); pending = fetch16(fetched - 16, lo16, hi16); }
-            uint64_t pb[4] = {0, 0, 0, 0};
-            if (streaming) ps.prefetch();
-            uint64_t syms = 0;
-            if (g == 8) {
+        auto refill = [&]() {  // before two symbols (at most 22 bits)
+            if (__any_sync(__activemask(), cnt < 22 && rp > start)) take_word();
+        };
+        auto symbol = [&]() -> uint32_t {
+            uint32_t e = table[uint32_t(cont) & mask];
+            uint32_t nb = e >> 8;
+            if (nb > cnt) { err = ST_STREAM_UNDERRUN; nb = cnt; }  // decompress.rs:176-196
+            cont >>= nb; cnt -= nb;
+            return e;
+        };
+        auto dec8 = [&](uint32_t& s_lo, uint32_t& s_hi) {
+            ring_top_up();
+            s_lo = 0; s_hi = 0;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    if ((j & 1) == 0) refill();  // two symbols need at most 22 bits, a refill leaves more than 32
-                    uint32_t e = table[uint32_t(cont) & mask];
-                    uint32_t nb = e >> 8;
-                    if (nb > cnt) { err = ST_STREAM_UNDERRUN; nb = cnt; }  // decompress.rs:176-196
-                    cont >>= nb; cnt -= nb;
-                    syms |= uint64_t(e & 0xFF) << (8 * j);
-                }
-            } else {
-                for (uint32_t j = 0; j < g; ++j) {
-                    refill();
-                    uint32_t e = table[uint32_t(cont) & mask];
-                    uint32_t nb = e >> 8;
-                    if (nb > cnt) { err = ST_STREAM_UNDERRUN; nb = cnt; }
-                    cont >>= nb; cnt -= nb;
-                    syms |= uint64_t(e & 0xFF) << (8 * j);
-                }
+            for (int j = 0; j < 8; ++j) {
+                if ((j & 1) == 0) refill();
+                uint32_t e = symbol();
+                const uint32_t ins = (0x3210u & ~(0xFu << (4 * (j & 3)))) | (4u << (4 * (j & 3)));  // low byte of e into byte j & 3
+                if (j < 4) s_lo = __byte_perm(s_lo, e, ins); else s_hi = __byte_perm(s_hi, e, ins);
             }
-            if (streaming) ps.take(ep.slot, pb);
-            else gather_partners(ep, pos, g, pb);
-            emit_with(ep, pos, g, syms, pb);
+        };
+        auto short_group = [&](uint32_t g) {
+            uint64_t syms = 0;
+            ring_top_up();
+            for (uint32_t j = 0; j < g; ++j) {
+                take_word();
+                syms |= uint64_t(symbol() & 0xFFu) << (8 * j);
+            }
+            emit(ep, pos, g, syms);
             pos += g; remaining -= g;
-            g = remaining < 8 ? remaining : 8;
-            if (!streaming && remaining) { ps.start(ep, pos, it.n); streaming = true; }
+        };
+        if (remaining) {
+            uint32_t g = first_group(ep, pos, remaining);
+            if (g < 8 || remaining < 16) short_group(g);
         }
+        fast_groups(ep, it.n, pos, remaining, dec8);
+        while (remaining) short_group(remaining < 8 ? remaining : 8);
         // every stream must end with no unread byte and only zero bits left
         // (decompress.rs:140-144, bitstream.rs:184-186)
         while (rp > start && !err) {
