@@ -653,15 +653,48 @@ __global__ void __launch_bounds__(32, 24) rans_decode_kernel_t(const DecodeItem*
 }
 
 // ---- canonical Huffman -----------------------------------------------------
+// Shared memory per chunk:
+//  * a one-symbol table over the next HUF_LUT_BITS stream bits, (length << 8) |
+//    symbol, 0 when the code is longer than the window: 1 KiB instead of the
+//    4 KiB of a table over all eleven bits, and shared memory per chunk is what
+//    bounds the streams an SM keeps in flight;
+//  * the canonical description (first code, count and list offset per length,
+//    the symbols in canonical order): codes longer than the window (the rarest
+//    symbols) and windows that no code covers are decoded from it.
 constexpr int HUF_WARP_CHUNKS = 8;
-constexpr int HUF_SMEM_PER_CHUNK = 2048 * 2;  // 2^11 entries of len<<8 | sym
-constexpr int HUF_SMEM = HUF_WARP_CHUNKS * HUF_SMEM_PER_CHUNK + RING_SMEM;
+constexpr int HUF_LUT_BITS = 9;
+constexpr int HUF_LUT_BYTES = 2 << HUF_LUT_BITS;
+constexpr int HUF_CANON_BYTES = 256 + 3 * 16 * 2;  // symbols in canonical order; u16 first[16], count[16], offs[16]
+constexpr int HUF_SMEM = HUF_WARP_CHUNKS * (HUF_LUT_BYTES + HUF_CANON_BYTES) + RING_SMEM;
+
+struct HuffCanon {
+    const uint8_t* syms;
+    const uint16_t* first;  // first[0] = max_bits
+    const uint16_t* count;  // count[0] = 1 when the tables are usable
+    const uint16_t* offs;
+};
+// One symbol from the low `max_bits` bits of `window` (stream order, first bit lowest): (length << 8) | symbol.
+// A window that no code covers reads as symbol 0 of full length, like an unassigned slot of the reference's table
+// (huffman/tree.rs:128-177).
+__device__ __forceinline__ uint32_t huff_canon_decode(const HuffCanon& hc, uint32_t max_bits, uint32_t window, uint32_t shortest = 1) {
+    const uint32_t v = __brev(window) >> (32 - max_bits);  // code bits, first bit highest
+    for (uint32_t len = shortest; len <= max_bits; ++len) {
+        uint32_t d = (v >> (max_bits - len)) - hc.first[len];
+        if (d < hc.count[len]) return (len << 8) | hc.syms[hc.offs[len] + d];
+    }
+    return max_bits << 8;
+}
 
 __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __restrict__ items, uint32_t n_items, Bases bases, uint32_t* __restrict__ status) {
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t lane = threadIdx.x, c = lane >> 2, s = lane & 3;
-    uint16_t* table = reinterpret_cast<uint16_t*>(smem) + c * 2048;
-    Ring ring{reinterpret_cast<uint32_t*>(smem + HUF_WARP_CHUNKS * HUF_SMEM_PER_CHUNK) + lane};
+    uint16_t* lut_all = reinterpret_cast<uint16_t*>(smem);                                  // [8][512]
+    uint8_t* canon_all = smem + HUF_WARP_CHUNKS * HUF_LUT_BYTES;                            // [8][HUF_CANON_BYTES]
+    Ring ring{reinterpret_cast<uint32_t*>(smem + HUF_WARP_CHUNKS * (HUF_LUT_BYTES + HUF_CANON_BYTES)) + lane};
+    auto canon_of = [&](uint32_t chunk) {
+        uint8_t* base = canon_all + chunk * HUF_CANON_BYTES;
+        return HuffCanon{base, reinterpret_cast<uint16_t*>(base + 256), reinterpret_cast<uint16_t*>(base + 256 + 32), reinterpret_cast<uint16_t*>(base + 256 + 64)};
+    };
 
     const uint32_t item_idx = blockIdx.x * HUF_WARP_CHUNKS + c;
     const bool valid = item_idx < n_items;
@@ -671,8 +704,7 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
     uint32_t err = ST_OK;
     uint32_t max_bits = 1, my_off = 0, my_len = 0;
 
-    // weights header + canonical table: lane s == 0 of each chunk builds it
-    // (weights.rs:34-85, tree.rs:103-177); the other three lanes help fill.
+    // weights header (weights.rs:34-85)
     uint32_t nsym = 0, hb = 0, hdr = 0;
     if (valid) {
         if (it.src_len < 1 || (src[0] & 0x80) == 0) err = ST_BAD_HEADER;
@@ -696,66 +728,96 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
         }
     }
     auto weight = [&](uint32_t i) -> uint32_t { uint8_t b = src[hb + (i >> 1)]; return (i & 1) ? (b >> 4) : (b & 0x0F); };
-    uint32_t next_code[12];
-    if (valid && !err) {
-        uint32_t counts[12];
+
+    // canonical description: lane s == 0 of each chunk (tree.rs:103-177); code assignment is sequential per length
+    if (s == 0) {
+        HuffCanon hc = canon_of(c);
+        uint16_t* first = const_cast<uint16_t*>(hc.first);
+        uint16_t* count = const_cast<uint16_t*>(hc.count);
+        uint16_t* offs = const_cast<uint16_t*>(hc.offs);
+        uint8_t* syms = const_cast<uint8_t*>(hc.syms);
+        uint32_t next_code[12];
+        if (valid && !err) {
+            uint32_t counts[12];
 #pragma unroll
-        for (int k = 0; k < 12; ++k) counts[k] = 0;
-        uint32_t mb = 0, tot = 0;
-        for (uint32_t i = 0; i < nsym; ++i) {
-            uint32_t w = weight(i);
-            if (w > 11) { err = ST_BAD_HEADER; break; }
-            if (w) {
-                tot++;
-                mb = w > mb ? w : mb;
+            for (int k = 0; k < 12; ++k) counts[k] = 0;
+            uint32_t mb = 0, tot = 0;
+            for (uint32_t i = 0; i < nsym; ++i) {
+                uint32_t w = weight(i);
+                if (w > 11) { err = ST_BAD_HEADER; break; }
+                if (w) {
+                    tot++;
+                    mb = w > mb ? w : mb;
 #pragma unroll
-                for (int k = 1; k < 12; ++k) counts[k] += (w == uint32_t(k));
+                    for (int k = 1; k < 12; ++k) counts[k] += (w == uint32_t(k));
+                }
+            }
+            if (tot == 0) err = ST_BAD_HEADER;
+            max_bits = mb < 1 ? 1 : mb;
+            uint32_t code = 0, before = 0;
+#pragma unroll
+            for (int bits = 1; bits < 12; ++bits) {
+                next_code[bits] = 0;
+                if (uint32_t(bits) <= max_bits) {
+                    code = (code + counts[bits - 1]) << 1;
+                    if (code > (1u << bits)) err = ST_BAD_HEADER;
+                    next_code[bits] = code;
+                }
+                first[bits] = uint16_t(code); count[bits] = uint16_t(counts[bits]); offs[bits] = uint16_t(before);
+                before += counts[bits];
             }
         }
-        if (tot == 0) err = ST_BAD_HEADER;
-        max_bits = mb < 1 ? 1 : mb;
-        uint32_t code = 0;
+        if (valid && !err) {
+            uint32_t placed[12];
 #pragma unroll
-        for (int bits = 1; bits < 12; ++bits) {
-            next_code[bits] = 0;
-            if (uint32_t(bits) <= max_bits) {
-                code = (code + counts[bits - 1]) << 1;
-                if (code > (1u << bits)) err = ST_BAD_HEADER;
-                next_code[bits] = code;
+            for (int k = 0; k < 12; ++k) placed[k] = 0;
+            for (uint32_t sym = 0; sym < nsym; ++sym) {
+                uint32_t len = weight(sym);
+                if (!len) continue;
+                uint32_t cde = 0, at = 0;
+#pragma unroll
+                for (int k = 1; k < 12; ++k) if (len == uint32_t(k)) { cde = next_code[k]; next_code[k] = cde + 1; at = offs[k] + placed[k]; placed[k]++; }
+                if (cde >= (1u << len)) { err = ST_BAD_HEADER; break; }
+                syms[at] = uint8_t(sym);
             }
         }
-    }
-    // fill with the fallback entry, then place the codes (only lane s == 0
-    // walks the symbols: canonical code assignment is sequential per length)
-    if (valid && !err) {
-        uint32_t size = 1u << max_bits;
-        uint16_t fb = uint16_t(max_bits << 8);
-        for (uint32_t i = s; i < size; i += 4) table[i] = fb;
-    }
-    __syncwarp();
-    if (valid && !err && s == 0) {
-        uint16_t fb = uint16_t(max_bits << 8);
-        for (uint32_t sym = 0; sym < nsym; ++sym) {
-            uint32_t len = weight(sym);
-            if (!len) continue;
-            uint32_t cde = 0;
-#pragma unroll
-            for (int k = 1; k < 12; ++k) if (len == uint32_t(k)) { cde = next_code[k]; next_code[k] = cde + 1; }
-            if (cde >= (1u << len)) { err = ST_BAD_HEADER; break; }
-            uint32_t rev = __brev(cde) >> (32 - len);
-            uint16_t entry = uint16_t((len << 8) | sym);
-            for (uint32_t idx = rev; idx < (1u << max_bits); idx += (1u << len)) {
-                if (table[idx] != fb && table[idx] != entry) err = ST_BAD_HEADER;
-                table[idx] = entry;
-            }
-        }
+        first[0] = uint16_t(max_bits);
+        count[0] = uint16_t(valid && !err);
     }
     { uint32_t be = __shfl_sync(0xFFFFFFFFu, err, c * 4); err = be > err ? be : err; }  // table errors of the builder lane reach its chunk
+    max_bits = __shfl_sync(0xFFFFFFFFu, max_bits, c * 4);
     __syncwarp();
+
+    // table: the four lanes of a chunk fill it, one symbol of the canonical list at a time
+    {
+        const HuffCanon hc = canon_of(c);
+        const bool build = valid && !err;
+        uint16_t* lut = lut_all + c * (1 << HUF_LUT_BITS);
+        if (build) {
+            const uint16_t fill = max_bits <= HUF_LUT_BITS ? uint16_t(max_bits << 8) : uint16_t(0);  // a slot no code covers; with longer codes the canonical decoder decides
+            for (uint32_t i = s; i < (1u << HUF_LUT_BITS); i += 4) lut[i] = fill;
+        }
+        __syncwarp();
+        if (build) {
+            const uint32_t total = uint32_t(hc.offs[11]) + hc.count[11];
+            for (uint32_t k = s; k < total; k += 4) {
+                uint32_t len = 1;
+                while (len < 11 && k >= uint32_t(hc.offs[len]) + hc.count[len]) ++len;
+                if (len > HUF_LUT_BITS) continue;
+                const uint32_t code = hc.first[len] + (k - hc.offs[len]);
+                const uint32_t rev = __brev(code) >> (32 - len);
+                const uint16_t entry = uint16_t((len << 8) | hc.syms[k]);
+                for (uint32_t idx = rev; idx < (1u << HUF_LUT_BITS); idx += (1u << len)) lut[idx] = entry;
+            }
+        }
+        __syncwarp();
+    }
 
     uint32_t seg_start = 0, seg_len = 0;
     if (valid) split_four_dev(it.n, s, seg_start, seg_len);
     if (valid && !err) {
+        const uint16_t* lut = lut_all + c * (1 << HUF_LUT_BITS);
+        const HuffCanon hc = canon_of(c);
         Epilogue ep = make_epilogue(bases, it);
         const uintptr_t start = reinterpret_cast<uintptr_t>(src + my_off);
         uintptr_t rp = start + my_len;  // one past the next byte to read (moves down)
@@ -767,7 +829,7 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
         uint4 pending = fetch16(fetched - 16, lo16, hi16);
 
         uint64_t cont = 0;
-        uint32_t cnt = 0;
+        int32_t cnt = 0;  // bits in the container
         // byte steps until the read position is word aligned
         while ((rp & 3) && rp > start) { --rp; cont |= uint64_t(ring.byte(rp)) << cnt; cnt += 8; }
         const uint32_t mask = (1u << max_bits) - 1;
@@ -786,38 +848,58 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
                 uint32_t take = rp - start >= 4 ? 4u : uint32_t(rp - start);
                 if (take < 4) w &= (1u << (8 * take)) - 1;
                 cont |= uint64_t(w) << cnt;
-                cnt += 8 * take;
+                cnt += 8 * int32_t(take);
                 rp -= take;
             }
         };
-        auto refill = [&]() {  // before two symbols (at most 22 bits)
-            if (__any_sync(__activemask(), cnt < 22 && rp > start)) take_word();
+        // (length << 8) | symbol of the next code, without consuming it
+        auto peek = [&]() -> uint32_t {
+            uint32_t e = lut[uint32_t(cont) & ((1u << HUF_LUT_BITS) - 1)];
+            if (e == 0) e = huff_canon_decode(hc, max_bits, uint32_t(cont) & mask, HUF_LUT_BITS + 1);  // the rarest symbols, or a window no code covers
+            return e;
         };
-        auto symbol = [&]() -> uint32_t {
-            uint32_t e = table[uint32_t(cont) & mask];
-            uint32_t nb = e >> 8;
-            if (nb > cnt) { err = ST_STREAM_UNDERRUN; nb = cnt; }  // decompress.rs:176-196
+        // one symbol with the reference's checks (decompress.rs:176-196)
+        auto one_symbol = [&]() -> uint32_t {
+            take_word();
+            uint32_t e = peek();
+            int32_t nb = int32_t(e >> 8);
+            if (nb > cnt) { err = ST_STREAM_UNDERRUN; nb = cnt; }
             cont >>= nb; cnt -= nb;
             return e;
         };
+        // Eight symbols in two halves.  After a refill the container holds more than 32 bits (unless the stream is
+        // at its end); four symbols take 44 bits at most and around ten on an exponent plane, so the halves run
+        // without a check per symbol: the lowest bit count seen is tested once, and a group that ran out of bits is
+        // decoded again one symbol at a time.
         auto dec8 = [&](uint32_t& s_lo, uint32_t& s_hi) {
             ring_top_up();
+            const uint64_t cont0 = cont;
+            const int32_t cnt0 = cnt;
+            const uintptr_t rp0 = rp;
+            int32_t lowest = 0;
             s_lo = 0; s_hi = 0;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                if ((j & 1) == 0) refill();
-                uint32_t e = symbol();
+                if ((j & 3) == 0) take_word();
+                uint32_t e = peek();
+                const uint32_t nb = e >> 8;
+                cont >>= nb; cnt -= int32_t(nb); lowest |= cnt;
                 const uint32_t ins = (0x3210u & ~(0xFu << (4 * (j & 3)))) | (4u << (4 * (j & 3)));  // low byte of e into byte j & 3
                 if (j < 4) s_lo = __byte_perm(s_lo, e, ins); else s_hi = __byte_perm(s_hi, e, ins);
+            }
+            if (lowest < 0) {
+                cont = cont0; cnt = cnt0; rp = rp0;
+                s_lo = 0; s_hi = 0;
+                for (uint32_t j = 0; j < 8; ++j) {
+                    uint32_t sym = one_symbol() & 0xFFu;
+                    if (j < 4) s_lo |= sym << (8 * j); else s_hi |= sym << (8 * (j - 4));
+                }
             }
         };
         auto short_group = [&](uint32_t g) {
             uint64_t syms = 0;
             ring_top_up();
-            for (uint32_t j = 0; j < g; ++j) {
-                take_word();
-                syms |= uint64_t(symbol() & 0xFFu) << (8 * j);
-            }
+            for (uint32_t j = 0; j < g; ++j) syms |= uint64_t(one_symbol() & 0xFFu) << (8 * j);
             emit(ep, pos, g, syms);
             pos += g; remaining -= g;
         };
