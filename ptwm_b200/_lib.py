@@ -16,7 +16,7 @@ _SOURCES = [os.path.join(_HERE, "csrc", f) for f in ("unity.cu", "ptwm_b200.cu",
                                                       "format.hpp", "host_common.hpp", "plan.h")] + [
     os.path.join(_HERE, "..", "include", "ptwm_b200.h")]
 
-NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared"]
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-Xcompiler", "-pthread", "-shared"]
 
 
 def build(force: bool = False, verbose: bool = False) -> str:

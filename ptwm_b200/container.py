@@ -262,6 +262,57 @@ class ContainerHandle:
         return [(self._infos[i]["name"], v) for i, v in zip(plan.indices, plan.views(out))]
 
 
+    def decode_model_streamed(self, names: Optional[Iterable[str]] = None, pieces: int = 8,
+                              indices: Optional[Sequence[int]] = None) -> list[tuple[str, torch.Tensor]]:
+        """decode_model for a container that is still in host memory (pinned,
+        for the copies to run asynchronously): the tensors are cut into
+        ``pieces`` contiguous runs of records; the bytes of run k+1 travel to
+        the GPU on a copy stream while run k is planned on the host and decoded
+        on the current stream, so only the first plan and the last decode are
+        not hidden behind the PCIe copy.  Nothing of the container stays
+        resident afterwards."""
+        from .sharding import contiguous_shards
+        if indices is None:
+            indices = list(range(len(self._infos))) if names is None else [self._idx(n) for n in names]
+        indices = sorted(int(i) for i in indices)
+        if not indices:
+            return []
+        dev = torch.device("cuda", self.device)
+        costs = [self._infos[i]["compressed"] for i in indices]
+        runs = [[indices[j] for j in r] for r in contiguous_shards(costs, max(1, min(pieces, len(indices)))) if len(r)]
+        compute = torch.cuda.current_stream(dev)
+        copier = torch.cuda.Stream(dev)
+        flags = self._flags()
+        # one buffer for the compressed bytes and one arena for the tensors; the pieces are slices of them
+        first = min(self._infos[i]["first_byte"] for i in indices)
+        last = max(self._infos[i]["end_byte"] for i in indices)
+        blob = torch.empty(max(last - first, 1), dtype=torch.uint8, device=dev)
+        arena_bytes = [sum((self._infos[i]["orig_size"] + 255) // 256 * 256 for i in run) for run in runs]
+        arena = torch.empty(max(sum(arena_bytes), 1), dtype=torch.uint8, device=dev)
+        copier.wait_stream(compute)  # the buffers may be recycled memory that earlier work on this stream still reads
+        jobs, result, at = [], [], 0
+        for run, nbytes in zip(runs, arena_bytes):
+            plan = DecodePlan(self, run)
+            lo, hi = plan.blob_span
+            if plan.out_bytes != nbytes or lo < first or hi > last:
+                raise PtwmError("internal: plan layout differs from the tensor infos")
+            with torch.cuda.stream(copier):
+                blob[lo - first:hi - first].copy_(self._host[lo:hi], non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(copier)
+            out = arena[at:at + nbytes]
+            at += nbytes
+            scratch = torch.empty(plan.scratch_bytes, dtype=torch.uint8, device=dev) if plan.scratch_bytes else None
+            compute.wait_event(arrived)
+            plan.run(blob[lo - first:hi - first], out, scratch, blob_first=lo, flags=flags | NO_SYNC)
+            jobs.append((plan, out, scratch))
+        for plan, out, scratch in jobs:
+            plan.finish(self.device, flags)
+            result.extend((self._infos[i]["name"], v) for i, v in zip(plan.indices, plan.views(out)))
+        blob.record_stream(copier)
+        return result
+
+
 class Decompressor:
     """Stateless decompressor; ``decompress`` returns a CUDA tensor."""
 

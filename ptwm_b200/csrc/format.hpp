@@ -6,10 +6,14 @@
 // the device copy of the same bytes.  Paths in comments are relative to
 // crates/ptwm-core/src of the reference.
 #pragma once
+#include <algorithm>
+#include <atomic>
 #include <cstdint>
 #include <cstring>
+#include <mutex>
 #include <stdexcept>
 #include <string>
+#include <thread>
 #include <unordered_set>
 #include <vector>
 
@@ -349,6 +353,7 @@ class FileReader {
     std::vector<detail::TableEntry> table_;
     std::vector<detail::RawChain> registry_;
     ParsedFile out_;
+    std::mutex shared_mu_;
 
     void make_chunks(PlaneDesc& p, bool chunked, const std::vector<std::pair<uint32_t, uint32_t>>& entries, uint64_t inline_off, uint64_t inline_len,
                      uint8_t state_version, uint16_t state_info) {
@@ -380,7 +385,10 @@ class FileReader {
                 if (!e) throw FormatError("shared state not in prelude");
                 if (state_version != e->version) throw FormatError("plane state_version does not match the prelude entry");
                 if (p.role >= 1 && p.role <= 8 && !(e->mask & (1u << (p.role - 1)))) throw FormatError("shared state applies_to_mask does not cover the plane role");
-                if (!e->checked) { if (xxh64_host(b_ + e->off, e->len) != e->hash) throw FormatError("shared state xxhash64 mismatch"); e->checked = true; }
+                {
+                    std::lock_guard<std::mutex> g(shared_mu_);  // records are read by several threads
+                    if (!e->checked) { if (xxh64_host(b_ + e->off, e->len) != e->hash) throw FormatError("shared state xxhash64 mismatch"); e->checked = true; }
+                }
                 ch.state_off = e->off; ch.state_len = e->len; ch.state_version = e->version;
             } else if (p.state_source == 3) throw FormatError("External state not supported");
             detail::classify_chunk(b_, p.codec, ch);
@@ -526,6 +534,8 @@ class FileReader {
         if (count > (footer - index_start) / 3) ir.bad("entry count exceeds the index bytes");
         size_t off = p3;
         std::unordered_set<std::string> names;
+        struct Rec { std::string name; size_t off, len; };
+        std::vector<Rec> recs;
         for (uint64_t i = 0; i < count; ++i) {
             size_t nl = size_t(ir.var_max(65535, "name length"));
             if (!nl) ir.bad("empty tensor name");
@@ -534,13 +544,37 @@ class FileReader {
             uint64_t rl = ir.var();
             if (rl < 3) ir.bad("record too short");
             if (rl > index_start - off) ir.bad("record runs past the body");
-            TensorDesc t;
-            try { t = read_record(off, off + size_t(rl)); }
-            catch (const FormatError& e) { if (!e.unsupported) throw; t = TensorDesc{}; t.unsupported = e.what(); }
-            t.name = name;
-            out_.tensors.push_back(std::move(t));
+            recs.push_back(Rec{std::move(name), off, size_t(rl)});
             off += size_t(rl);
         }
+        // Reading a record touches every chunk header of its planes, scattered over the whole file: for a large
+        // container that is a hundred thousand cache misses, so the records are read by several threads.  The
+        // first failing record (in index order) is the one reported, as if they had been read in turn.
+        out_.tensors.resize(recs.size());
+        std::vector<std::string> failed(recs.size());
+        std::vector<uint8_t> has_failed(recs.size(), 0);
+        auto read_one = [&](size_t i) {
+            TensorDesc t;
+            try { t = read_record(recs[i].off, recs[i].off + recs[i].len); }
+            catch (const FormatError& e) {
+                if (!e.unsupported) { failed[i] = e.what(); has_failed[i] = 1; return; }
+                t = TensorDesc{}; t.unsupported = e.what();
+            }
+            t.name = recs[i].name;
+            out_.tensors[i] = std::move(t);
+        };
+        size_t workers = std::thread::hardware_concurrency();
+        workers = std::min<size_t>(std::min<size_t>(workers ? workers : 1, 16), recs.size() / 4);
+        if (n_ < (size_t(64) << 20) || workers < 2) {
+            for (size_t i = 0; i < recs.size(); ++i) { read_one(i); if (has_failed[i]) break; }
+        } else {
+            std::atomic<size_t> next{0};
+            std::vector<std::thread> pool;
+            for (size_t w = 0; w < workers; ++w)
+                pool.emplace_back([&] { for (size_t i = next.fetch_add(1); i < recs.size(); i = next.fetch_add(1)) read_one(i); });
+            for (auto& th : pool) th.join();
+        }
+        for (size_t i = 0; i < recs.size(); ++i) if (has_failed[i]) throw FormatError(failed[i]);
         ir.done("the last index entry");
         if (off != index_start) throw FormatError("compact container: records do not cover the body");
         return std::move(out_);

@@ -118,6 +118,12 @@ def check_container(blob: bytes, expected: dict, verify=True):
         if g != raw:
             first = next(i for i in range(len(raw)) if g[i] != raw[i])
             raise AssertionError(f"{name}: first mismatch at byte {first} of {len(raw)}")
+    # the streamed form (host copy, pieces decoded while later bytes are still being copied) gives the same tensors
+    for pieces in (1, 3):
+        streamed = dict(h.decode_model_streamed(pieces=pieces))
+        assert list(streamed) == list(expected)
+        for name, raw in expected.items():
+            assert bytes_of(streamed[name]) == raw, (name, pieces)
     return h, got
 
 
