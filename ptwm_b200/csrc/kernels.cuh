@@ -427,8 +427,11 @@ __device__ __forceinline__ uint32_t ring_byte(const uint32_t* rw, uint32_t q) {
 }
 // The eight ring bytes from q on, big-endian: byte q is the top byte of `wh`.
 __device__ __forceinline__ void ring_window_be(const uint32_t* rw, uint32_t q, uint32_t& wh, uint32_t& wl) {
-    uint32_t k = q >> 2;
-    uint32_t w0 = rw[(k & 15u) << 5], w1 = rw[((k + 1) & 15u) << 5], w2 = rw[((k + 2) & 15u) << 5];
+    const uint8_t* rb = reinterpret_cast<const uint8_t*>(rw);
+    const uint32_t t = q << 5;  // word k of the ring sits at byte (k & 15) * 128 of the lane's column
+    uint32_t w0 = *reinterpret_cast<const uint32_t*>(rb + (t & 0x780u));
+    uint32_t w1 = *reinterpret_cast<const uint32_t*>(rb + ((t + 0x80u) & 0x780u));
+    uint32_t w2 = *reinterpret_cast<const uint32_t*>(rb + ((t + 0x100u) & 0x780u));
     uint32_t sel = 0x0123u + 0x1111u * (q & 3u);
     wh = __byte_perm(w0, w1, sel);
     wl = __byte_perm(w1, w2, sel);
@@ -440,7 +443,7 @@ template <int LS>
 __device__ __forceinline__ uint32_t rans_lookup(const uint32_t* tab, const uint32_t* lst, uint32_t& x) {
     uint32_t idx = x & 2047u;
     uint32_t w = tab[idx >> 4];
-    uint32_t k = (w >> 16) + __popc((w << 16) << (~idx & 15u));  // boundaries at or below the slot
+    uint32_t k = (w >> 16) + __popc(w << ((~idx & 15u) | 16u));  // boundaries at or below the slot: the count above the bitmap, the bitmap's bits up to the slot
     uint32_t e = lst[k * LS];
     x = ((e >> 8) & 0xFFFu) * (x >> 11) + (idx - (e >> 20));
     return e;
