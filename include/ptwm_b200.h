@@ -57,7 +57,11 @@ int64_t ptwm_hardware_backend_v1_dispatch_decode_cuda(uint8_t state_format_versi
                                                       uint64_t out_dev_ptr, size_t out_len, uint32_t device_ordinal);
 
 /* kind = "plane_codec".  Replace PlaneCodecCudaStreamHandleFn / PlaneCodecCudaDecodeFn /
- * PlaneCodecCudaEncodeFn (native.rs:150,163-174,185-197). */
+ * PlaneCodecCudaEncodeFn (native.rs:150,163-174,185-197).  encode_cuda turns one plane in
+ * device memory into its payload (identity: the bytes; huffman / rans: TAG|len|blob with the
+ * reference's raw fallback, byte for byte what codecs/huffman.rs:37-88 and codecs/rans.rs:38-95
+ * produce); tans and order1_scale_ac answer PTWM_RC_UNSUPPORTED.  *needed_out receives the
+ * payload size, also when out_cap is too small (PTWM_RC_BUFFER_TOO_SMALL). */
 uint64_t ptwm_plane_codec_v1_cuda_stream_handle(uint32_t device_ordinal);
 int64_t ptwm_plane_codec_v1_decode_cuda(uint8_t state_format_version, const uint8_t* state_ptr, size_t state_len, const uint8_t* codec_id_ptr,
                                         size_t codec_id_len, uint64_t in_dev_ptr, size_t in_len, uint64_t out_dev_ptr, size_t out_cap,

@@ -38,8 +38,9 @@ struct EncResult {       // per chunk, read back by the host
 struct GatherItem {
     uint64_t dst;        // absolute offset of the chunk frame in the container
     uint32_t chunk;
-    uint32_t mode;       // 0 identity (bare bytes), 1 raw-tagged, 2 rANS, 3 Huffman
+    uint32_t mode;       // 0 identity (bare bytes), 1 raw-tagged, 2 rANS, 3 Huffman; + GATHER_BARE: the payload alone, no chunk frame header
 };
+constexpr uint32_t GATHER_BARE = 0x100;
 
 // layout of the 1 KiB table area per chunk
 //   rANS:    freqs u16[256] | cum u16[256]
@@ -187,10 +188,13 @@ __global__ void __launch_bounds__(128) gather_kernel(const GatherItem* __restric
     const EncResult r = results[g.chunk];
     uint8_t* d = out + g.dst;
     const uint32_t t = threadIdx.x;
-    if (t < 5) d[t] = 0;
-    d += 5;
-    if (g.mode <= 1) {
-        if (g.mode == 1) { if (t == 0) d[0] = 0; d += 1; }
+    const uint32_t mode = g.mode & 0xFFu;
+    if (!(g.mode & GATHER_BARE)) {
+        if (t < 5) d[t] = 0;
+        d += 5;
+    }
+    if (mode <= 1) {
+        if (mode == 1) { if (t == 0) d[0] = 0; d += 1; }
         const uint8_t* p = planes + c.plane_off;
         for (uint32_t i = t; i < c.n; i += blockDim.x) d[i] = p[i];
         return;
@@ -199,7 +203,7 @@ __global__ void __launch_bounds__(128) gather_kernel(const GatherItem* __restric
     d += 5;
     const uint8_t* tab = tables + uint64_t(g.chunk) * ENC_TABLE_BYTES;
     uint32_t hdr;
-    if (g.mode == 2) {
+    if (mode == 2) {
         const uint16_t* freqs = reinterpret_cast<const uint16_t*>(tab);
         hdr = 1 + 2 * (r.hdr_n + 1);
         if (t == 0) d[0] = uint8_t(r.hdr_n);

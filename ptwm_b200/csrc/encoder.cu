@@ -435,6 +435,78 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
 
 }  // namespace
 
+// One plane into one payload, device to device: the body of ptwm_plane_codec_v1_encode_cuda.
+// Identity copies; Huffman and rANS run the container encoder's kernels on a single chunk that spans the
+// plane and keep the reference's rules for falling back to the raw-tagged form (codecs/huffman.rs:37-88,
+// codecs/rans.rs:38-95).  `needed` receives the payload size, also when `out_cap` is too small (-2).
+int64_t ptwm::encode_plane_cuda(int codec, uint64_t in_dev, size_t n, uint64_t out_dev, size_t out_cap, uint64_t* needed, cudaStream_t st) {
+    auto need = [&](uint64_t v) { if (needed) *needed = v; return v; };
+    uint8_t* out = reinterpret_cast<uint8_t*>(uintptr_t(out_dev));
+    const uint8_t* in = reinterpret_cast<const uint8_t*>(uintptr_t(in_dev));
+    if (codec == C_IDENTITY) {
+        if (need(n) > out_cap) return fail(PTWM_RC_BUFFER_TOO_SMALL, "output buffer too small");
+        if (n) CUDA_TRY(cudaMemcpyAsync(out, in, n, cudaMemcpyDeviceToDevice, st));
+        CUDA_TRY(cudaStreamSynchronize(st));
+        return int64_t(n);
+    }
+    if (codec != C_HUFFMAN && codec != C_RANS) return fail(PTWM_RC_UNSUPPORTED, "device encode covers identity, huffman and rans");
+    if (n == 0) {  // an empty plane is the raw tag alone
+        if (need(1) > out_cap) return fail(PTWM_RC_BUFFER_TOO_SMALL, "output buffer too small");
+        CUDA_TRY(cudaMemsetAsync(out, 0, 1, st));
+        CUDA_TRY(cudaStreamSynchronize(st));
+        return 1;
+    }
+    uint32_t mode = 1;
+    uint64_t size = 1 + uint64_t(n);
+    DeviceBuf d_chunk, d_codec, d_hist, d_phist, d_tables, d_results, d_slots, d_gather;
+    EncChunk chunk{0, 0, 0, 0, 0, 0};
+    if (n <= 0xFFFFFFFFull) {  // the length prefix is a u32; longer planes stay raw
+        const uint64_t slot_cap = ((n / 4 + 1) * 11 + 7) / 8 + 64;  // a symbol takes at most 11 bits in either codec
+        if (slot_cap > 0xFFFFFFFFull) return fail(PTWM_RC_UNSUPPORTED, "plane too long for the device encoder");
+        chunk.n = uint32_t(n); chunk.slot_cap = uint32_t(slot_cap);
+        const uint8_t codec_byte = uint8_t(codec);
+        CUDA_TRY(d_chunk.alloc(sizeof(EncChunk)));
+        CUDA_TRY(d_codec.alloc(1));
+        CUDA_TRY(d_hist.alloc(256 * sizeof(uint32_t)));
+        CUDA_TRY(d_phist.alloc(256 * sizeof(unsigned long long)));
+        CUDA_TRY(d_tables.alloc(ENC_TABLE_BYTES));
+        CUDA_TRY(d_results.alloc(sizeof(EncResult)));
+        CUDA_TRY(d_slots.alloc(4 * slot_cap));
+        CUDA_TRY(cudaMemcpyAsync(d_chunk.p, &chunk, sizeof(chunk), cudaMemcpyHostToDevice, st));
+        CUDA_TRY(cudaMemcpyAsync(d_codec.p, &codec_byte, 1, cudaMemcpyHostToDevice, st));
+        CUDA_TRY(cudaMemsetAsync(d_phist.p, 0, 256 * sizeof(unsigned long long), st));
+        hist_kernel<<<1, 128, 0, st>>>(d_chunk.as<EncChunk>(), in, d_hist.as<uint32_t>(), d_phist.as<unsigned long long>());
+        table_kernel<<<1, 64, 0, st>>>(d_chunk.as<EncChunk>(), 1, d_codec.as<uint8_t>(), d_hist.as<uint32_t>(), d_tables.as<uint8_t>(), d_results.as<EncResult>());
+        encode_kernel<<<1, 128, 0, st>>>(d_chunk.as<EncChunk>(), 1, d_codec.as<uint8_t>(), in, d_tables.as<uint8_t>(), d_slots.as<uint8_t>(), d_results.as<EncResult>());
+        CUDA_TRY(cudaGetLastError());
+        EncResult r;
+        CUDA_TRY(cudaMemcpyAsync(&r, d_results.p, sizeof(r), cudaMemcpyDeviceToHost, st));
+        CUDA_TRY(cudaStreamSynchronize(st));
+        const uint64_t hdr = codec == C_RANS ? 1 + 2 * (uint64_t(r.hdr_n) + 1) : (r.hdr_n <= 127 ? 1 : 2) + (uint64_t(r.hdr_n) + 1) / 2;
+        const uint64_t blob = hdr + 16 + uint64_t(r.stream_len[0]) + r.stream_len[1] + r.stream_len[2] + r.stream_len[3];
+        const bool coded = r.coded && blob < n && (codec != C_RANS || n <= (1ull << 30) || n <= blob * 64);
+        if (coded) { mode = codec == C_RANS ? 2 : 3; size = 1 + 4 + blob; }
+    } else {
+        CUDA_TRY(d_chunk.alloc(sizeof(EncChunk)));
+        CUDA_TRY(d_results.alloc(sizeof(EncResult)));
+        CUDA_TRY(d_tables.alloc(ENC_TABLE_BYTES));
+        CUDA_TRY(d_slots.alloc(16));
+    }
+    if (need(size) > out_cap) return fail(PTWM_RC_BUFFER_TOO_SMALL, "output buffer too small");
+    if (mode == 1 && n > 0xFFFFFFFFull) {  // raw: tag byte, then the plane
+        CUDA_TRY(cudaMemsetAsync(out, 0, 1, st));
+        CUDA_TRY(cudaMemcpyAsync(out + 1, in, n, cudaMemcpyDeviceToDevice, st));
+    } else {
+        const GatherItem g{0, 0, mode | GATHER_BARE};
+        CUDA_TRY(d_gather.alloc(sizeof(g)));
+        CUDA_TRY(cudaMemcpyAsync(d_gather.p, &g, sizeof(g), cudaMemcpyHostToDevice, st));
+        gather_kernel<<<1, 128, 0, st>>>(d_gather.as<GatherItem>(), d_chunk.as<EncChunk>(), d_results.as<EncResult>(), in, d_tables.as<uint8_t>(), d_slots.as<uint8_t>(), out);
+        CUDA_TRY(cudaGetLastError());
+    }
+    CUDA_TRY(cudaStreamSynchronize(st));
+    return int64_t(size);
+}
+
 extern "C" {
 
 int64_t ptwm_b200_encode_model(const ptwm_b200_encode_tensor* tensors, size_t n, const ptwm_b200_encode_options* options, uint32_t device_ordinal, uint64_t stream,

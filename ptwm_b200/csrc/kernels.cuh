@@ -417,7 +417,11 @@ constexpr uint32_t RANS_NARROW_SYMBOLS = 38;
 constexpr int RANS_RANK_BYTES = 512;
 __host__ __device__ inline uint32_t rans_l_entries(uint32_t max_sym) { return (max_sym + 3 + 3) & ~3u; }
 __host__ __device__ inline uint32_t rans_smem_bytes(uint32_t l_entries, bool per_lane = false) {
+#ifdef PTWM_RANS_SMEM_PAD
+    return RANS_WARP_CHUNKS * RANS_RANK_BYTES + (per_lane ? 128 * l_entries : RANS_WARP_CHUNKS * 4 * l_entries) + RING_SMEM + PTWM_RANS_SMEM_PAD;
+#else
     return RANS_WARP_CHUNKS * RANS_RANK_BYTES + (per_lane ? 128 * l_entries : RANS_WARP_CHUNKS * 4 * l_entries) + RING_SMEM;
+#endif
 }
 
 // Ring addressing: byte q of a lane's ring lives in word (q >> 2) & 15 of the
@@ -478,7 +482,11 @@ __device__ __forceinline__ void rans_group8(const uint32_t* tab, const uint32_t*
         const uint32_t ins = (0x3210u & ~(0xFu << (4 * (j & 3)))) | (4u << (4 * (j & 3)));  // low byte of e into byte j & 3
         if (j < 4) s_lo = __byte_perm(s_lo, e, ins); else s_hi = __byte_perm(s_hi, e, ins);
         // bytes until x >= 2^23, at most three: 0 for clz <= 8, 1 for 9..16, 2 for 17..24, 3 above
+#ifdef PTWM_RANS_NOCLZ
+        uint32_t sh = (x < (1u << 23) ? 8u : 0u) + (x < (1u << 15) ? 8u : 0u) + (x < (1u << 7) ? 8u : 0u);
+#else
         uint32_t sh = uint32_t(max(int(__clz(x)) - 1, 0)) & 0x18u;
+#endif
         x = __funnelshift_l(wh, x, sh);
         wh = __funnelshift_l(wl, wh, sh);
         wl <<= sh;
@@ -492,8 +500,11 @@ __device__ __forceinline__ void rans_group8(const uint32_t* tab, const uint32_t*
     }
 }
 
+#ifndef PTWM_RANS_MINBLOCKS
+#define PTWM_RANS_MINBLOCKS 24
+#endif
 template <bool PER_LANE>
-__global__ void __launch_bounds__(32, 24) rans_decode_kernel_t(const DecodeItem* __restrict__ items, uint32_t n_items, Bases bases, uint32_t* __restrict__ status,
+__global__ void __launch_bounds__(32, PTWM_RANS_MINBLOCKS) rans_decode_kernel_t(const DecodeItem* __restrict__ items, uint32_t n_items, Bases bases, uint32_t* __restrict__ status,
                                                            uint32_t l_entries) {
     constexpr int LS = PER_LANE ? 32 : 1;
     extern __shared__ __align__(16) uint8_t smem[];
@@ -517,7 +528,7 @@ __global__ void __launch_bounds__(32, 24) rans_decode_kernel_t(const DecodeItem*
         else {
             max_sym = src[0];
             hdr = 1 + 2 * (max_sym + 1);
-            if (it.src_len < hdr + 16 || (!PER_LANE && max_sym + 3 > l_entries)) err = ST_BAD_HEADER;
+            if (it.src_len < hdr + 16) err = ST_BAD_HEADER;
             else {
                 uint64_t total = 0;
                 uint32_t off = hdr + 16;
@@ -556,7 +567,7 @@ __global__ void __launch_bounds__(32, 24) rans_decode_kernel_t(const DecodeItem*
         }
         uint32_t total = __shfl_sync(0xFFFFFFFFu, incl, 31), distinct = __shfl_sync(0xFFFFFFFFu, rincl, 31);
         bool bad = total != 2048;  // decompress.rs:49-55
-        if (PER_LANE && distinct + 2 > l_entries) bad = true;  // the host only sends chunks that fit; a blob that differs from the planned one may not
+        if (distinct + 2 > l_entries) bad = true;  // the host sizes the list from the planned bytes; a blob that differs from them may not fit
         if (bad) { if (c == c2) err = ST_BAD_HEADER; continue; }
         uint32_t start = incl - sum, rank = rincl - present;
         uint32_t* tab = ranktab + c2 * 128;

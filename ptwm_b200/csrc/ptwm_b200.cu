@@ -115,7 +115,7 @@ struct ptwm_b200_plan {
     // per launch slot: 0-3 phase-0 decoders (rANS, Huffman, tANS, O1SAC), 4 scratch copies, 5-8 phase-1 decoders, 9 final merge, 10 CRC, 11 XXH64
     // rANS chunks per phase: the first `rans_narrow` items hold few distinct symbols and go to the kernel with a symbol
     // list per lane (`rans_rows` rows); the rest go to the general kernel, sized by the largest alphabet bound among them.
-    uint32_t rans_max_sym[2] = {0, 0}, rans_narrow[2] = {0, 0}, rans_rows[2] = {0, 0};
+    uint32_t rans_wide_distinct[2] = {0, 0}, rans_narrow[2] = {0, 0}, rans_rows[2] = {0, 0};
     uint64_t slot_bytes[12] = {0};
     uint32_t slot_items[12] = {0};
     std::mutex mu;
@@ -238,7 +238,11 @@ void finish_lists(ptwm_b200_plan& pl) {
     for (int ph = 0; ph < 2; ++ph) {
         for (int cc = 0; cc < 4; ++cc) {
             auto& v = pl.dec[ph][cc];
+#ifdef PTWM_RANS_ALL_SHARED
+            auto narrow = [cc](const DecodeItem&) { return false; };
+#else
             auto narrow = [cc](const DecodeItem& a) { return cc == 0 && (a.row_len >> 16) <= RANS_NARROW_SYMBOLS; };
+#endif
             std::stable_sort(v.begin(), v.end(), [&](const DecodeItem& a, const DecodeItem& b) {
                 bool na = narrow(a), nb = narrow(b);
                 return na != nb ? na : a.n > b.n;
@@ -250,7 +254,7 @@ void finish_lists(ptwm_b200_plan& pl) {
                 uint32_t most = 0;
                 for (auto& it : v) {
                     if (narrow(it)) { pl.rans_narrow[ph]++; most = std::max(most, it.row_len >> 16); }
-                    else pl.rans_max_sym[ph] = std::max(pl.rans_max_sym[ph], it.row_len & 0xFFu);
+                    else pl.rans_wide_distinct[ph] = std::max(pl.rans_wide_distinct[ph], it.row_len >> 16);  // most distinct symbols among the rest
                 }
                 pl.rans_rows[ph] = most + 2;
                 if (pl.rans_narrow[ph] && pl.rans_narrow[ph] < v.size()) pl.launches++;
@@ -324,7 +328,7 @@ int64_t enqueue(ptwm_b200_plan& pl, DevicePlan& d, const Bases& bases, uint32_t 
                         CUDA_TRY(cudaGetLastError());
                     }
                     if (nw) {
-                        const uint32_t le = rans_l_entries(pl.rans_max_sym[ph]);
+                        const uint32_t le = (pl.rans_wide_distinct[ph] + 2 + 3) & ~3u;
                         rans_decode_kernel_t<false><<<(nw + RANS_WARP_CHUNKS - 1) / RANS_WARP_CHUNKS, 32, rans_smem_bytes(le), st>>>(it + nn, nw, bases, status, le);
                     }
                     break;
@@ -520,11 +524,43 @@ int64_t ptwm_plane_codec_v1_decode_cuda(uint8_t sfv, const uint8_t* state_ptr, s
                                         uint64_t in_dev_ptr, size_t in_len, uint64_t out_dev_ptr, size_t out_cap, uint32_t device_ordinal) {
     return decode_plane_cuda(sfv, state_ptr, state_len, codec_id_ptr, codec_id_len, in_dev_ptr, in_len, out_dev_ptr, out_cap, device_ordinal);
 }
-int64_t ptwm_plane_codec_v1_encode_cuda(uint8_t, const uint8_t*, size_t, const uint8_t*, size_t, uint64_t, size_t, uint64_t, size_t, uint64_t* needed_out, uint32_t) {
+int64_t ptwm_plane_codec_v1_encode_cuda(uint8_t, const uint8_t*, size_t, const uint8_t* codec_id, size_t codec_id_len, uint64_t in_dev, size_t in_len, uint64_t out_dev,
+                                        size_t out_cap, uint64_t* needed_out, uint32_t device_ordinal) {
     if (needed_out) *needed_out = 0;
-    return fail(PTWM_RC_UNSUPPORTED, "device encode is not built yet");
+    if (!codec_id || codec_id_len != 32) return fail(PTWM_RC_INVALID_INPUT, "codec_id must be a 32-byte canonical id");
+    int codec = -1;
+    for (const BuiltinId& b : kBuiltins) if (!std::memcmp(b.id, codec_id, 32)) codec = b.codec;
+    if (codec < 0) return fail(PTWM_RC_UNSUPPORTED, "codec id is not one of identity, huffman, rans, tans, order1_scale_ac");
+    if ((in_len && !in_dev) || (out_cap && !out_dev)) return fail(PTWM_RC_INVALID_INPUT, "null device pointer");
+    DeviceGuard guard{int(device_ordinal)};
+    if (guard.err != cudaSuccess) return fail(PTWM_RC_CUDA, std::string("cudaSetDevice: ") + cudaGetErrorString(guard.err));
+    DeviceState* ds;
+    int64_t rc = device_state(int(device_ordinal), &ds);
+    if (rc < 0) return rc;
+    return encode_plane_cuda(codec, in_dev, in_len, out_dev, out_cap, needed_out, ds->stream);
 }
-int64_t ptwm_plane_codec_v1_encode(const uint8_t*, size_t, uint8_t*, size_t) { return fail(PTWM_RC_UNSUPPORTED, "device encode is not built yet"); }
+// Host buffers, rANS (the codec this bundle registers as its plane codec): the payload is built on GPU 0.
+int64_t ptwm_plane_codec_v1_encode(const uint8_t* in, size_t in_len, uint8_t* out, size_t out_len) {
+    if ((in_len && !in) || (out_len && !out)) return fail(PTWM_RC_INVALID_INPUT, "null buffer");
+    DeviceGuard guard{0};
+    if (guard.err != cudaSuccess) return fail(PTWM_RC_MISSING_CAPABILITY, "no CUDA device");
+    DeviceState* ds;
+    int64_t rc = device_state(0, &ds);
+    if (rc < 0) return rc;
+    const size_t cap = in_len + 16;
+    uint8_t *d_in = nullptr, *d_out = nullptr;
+    CUDA_TRY(cudaMalloc(&d_in, in_len ? in_len : 1));
+    struct Free { uint8_t* p; ~Free() { cudaFree(p); } } f1{d_in};
+    CUDA_TRY(cudaMalloc(&d_out, cap));
+    Free f2{d_out};
+    CUDA_TRY(cudaMemcpy(d_in, in, in_len, cudaMemcpyHostToDevice));
+    uint64_t needed = 0;
+    int64_t n = encode_plane_cuda(C_RANS, uint64_t(reinterpret_cast<uintptr_t>(d_in)), in_len, uint64_t(reinterpret_cast<uintptr_t>(d_out)), cap, &needed, ds->stream);
+    if (n < 0) return n;
+    if (size_t(n) > out_len) return fail(PTWM_RC_BUFFER_TOO_SMALL, "output buffer too small");
+    CUDA_TRY(cudaMemcpy(out, d_out, size_t(n), cudaMemcpyDeviceToHost));
+    return n;
+}
 
 int64_t ptwm_plane_codec_v1_decode_stateful(uint8_t sv, const uint8_t* state, size_t state_len, const uint8_t* in, size_t in_len, uint8_t* out, size_t out_cap) {
     if ((in_len && !in) || (out_cap && !out)) return fail(PTWM_RC_INVALID_INPUT, "null buffer");

@@ -68,3 +68,53 @@ def test_encode_rejects_host_tensors_and_unknown_codec():
         compress_model({"a": torch.zeros(4, device="cuda")}, CompressionConfig(codec_menu=(7,)))
     with pytest.raises(ptwm_b200.PtwmError):
         compress_model({"a": torch.zeros(4, device="cuda")}, CompressionConfig(forced_codec=7))
+
+
+# ---- one plane through the reference's plane_codec ABI -------------------------------------
+from test_gpu_decode import IDS, plane_cases  # noqa: E402  (canonical ids and the plane inputs of the decode tests)
+from ptwm_b200 import _lib  # noqa: E402
+
+
+def encode_cuda(codec, plane: bytes, cap=None):
+    L = _lib.lib()
+    src = torch.frombuffer(bytearray(plane or b"\0"), dtype=torch.uint8).cuda()
+    cap = len(plane) + 16 if cap is None else cap
+    out = torch.zeros(max(cap, 1), dtype=torch.uint8, device="cuda")
+    needed = _lib.C.c_uint64(0)
+    rc = L.ptwm_plane_codec_v1_encode_cuda(1, None, 0, bytes.fromhex(IDS[codec]), 32, src.data_ptr() if plane else 0, len(plane), out.data_ptr(), cap,
+                                           _lib.C.byref(needed), 0)
+    return rc, needed.value, bytes(out[:max(rc, 0)].cpu().numpy().tobytes())
+
+
+@pytest.mark.parametrize("codec", [oracle.IDENTITY, oracle.HUFFMAN, oracle.RANS])
+def test_plane_encode_cuda_matches_oracle(codec):
+    coded = 0
+    for name, plane in plane_cases():
+        if len(plane) > (1 << 20):
+            continue
+        expect = oracle.plane_encode(codec, plane)[2]
+        rc, needed, got = encode_cuda(codec, plane)
+        assert rc == len(expect) == needed, (name, rc, len(expect), needed)
+        assert got == expect, name
+        coded += codec != oracle.IDENTITY and got[:1] == b"\x01"
+    if codec != oracle.IDENTITY:
+        assert coded >= 5
+
+
+def test_plane_encode_cuda_reports_the_size_it_needs():
+    plane = bytes(range(256)) * 64
+    rc, needed, _ = encode_cuda(oracle.RANS, plane, cap=8)
+    assert rc == -2 and needed == len(oracle.plane_encode(oracle.RANS, plane)[2])
+    rc, _, _ = encode_cuda(oracle.TANS, plane)
+    assert rc == -5
+
+
+def test_host_buffer_encode_round_trips_through_host_decode():
+    L = _lib.lib()
+    plane = np.random.default_rng(3).normal(0, 3, 50000).astype(np.int8).tobytes()
+    out = _lib.C.create_string_buffer(len(plane) + 16)
+    n = L.ptwm_plane_codec_v1_encode(plane, len(plane), out, len(plane) + 16)
+    assert n > 0 and out.raw[:n] == oracle.plane_encode(oracle.RANS, plane)[2]
+    back = _lib.C.create_string_buffer(len(plane))
+    m = L.ptwm_plane_codec_v1_decode(out.raw[:n], n, back, len(plane))
+    assert m == len(plane) and back.raw == plane
