@@ -417,11 +417,7 @@ constexpr uint32_t RANS_NARROW_SYMBOLS = 38;
 constexpr int RANS_RANK_BYTES = 512;
 __host__ __device__ inline uint32_t rans_l_entries(uint32_t max_sym) { return (max_sym + 3 + 3) & ~3u; }
 __host__ __device__ inline uint32_t rans_smem_bytes(uint32_t l_entries, bool per_lane = false) {
-#ifdef PTWM_RANS_SMEM_PAD
-    return RANS_WARP_CHUNKS * RANS_RANK_BYTES + (per_lane ? 128 * l_entries : RANS_WARP_CHUNKS * 4 * l_entries) + RING_SMEM + PTWM_RANS_SMEM_PAD;
-#else
     return RANS_WARP_CHUNKS * RANS_RANK_BYTES + (per_lane ? 128 * l_entries : RANS_WARP_CHUNKS * 4 * l_entries) + RING_SMEM;
-#endif
 }
 
 // Ring addressing: byte q of a lane's ring lives in word (q >> 2) & 15 of the
@@ -482,11 +478,7 @@ __device__ __forceinline__ void rans_group8(const uint32_t* tab, const uint32_t*
         const uint32_t ins = (0x3210u & ~(0xFu << (4 * (j & 3)))) | (4u << (4 * (j & 3)));  // low byte of e into byte j & 3
         if (j < 4) s_lo = __byte_perm(s_lo, e, ins); else s_hi = __byte_perm(s_hi, e, ins);
         // bytes until x >= 2^23, at most three: 0 for clz <= 8, 1 for 9..16, 2 for 17..24, 3 above
-#ifdef PTWM_RANS_NOCLZ
-        uint32_t sh = (x < (1u << 23) ? 8u : 0u) + (x < (1u << 15) ? 8u : 0u) + (x < (1u << 7) ? 8u : 0u);
-#else
         uint32_t sh = uint32_t(max(int(__clz(x)) - 1, 0)) & 0x18u;
-#endif
         x = __funnelshift_l(wh, x, sh);
         wh = __funnelshift_l(wl, wh, sh);
         wl <<= sh;
@@ -500,11 +492,10 @@ __device__ __forceinline__ void rans_group8(const uint32_t* tab, const uint32_t*
     }
 }
 
-#ifndef PTWM_RANS_MINBLOCKS
-#define PTWM_RANS_MINBLOCKS 24
-#endif
+// 24 blocks per SM keeps the kernel at 80 registers: more blocks than that gave nothing (the load/store pipe, the
+// integer pipe and the issue slots are each about 55-60 % busy at 22), fewer registers spill.
 template <bool PER_LANE>
-__global__ void __launch_bounds__(32, PTWM_RANS_MINBLOCKS) rans_decode_kernel_t(const DecodeItem* __restrict__ items, uint32_t n_items, Bases bases, uint32_t* __restrict__ status,
+__global__ void __launch_bounds__(32, 24) rans_decode_kernel_t(const DecodeItem* __restrict__ items, uint32_t n_items, Bases bases, uint32_t* __restrict__ status,
                                                            uint32_t l_entries) {
     constexpr int LS = PER_LANE ? 32 : 1;
     extern __shared__ __align__(16) uint8_t smem[];

@@ -114,7 +114,7 @@ struct ptwm_b200_plan {
     uint32_t launches = 0;
     // per launch slot: 0-3 phase-0 decoders (rANS, Huffman, tANS, O1SAC), 4 scratch copies, 5-8 phase-1 decoders, 9 final merge, 10 CRC, 11 XXH64
     // rANS chunks per phase: the first `rans_narrow` items hold few distinct symbols and go to the kernel with a symbol
-    // list per lane (`rans_rows` rows); the rest go to the general kernel, sized by the largest alphabet bound among them.
+    // list per lane (`rans_rows` rows); the rest go to the general kernel, whose shared list is sized by the most distinct symbols among them.
     uint32_t rans_wide_distinct[2] = {0, 0}, rans_narrow[2] = {0, 0}, rans_rows[2] = {0, 0};
     uint64_t slot_bytes[12] = {0};
     uint32_t slot_items[12] = {0};
@@ -238,11 +238,7 @@ void finish_lists(ptwm_b200_plan& pl) {
     for (int ph = 0; ph < 2; ++ph) {
         for (int cc = 0; cc < 4; ++cc) {
             auto& v = pl.dec[ph][cc];
-#ifdef PTWM_RANS_ALL_SHARED
-            auto narrow = [cc](const DecodeItem&) { return false; };
-#else
             auto narrow = [cc](const DecodeItem& a) { return cc == 0 && (a.row_len >> 16) <= RANS_NARROW_SYMBOLS; };
-#endif
             std::stable_sort(v.begin(), v.end(), [&](const DecodeItem& a, const DecodeItem& b) {
                 bool na = narrow(a), nb = narrow(b);
                 return na != nb ? na : a.n > b.n;
