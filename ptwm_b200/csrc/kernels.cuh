@@ -330,6 +330,50 @@ __device__ __forceinline__ void fused16_rounds(const Epilogue& ep, uint32_t chun
     }
     pos += rounds * 32; remaining -= rounds * 32;
 }
+// Fused lane, fp8 elements: the two nibble planes (one nibble per byte) of 32 elements become one 32-byte store.
+__device__ __forceinline__ uint32_t compose_fp8x4(uint32_t hi, uint32_t lo, bool e4m3) {  // split/dtype8.rs:39-44,57-62 on four elements
+    uint32_t r = ((hi & 0x0F0F0F0Fu) << 4) | (lo & 0x0F0F0F0Fu);
+    return e4m3 ? ((r & 0xF0F0F0F0u) >> 1) | ((r & 0x08080808u) << 4) | (r & 0x07070707u)
+                : ((r & 0xF8F8F8F8u) >> 1) | ((r & 0x04040404u) << 5) | (r & 0x03030303u);
+}
+template <class Dec8>
+__device__ __forceinline__ void fused8_rounds(const Epilogue& ep, uint32_t chunk_n, uint32_t& pos, uint32_t& remaining, Dec8&& dec8) {
+    while (remaining >= 8 && ((reinterpret_cast<uintptr_t>(ep.dst) + pos) & 31) != 0) {
+        uint32_t s_lo, s_hi;  // groups of eight up to a 32-byte boundary of the destination
+        dec8(s_lo, s_hi);
+        emit(ep, pos, 8, uint64_t(s_lo) | uint64_t(s_hi) << 32);
+        pos += 8; remaining -= 8;
+    }
+    const uintptr_t p_lo = reinterpret_cast<uintptr_t>(ep.partner[0]), p_hi = p_lo + chunk_n;
+    const uintptr_t pa = p_lo + pos;
+    uintptr_t q = pa & ~uintptr_t(31);
+    uint8_t* out = ep.dst + pos;
+    uint32_t rounds = 0;
+    if ((reinterpret_cast<uintptr_t>(out) & 31) == 0 && q + 96 <= p_hi) {
+        rounds = uint32_t((p_hi - q - 96) >> 5) + 1;
+        if (rounds > (remaining >> 5)) rounds = remaining >> 5;
+    }
+    if (!rounds) return;
+    const uint32_t off = uint32_t(pa & 31);
+    const bool high_plane = ep.slot == 0, e4m3 = ep.kind == K_E4M3;  // plane 0 holds the high nibbles
+    Block32 cur = load_block_guarded(q, p_lo, p_hi), nxt = ldg256(reinterpret_cast<const void*>(q + 32));
+    for (uint32_t r = 0; r < rounds; ++r) {
+        const Block32 ahead = ldg256(reinterpret_cast<const void*>(q + 64));
+        uint32_t pw[8], v[8];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            uint32_t s_lo, s_hi;
+            dec8(s_lo, s_hi);
+            if (g == 0) extract32(cur, nxt, off, pw);
+            v[2 * g] = high_plane ? compose_fp8x4(s_lo, pw[2 * g], e4m3) : compose_fp8x4(pw[2 * g], s_lo, e4m3);
+            v[2 * g + 1] = high_plane ? compose_fp8x4(s_hi, pw[2 * g + 1], e4m3) : compose_fp8x4(pw[2 * g + 1], s_hi, e4m3);
+        }
+        stg256(out, make_uint4(v[0], v[1], v[2], v[3]), make_uint4(v[4], v[5], v[6], v[7]));
+        out += 32; q += 32;
+        cur = nxt; nxt = ahead;
+    }
+    pos += rounds * 32; remaining -= rounds * 32;
+}
 // Plain lane: eight symbols are eight bytes of the plane; 32 bytes per store.
 template <class Dec8>
 __device__ __forceinline__ void plain_rounds(const Epilogue& ep, uint32_t& pos, uint32_t& remaining, Dec8&& dec8) {
@@ -370,6 +414,7 @@ template <class Dec8>
 __device__ __forceinline__ void fast_groups(const Epilogue& ep, uint32_t chunk_n, uint32_t& pos, uint32_t& remaining, Dec8&& dec8) {
     if (!ep.fused) plain_rounds(ep, pos, remaining, dec8);
     else if (ep.kind == K_M16) fused16_rounds(ep, chunk_n, pos, remaining, dec8);
+    else if (ep.kind == K_E4M3 || ep.kind == K_E5M2) fused8_rounds(ep, chunk_n, pos, remaining, dec8);
     else fused_groups(ep, chunk_n, pos, remaining, dec8);
 }
 

@@ -239,3 +239,30 @@ def test_partial_blob_span_and_subset_plan():
         for i, v in zip(idx, plan.views(out)):
             assert bytes_of(v) == specs[i].raw, specs[i].name
     assert seen == list(range(len(specs)))
+
+
+# ---- planes that leave the fast paths -------------------------------------------------------
+def _hard_plane(n, seed):
+    """Exponent-plane bytes with long runs of rare symbols: rANS groups that need more than
+    eight renormalisation bytes, Huffman codes longer than the table window, and enough distinct
+    symbols in some chunks to leave the per-lane symbol lists."""
+    rng = np.random.default_rng(seed)
+    plane = ((rng.normal(0, 1.2, n).astype(np.int64) + 120) % 256).astype(np.uint8)
+    for start in range(1000, n - 600, 9000):          # bursts of (nearly) uniform bytes inside a peaked chunk
+        plane[start:start + 500] = rng.integers(0, 256, 500, dtype=np.uint8)
+    plane[n // 2:n // 2 + 70000] = rng.integers(0, 48, 70000, dtype=np.uint8) * 5   # a chunk with 48 distinct symbols
+    return plane.tobytes()
+
+
+@pytest.mark.parametrize("codec", [oracle.RANS, oracle.HUFFMAN])
+@pytest.mark.parametrize("offset", [0, 3])
+def test_fused_16bit_leaves_and_reenters_the_fast_loops(codec, offset):
+    n = 5 * 65536 + 12345
+    low = np.random.default_rng(11).integers(0, 256, n, dtype=np.uint8).tobytes()
+    raw = oracle.merge_inverse(oracle.M16, [low, _hard_plane(n, 5)])
+    specs = []
+    if offset:  # an odd-sized neighbour shifts every later payload in the file to another alignment
+        specs.append(oracle.TensorSpec("pad", oracle.DT_U8, [offset], bytes(range(offset))))
+    specs.append(oracle.TensorSpec("w", oracle.DT_BF16, [n], raw))
+    blob = oracle.write_container(specs, chunk_size=65536, forced_codec=codec)
+    check_container(blob, {s.name: s.raw for s in specs})
