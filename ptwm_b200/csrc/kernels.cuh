@@ -52,6 +52,8 @@ __device__ __forceinline__ uint64_t ld_bytes(const uint8_t* p, uint32_t count) {
     return v;
 }
 
+__device__ __forceinline__ void stg256(void* p, uint4 a, uint4 b);
+
 // ---- element composition ---------------------------------------------------
 __device__ __forceinline__ uint32_t revert16x2(uint32_t r) {  // split/dtype16.rs:20-25
     return ((r << 8) & 0x80008000u) | ((r >> 1) & 0x7F807F80u) | (r & 0x007F007Fu);
@@ -123,7 +125,9 @@ __device__ __forceinline__ void compose_store(int kind, uint8_t* dst, uint64_t p
                 w[4 * half + 3] = revert32(__byte_perm(t2, t3, 0x7632));
             }
             uint8_t* p = dst + pos * 4;
-            if (count == 8 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+            if (count == 8 && (reinterpret_cast<uintptr_t>(p) & 31) == 0) {
+                stg256(p, make_uint4(w[0], w[1], w[2], w[3]), make_uint4(w[4], w[5], w[6], w[7]));  // one sector per lane and instruction
+            } else if (count == 8 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
                 reinterpret_cast<uint4*>(p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
                 reinterpret_cast<uint4*>(p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
             } else {
@@ -374,6 +378,81 @@ __device__ __forceinline__ void fused8_rounds(const Epilogue& ep, uint32_t chunk
     }
     pos += rounds * 32; remaining -= rounds * 32;
 }
+// Fused lane, 32-bit elements, the lane decoding plane 3 (the exponent byte, the usual case: the three mantissa
+// planes are stored raw or were decoded before).  Rounds of 16 elements: each of the three partner planes arrives as
+// aligned 16-byte blocks one round ahead, the composed elements leave as two 32-byte stores.
+__device__ __forceinline__ uint4 load_block16_guarded(uintptr_t a, uintptr_t lo, uintptr_t hi) {
+    if (a >= lo && a + 16 <= hi) return __ldg(reinterpret_cast<const uint4*>(a));
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        uint32_t v = 0;
+        for (int i = 0; i < 4; ++i) {
+            uintptr_t q = a + 4 * k + i;
+            if (q >= lo && q < hi) v |= uint32_t(__ldg(reinterpret_cast<const uint8_t*>(q))) << (8 * i);
+        }
+        w[k] = v;
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+// The 16 bytes that start `off` (0..15) bytes into the 32 bytes (cur, nxt), as four words.
+__device__ __forceinline__ void extract16(const uint4& cur, const uint4& nxt, uint32_t off, uint32_t out[4]) {
+    const uint32_t a[8] = {cur.x, cur.y, cur.z, cur.w, nxt.x, nxt.y, nxt.z, nxt.w};
+    uint32_t b[6], c[5];
+    const bool j2 = off & 8, j1 = off & 4;
+#pragma unroll
+    for (int i = 0; i < 6; ++i) b[i] = j2 ? a[i + 2] : a[i];
+#pragma unroll
+    for (int i = 0; i < 5; ++i) c[i] = j1 ? b[i + 1] : b[i];
+    const uint32_t sel = 0x3210u + 0x1111u * (off & 3u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) out[i] = __byte_perm(c[i], c[i + 1], sel);
+}
+template <class Dec8>
+__device__ __forceinline__ void fused32_rounds(const Epilogue& ep, uint32_t chunk_n, uint32_t& pos, uint32_t& remaining, Dec8&& dec8) {
+    uint8_t* out = ep.dst + size_t(pos) * 4;
+    uintptr_t q[3], lo[3], hi[3];
+    uint32_t off[3], rounds = remaining >> 4;
+    if (reinterpret_cast<uintptr_t>(out) & 31) rounds = 0;
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+        lo[j] = reinterpret_cast<uintptr_t>(ep.partner[j]); hi[j] = lo[j] + chunk_n;
+        const uintptr_t pa = lo[j] + pos;
+        q[j] = pa & ~uintptr_t(15); off[j] = uint32_t(pa & 15);
+        // round r reads the block at q + 16 (r + 2): it must end inside the chunk
+        const uint32_t fit = q[j] + 48 <= hi[j] ? uint32_t((hi[j] - q[j] - 48) >> 4) + 1 : 0;
+        rounds = fit < rounds ? fit : rounds;
+    }
+    if (!rounds) return;
+    uint4 cur[3], nxt[3];
+#pragma unroll
+    for (int j = 0; j < 3; ++j) { cur[j] = load_block16_guarded(q[j], lo[j], hi[j]); nxt[j] = __ldg(reinterpret_cast<const uint4*>(q[j] + 16)); }
+    for (uint32_t r = 0; r < rounds; ++r) {
+        uint4 ahead[3];
+#pragma unroll
+        for (int j = 0; j < 3; ++j) ahead[j] = __ldg(reinterpret_cast<const uint4*>(q[j] + 32));
+        uint32_t sy[4], pw[3][4], w[16];
+        dec8(sy[0], sy[1]);
+        dec8(sy[2], sy[3]);
+#pragma unroll
+        for (int j = 0; j < 3; ++j) extract16(cur[j], nxt[j], off[j], pw[j]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {  // four elements: bytes 0..2 from the partner planes, byte 3 from this lane (transforms/fusion.rs:287-292)
+            const uint32_t t0 = __byte_perm(pw[0][k], pw[1][k], 0x5140), t1 = __byte_perm(pw[2][k], sy[k], 0x5140);
+            const uint32_t t2 = __byte_perm(pw[0][k], pw[1][k], 0x7362), t3 = __byte_perm(pw[2][k], sy[k], 0x7362);
+            w[4 * k + 0] = revert32(__byte_perm(t0, t1, 0x5410));
+            w[4 * k + 1] = revert32(__byte_perm(t0, t1, 0x7632));
+            w[4 * k + 2] = revert32(__byte_perm(t2, t3, 0x5410));
+            w[4 * k + 3] = revert32(__byte_perm(t2, t3, 0x7632));
+        }
+        stg256(out, make_uint4(w[0], w[1], w[2], w[3]), make_uint4(w[4], w[5], w[6], w[7]));
+        stg256(out + 32, make_uint4(w[8], w[9], w[10], w[11]), make_uint4(w[12], w[13], w[14], w[15]));
+        out += 64;
+#pragma unroll
+        for (int j = 0; j < 3; ++j) { cur[j] = nxt[j]; nxt[j] = ahead[j]; q[j] += 16; }
+    }
+    pos += rounds * 16; remaining -= rounds * 16;
+}
 // Plain lane: eight symbols are eight bytes of the plane; 32 bytes per store.
 template <class Dec8>
 __device__ __forceinline__ void plain_rounds(const Epilogue& ep, uint32_t& pos, uint32_t& remaining, Dec8&& dec8) {
@@ -415,7 +494,10 @@ __device__ __forceinline__ void fast_groups(const Epilogue& ep, uint32_t chunk_n
     if (!ep.fused) plain_rounds(ep, pos, remaining, dec8);
     else if (ep.kind == K_M16) fused16_rounds(ep, chunk_n, pos, remaining, dec8);
     else if (ep.kind == K_E4M3 || ep.kind == K_E5M2) fused8_rounds(ep, chunk_n, pos, remaining, dec8);
-    else fused_groups(ep, chunk_n, pos, remaining, dec8);
+    else {
+        if (ep.kind == K_M32 && ep.slot == 3) fused32_rounds(ep, chunk_n, pos, remaining, dec8);
+        fused_groups(ep, chunk_n, pos, remaining, dec8);  // the other plane orders, and what the rounds left
+    }
 }
 
 // ---- per-lane byte window over a stream ------------------------------------
@@ -537,10 +619,11 @@ __device__ __forceinline__ void rans_group8(const uint32_t* tab, const uint32_t*
     }
 }
 
-// 24 blocks per SM keeps the kernel at 80 registers: more blocks than that gave nothing (the load/store pipe, the
-// integer pipe and the issue slots are each about 55-60 % busy at 22), fewer registers spill.
+// 20 blocks per SM lets the compiler use 96 registers (21 blocks), which the 32-bit rounds need to stay out of local
+// memory; shared memory allows 22, and more blocks than that gave nothing (the load/store pipe, the integer pipe and the
+// issue slots are each about 55-60 % busy there).
 template <bool PER_LANE>
-__global__ void __launch_bounds__(32, 24) rans_decode_kernel_t(const DecodeItem* __restrict__ items, uint32_t n_items, Bases bases, uint32_t* __restrict__ status,
+__global__ void __launch_bounds__(32, 20) rans_decode_kernel_t(const DecodeItem* __restrict__ items, uint32_t n_items, Bases bases, uint32_t* __restrict__ status,
                                                            uint32_t l_entries) {
     constexpr int LS = PER_LANE ? 32 : 1;
     extern __shared__ __align__(16) uint8_t smem[];
