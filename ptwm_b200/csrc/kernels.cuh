@@ -1055,114 +1055,149 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
 }
 
 // ---- tANS ------------------------------------------------------------------
-// One stream per chunk: lane 4k decodes chunk k of the warp, all lanes help
-// build the 2048-entry table (symbol | nb<<8 | baseline<<16).
-constexpr int TANS_WARP_CHUNKS = 8;
-constexpr int TANS_SMEM_PER_CHUNK = 2048 * 4 + 2048;  // decode table + spread symbols
-constexpr int TANS_SMEM = TANS_WARP_CHUNKS * TANS_SMEM_PER_CHUNK;
+// One stream per chunk, so one lane per chunk: a CTA of one warp decodes 32
+// chunks.  Per chunk the decode table is kept as the spread symbols (u8 per
+// state) and (nbits << 11 | baseline) (u16 per state): 6 KiB instead of the
+// 8 KiB of a word per state, 192 KiB per CTA.  Both tables are interleaved
+// [state group][lane] so that a lane only ever touches its own bank: no
+// conflicts whatever the states are, and no synchronisation between lanes.
+constexpr int TANS_CTA_CHUNKS = 32;
+constexpr int TANS_SYM_BYTES = 2048 * 32;      // [state >> 2][lane][state & 3]
+constexpr int TANS_NB_BYTES = 2048 * 2 * 32;   // [state >> 1][lane][state & 1] of u16
+constexpr int TANS_SMEM = TANS_SYM_BYTES + TANS_NB_BYTES;
 
 __global__ void __launch_bounds__(32) tans_decode_kernel(const DecodeItem* __restrict__ items, uint32_t n_items, Bases bases, uint32_t* __restrict__ status) {
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t lane = threadIdx.x;
-    uint32_t* dt_all = reinterpret_cast<uint32_t*>(smem);
-    uint8_t* spread_all = smem + TANS_WARP_CHUNKS * 2048 * 4;
-    for (uint32_t c = 0; c < TANS_WARP_CHUNKS; ++c) {
-        const uint32_t item_idx = blockIdx.x * TANS_WARP_CHUNKS + c;
-        if (item_idx >= n_items) break;
-        const DecodeItem it = items[item_idx];
-        const uint8_t* src = rd(bases, it.src);
-        uint32_t* dt = dt_all + c * 2048;
-        uint8_t* sp = spread_all + c * 2048;
-        uint32_t err = ST_OK;
-        // header (mod.rs:388-425): every lane parses it redundantly
-        uint32_t nsym = 0;
-        if (it.src_len < 3 || src[0] != 11) err = ST_BAD_HEADER;
-        else {
-            nsym = uint32_t(src[1]) | uint32_t(src[2]) << 8;
-            if (nsym < 2 || nsym > 256 || 3 + nsym * 3 + 8 > it.src_len) err = ST_BAD_HEADER;
-        }
-        if (err) { if (lane == 0) atomicMax(&status[it.id], err); continue; }
-        // lane 0 builds the tables: the spread walks a running position and
-        // the decode entries count earlier slots of the same symbol, so both
-        // are sequential (mod.rs:199-211,346-369).
-        if (lane == 0) {
-            uint32_t norm[256];
-            for (uint32_t i = 0; i < 256; ++i) norm[i] = 0;
-            uint32_t sum = 0;
-            for (uint32_t i = 0; i < nsym; ++i) {
-                uint32_t sy = src[3 + 3 * i], fr = uint32_t(src[4 + 3 * i]) | uint32_t(src[5 + 3 * i]) << 8;
-                if (fr == 0 || norm[sy] != 0) { err = ST_BAD_HEADER; break; }  // mod.rs:404-411
-                norm[sy] = fr;
-                sum += fr;
-            }
-            if (!err && sum != 2048) err = ST_BAD_HEADER;
-            if (!err) {
-                uint32_t pos = 0;
-                for (uint32_t sy = 0; sy < 256; ++sy)
-                    for (uint32_t k = 0; k < norm[sy]; ++k) { sp[pos] = uint8_t(sy); pos = (pos + 1283u) & 2047u; }
-                for (uint32_t u = 0; u < 2048; ++u) {
-                    uint32_t sy = sp[u];
-                    uint32_t x = norm[sy]++;
-                    uint32_t nb = 11 - (31 - __clz(x));
-                    uint32_t baseline = (x << nb) - 2048;
-                    dt[u] = sy | (nb << 8) | (baseline << 16);
-                }
-            }
-        }
-        err = __shfl_sync(0xFFFFFFFFu, err, 0);
-        if (err) { if (lane == 0) atomicMax(&status[it.id], err); continue; }
-        __syncwarp();
-        if (lane == 0) {
-            Epilogue ep = make_epilogue(bases, it);
-            const uint8_t* hp = src + 3 + nsym * 3;
-            uint64_t total_bits = uint64_t(ld_u32_unaligned(hp)) | uint64_t(ld_u32_unaligned(hp + 4)) << 32;
-            const uint8_t* bs = hp + 8;
-            uint64_t bslen = it.src_len - (3 + nsym * 3 + 8);
-            if (total_bits > bslen * 8) err = ST_BAD_HEADER;
-            else {
-                // LIFO reader (mod.rs:118-147): bits [bpos-cnt, bpos) sit right-aligned in `cont`
-                uint64_t nbytes = (total_bits + 7) >> 3;  // bytes that hold declared bits
-                uint64_t bi = nbytes;                      // next byte to load is bs[bi-1]
-                uint64_t cont = 0; uint32_t cnt = 0;
-                uint32_t top = uint32_t(total_bits & 7);
-                if (top) { --bi; cont = bs[bi] & ((1u << top) - 1); cnt = top; }
-                auto read = [&](uint32_t nb) -> uint32_t {
-                    if (nb == 0) return 0;
-                    while (cnt < nb && bi > 0) { --bi; cont = (cont << 8) | bs[bi]; cnt += 8; }
-                    if (cnt < nb) { err = ST_STREAM_UNDERRUN; return 0; }
-                    uint32_t v = uint32_t(cont >> (cnt - nb)) & ((1u << nb) - 1);
-                    cnt -= nb;
-                    cont &= (cnt ? ((1ull << cnt) - 1) : 0ull);
-                    return v;
-                };
-                uint32_t state = read(11);
-                uint64_t pos = 0;
-                uint32_t remaining = it.n;
-                uint32_t g = first_group(ep, pos, remaining);
-                while (remaining && !err) {
-                    uint64_t syms = 0;
-                    for (uint32_t j = 0; j < g; ++j) {
-                        uint32_t e = dt[state & 2047u];
-                        syms |= uint64_t(e & 0xFF) << (8 * j);
-                        state = (e >> 16) + read((e >> 8) & 0xFF);
-                        if (state >= 2048) { err = ST_STREAM_UNDERRUN; state = 0; }
-                    }
-                    emit(ep, pos, g, syms);
-                    pos += g; remaining -= g;
-                    g = remaining < 8 ? remaining : 8;
-                }
-                if (!err && (cnt != 0 || bi != 0 || state != 0)) err = ST_NOT_CONSUMED;  // mod.rs:442-449
-            }
-            if (err) atomicMax(&status[it.id], err);
-        }
-        __syncwarp();
+    const uint32_t item_idx = blockIdx.x * TANS_CTA_CHUNKS + lane;
+    if (item_idx >= n_items) return;
+    const DecodeItem it = items[item_idx];
+    const uint8_t* src = rd(bases, it.src);
+    uint8_t* sym_tab = smem + lane * 4;
+    uint8_t* nb_tab = smem + TANS_SYM_BYTES + lane * 4;
+    auto sym_at = [&](uint32_t u) -> uint8_t& { return sym_tab[((u >> 2) << 7) | (u & 3u)]; };
+    auto nb_at = [&](uint32_t u) -> uint16_t& { return *reinterpret_cast<uint16_t*>(nb_tab + (((u >> 1) << 7) | ((u & 1u) << 1))); };
+    uint32_t err = ST_OK;
+
+    // header (mod.rs:388-425)
+    uint32_t nsym = 0;
+    if (it.src_len < 3 || src[0] != 11) err = ST_BAD_HEADER;
+    else {
+        nsym = uint32_t(src[1]) | uint32_t(src[2]) << 8;
+        if (nsym < 2 || nsym > 256 || 3 + nsym * 3 + 8 > it.src_len) err = ST_BAD_HEADER;
     }
+    // tables: the spread walks a running position and the decode entries count earlier states of the same
+    // symbol, so both are sequential (mod.rs:199-211,346-369); every lane builds its own chunk's
+    if (!err) {
+        uint32_t norm[256];
+        for (uint32_t i = 0; i < 256; ++i) norm[i] = 0;
+        uint32_t sum = 0;
+        for (uint32_t i = 0; i < nsym; ++i) {
+            uint32_t sy = src[3 + 3 * i], fr = uint32_t(src[4 + 3 * i]) | uint32_t(src[5 + 3 * i]) << 8;
+            if (fr == 0 || norm[sy] != 0) { err = ST_BAD_HEADER; break; }  // mod.rs:404-411
+            norm[sy] = fr;
+            sum += fr;
+        }
+        if (!err && sum != 2048) err = ST_BAD_HEADER;
+        if (!err) {
+            uint32_t pos = 0;
+            for (uint32_t sy = 0; sy < 256; ++sy)
+                for (uint32_t k = 0; k < norm[sy]; ++k) { sym_at(pos) = uint8_t(sy); pos = (pos + 1283u) & 2047u; }
+            for (uint32_t u = 0; u < 2048; ++u) {
+                uint32_t sy = sym_at(u);
+                uint32_t x = norm[sy]++;
+                uint32_t nb = 11 - (31 - __clz(x));
+                nb_at(u) = uint16_t(((x << nb) - 2048) | (nb << 11));
+            }
+        }
+    }
+    if (!err) {
+        Epilogue ep = make_epilogue(bases, it);
+        const uint8_t* hp = src + 3 + nsym * 3;
+        const uint64_t total_bits = uint64_t(ld_u32_unaligned(hp)) | uint64_t(ld_u32_unaligned(hp + 4)) << 32;
+        const uint8_t* bs = hp + 8;
+        const uint64_t bslen = it.src_len - (3 + nsym * 3 + 8);
+        if (total_bits > bslen * 8) err = ST_BAD_HEADER;
+        else {
+            // LIFO reader (mod.rs:118-147): the stream is read from its last byte down; the `cnt` unread bits sit in
+            // the low end of `cont`, the next to be used on top.  A word read little-endian from below the read
+            // position has its bytes in exactly that order.
+            uint32_t bi = uint32_t((total_bits + 7) >> 3);  // bytes that hold declared bits; the next to load is bs[bi-1]
+            uint64_t cont = 0;
+            int32_t cnt = 0;
+            const uint32_t top = uint32_t(total_bits & 7);
+            if (top) { --bi; cont = bs[bi] & ((1u << top) - 1); cnt = int32_t(top); }
+            auto refill = [&]() {  // up to more than 32 bits, by bytes until the position is word aligned, then by words
+                while (cnt <= 32 && bi > 0) {
+                    if (bi >= 4 && ((reinterpret_cast<uintptr_t>(bs) + bi) & 3) == 0) {
+                        cont = (cont << 32) | __ldg(reinterpret_cast<const uint32_t*>(bs + bi - 4));
+                        cnt += 32; bi -= 4;
+                    } else { --bi; cont = (cont << 8) | bs[bi]; cnt += 8; }
+                }
+            };
+            auto take = [&](uint32_t nb) -> uint32_t { cnt -= int32_t(nb); return uint32_t(cont >> (cnt & 63)) & ((1u << nb) - 1u); };
+            refill();
+            uint32_t state = 0;
+            if (cnt < 11) err = ST_STREAM_UNDERRUN; else state = take(11);
+            // one symbol with the reference's checks
+            auto one_symbol = [&]() -> uint32_t {
+                refill();
+                const uint32_t sy = sym_at(state), e = nb_at(state), nb = e >> 11;
+                if (int32_t(nb) > cnt) { err = ST_STREAM_UNDERRUN; return sy; }
+                state = (e & 2047u) + take(nb);
+                if (state >= 2048) { err = ST_STREAM_UNDERRUN; state = 0; }
+                return sy;
+            };
+            // Eight symbols in two halves of four: after a refill the container holds more than 32 bits (unless the
+            // stream is at its end) and four symbols take at most 44, around ten on an exponent plane, so the
+            // halves run unchecked; a group that ran out of bits is decoded again one symbol at a time.
+            auto dec8 = [&](uint32_t& s_lo, uint32_t& s_hi) {
+                const uint64_t cont0 = cont;
+                const int32_t cnt0 = cnt;
+                const uint32_t bi0 = bi, state0 = state;
+                int32_t lowest = 0;
+                s_lo = 0; s_hi = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if ((j & 3) == 0) refill();
+                    const uint32_t sy = sym_at(state), e = nb_at(state);
+                    state = ((e & 2047u) + take(e >> 11)) & 2047u;
+                    lowest |= cnt;
+                    const uint32_t ins = (0x3210u & ~(0xFu << (4 * (j & 3)))) | (4u << (4 * (j & 3)));
+                    if (j < 4) s_lo = __byte_perm(s_lo, sy, ins); else s_hi = __byte_perm(s_hi, sy, ins);
+                }
+                if (lowest < 0) {
+                    cont = cont0; cnt = cnt0; bi = bi0; state = state0;
+                    s_lo = 0; s_hi = 0;
+                    for (uint32_t j = 0; j < 8 && !err; ++j) {
+                        uint32_t sy = one_symbol();
+                        if (j < 4) s_lo |= sy << (8 * j); else s_hi |= sy << (8 * (j - 4));
+                    }
+                }
+            };
+            uint32_t pos = 0, remaining = it.n;
+            auto short_group = [&](uint32_t g) {
+                uint64_t syms = 0;
+                for (uint32_t j = 0; j < g && !err; ++j) syms |= uint64_t(one_symbol()) << (8 * j);
+                emit(ep, pos, g, syms);
+                pos += g; remaining -= g;
+            };
+            if (!err && remaining) {
+                uint32_t g = first_group(ep, pos, remaining);
+                if (g < 8 || remaining < 16) short_group(g);
+            }
+            if (!err) fast_groups(ep, it.n, pos, remaining, dec8);
+            while (remaining && !err) short_group(remaining < 8 ? remaining : 8);
+            if (!err && (cnt != 0 || bi != 0 || state != 0)) err = ST_NOT_CONSUMED;  // mod.rs:442-449
+        }
+    }
+    if (err) atomicMax(&status[it.id], err);
 }
 
 // ---- Order1ScaleAC ---------------------------------------------------------
-// One range-coder stream per chunk.  The warp first turns the chunk's PMFs
-// into cumulative tables in the scratch arena (u16, 257 per context), then
-// lane 0 decodes.
+// One range-coder stream per chunk, one warp per chunk.  The warp first turns
+// the chunk's PMFs into cumulative tables in the scratch arena (u16, 257 per
+// context), then decodes the stream together.
 __global__ void __launch_bounds__(32) o1sac_decode_kernel(const DecodeItem* __restrict__ items, uint32_t n_items, Bases bases, uint32_t* __restrict__ status) {
     const uint32_t lane = threadIdx.x;
     const uint32_t item_idx = blockIdx.x;
@@ -1207,8 +1242,10 @@ __global__ void __launch_bounds__(32) o1sac_decode_kernel(const DecodeItem* __re
     __syncwarp();
     __threadfence_block();
     if (err) { if (lane == 0) atomicMax(&status[it.id], err); return; }
-    if (lane != 0) return;
 
+    // The stream is serial, so the warp shares it: every lane carries the same coder state, the search for the
+    // symbol (the largest index whose cumulative count is <= target, order1_scale_ac.rs:474-486) is two rounds of
+    // 32 and 8 parallel probes with a ballot instead of eight dependent loads, and lane 0 places the symbols.
     Epilogue ep = make_epilogue(bases, it);
     const uint8_t* src = rd(bases, it.src);
     const uint32_t slen = it.src_len;
@@ -1232,9 +1269,16 @@ __global__ void __launch_bounds__(32) o1sac_decode_kernel(const DecodeItem* __re
             uint32_t offset = uint32_t(code) - low;
             uint32_t target = offset / rpt;
             if (target > 4095) target = 4095;
-            uint32_t lo = 0, hi = 256;  // order1_scale_ac.rs:474-486
-            while (lo + 1 < hi) { uint32_t mid = (lo + hi) >> 1; if (ct[mid] <= target) lo = mid; else hi = mid; }
-            uint32_t cumv = ct[lo], prob = uint32_t(ct[lo + 1]) - cumv;
+            const uint32_t c1 = ct[lane * 8];                                          // entries 0, 8, ..., 248
+            const uint32_t blocks = __popc(__ballot_sync(0xFFFFFFFFu, c1 <= target));  // >= 1: entry 0 is 0
+            const uint32_t base = (blocks - 1) * 8;
+            const uint32_t c2 = ct[base + (lane & 7)];                                 // the block's eight entries (lanes 8.. repeat them)
+            const uint32_t within = __popc(__ballot_sync(0xFFFFFFFFu, c2 <= target) & 0xFFu);  // >= 1: the block's first entry is <= target
+            const uint32_t lo = base + within - 1;
+            const uint32_t cumv = __shfl_sync(0xFFFFFFFFu, c2, within - 1);
+            const uint32_t above_in = __shfl_sync(0xFFFFFFFFu, c2, within & 7), above_out = __shfl_sync(0xFFFFFFFFu, c1, blocks & 31);
+            const uint32_t next = within < 8 ? above_in : (blocks < 32 ? above_out : 4096u);  // entry lo + 1; entry 256 is the total
+            const uint32_t prob = next - cumv;
             low = low + cumv * rpt;  // & 0xFFFFFFFF by width
             range = uint64_t(prob) * rpt;
             while (range < (1ull << 24)) {
@@ -1248,7 +1292,7 @@ __global__ void __launch_bounds__(32) o1sac_decode_kernel(const DecodeItem* __re
             prev = int(lo);
             row_pos = row_pos + 1 == row_len ? 0 : row_pos + 1;
         }
-        emit(ep, pos, g, syms);
+        if (lane == 0) emit(ep, pos, g, syms);
         pos += g; remaining -= g;
         g = remaining < 8 ? remaining : 8;
     }

@@ -179,7 +179,7 @@ void plan_tensor(ptwm_b200_plan& pl, uint32_t ti, const TensorDesc& t, uint64_t 
             for (int p = 0; p < np; ++p) {
                 const ChunkDesc& ch = t.planes[size_t(p)].chunks[k];
                 uint16_t codec = t.planes[size_t(p)].codec;
-                if (!ch.raw && (codec == C_RANS || codec == C_HUFFMAN)) fused_plane = p;
+                if (!ch.raw && (codec == C_RANS || codec == C_HUFFMAN || codec == C_TANS)) fused_plane = p;
             }
             if (np == 1) {
                 const ChunkDesc& ch = t.planes[0].chunks[k];
@@ -330,7 +330,7 @@ int64_t enqueue(ptwm_b200_plan& pl, DevicePlan& d, const Bases& bases, uint32_t 
                     break;
                 }
                 case 1: huffman_decode_kernel<<<(n + HUF_WARP_CHUNKS - 1) / HUF_WARP_CHUNKS, 32, HUF_SMEM, st>>>(it, n, bases, status); break;
-                case 2: tans_decode_kernel<<<(n + TANS_WARP_CHUNKS - 1) / TANS_WARP_CHUNKS, 32, TANS_SMEM, st>>>(it, n, bases, status); break;
+                case 2: tans_decode_kernel<<<(n + TANS_CTA_CHUNKS - 1) / TANS_CTA_CHUNKS, 32, TANS_SMEM, st>>>(it, n, bases, status); break;
                 default: o1sac_decode_kernel<<<n, 32, 0, st>>>(it, n, bases, status); break;
             }
             CUDA_TRY(cudaGetLastError());

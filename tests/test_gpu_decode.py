@@ -266,3 +266,13 @@ def test_fused_16bit_leaves_and_reenters_the_fast_loops(codec, offset):
     specs.append(oracle.TensorSpec("w", oracle.DT_BF16, [n], raw))
     blob = oracle.write_container(specs, chunk_size=65536, forced_codec=codec)
     check_container(blob, {s.name: s.raw for s in specs})
+
+
+@pytest.mark.parametrize("case", [dict(forced_codec=oracle.RANS, chunk_size=65536), dict(forced_codec=oracle.HUFFMAN, chunk_size=20001, emit_crc=True),
+                                  dict(menu=(oracle.HUFFMAN, oracle.RANS), chunk_size=32768, emit_hash=True), dict(forced_codec=oracle.RANS, chunk_size=20001)])
+def test_larger_mixed_model_runs_the_round_loops(case):
+    """Tensors of several chunks each, chunk sizes that leave every stream and partner plane at an odd address:
+    the 32- and 16-element round loops of the 16-bit, fp8 and fp32 paths, their heads and tails."""
+    specs = mixed_model(scale=4)
+    blob = oracle.write_container(specs, **case)
+    check_container(blob, {s.name: s.raw for s in specs})
