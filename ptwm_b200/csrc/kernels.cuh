@@ -1058,12 +1058,14 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
 // One stream per chunk, so one lane per chunk: a CTA of one warp decodes 32
 // chunks.  Per chunk the decode table is kept as the spread symbols (u8 per
 // state) and (nbits << 11 | baseline) (u16 per state): 6 KiB instead of the
-// 8 KiB of a word per state, 192 KiB per CTA.  Both tables are interleaved
-// [state group][lane] so that a lane only ever touches its own bank: no
-// conflicts whatever the states are, and no synchronisation between lanes.
+// 8 KiB of a word per state, 192 KiB per CTA.  Both tables are laid out
+// [state][lane], so the address of an entry is one multiply-add from the
+// state; a lane only touches its own columns (no synchronisation between
+// lanes), and with one warp per SM the few bank conflicts of that layout cost
+// less than a longer address computation on the serial chain would.
 constexpr int TANS_CTA_CHUNKS = 32;
-constexpr int TANS_SYM_BYTES = 2048 * 32;      // [state >> 2][lane][state & 3]
-constexpr int TANS_NB_BYTES = 2048 * 2 * 32;   // [state >> 1][lane][state & 1] of u16
+constexpr int TANS_SYM_BYTES = 2048 * 32;      // [state][lane] of u8
+constexpr int TANS_NB_BYTES = 2048 * 2 * 32;   // [state][lane] of u16
 constexpr int TANS_SMEM = TANS_SYM_BYTES + TANS_NB_BYTES;
 
 __global__ void __launch_bounds__(32) tans_decode_kernel(const DecodeItem* __restrict__ items, uint32_t n_items, Bases bases, uint32_t* __restrict__ status) {
@@ -1073,10 +1075,10 @@ __global__ void __launch_bounds__(32) tans_decode_kernel(const DecodeItem* __res
     if (item_idx >= n_items) return;
     const DecodeItem it = items[item_idx];
     const uint8_t* src = rd(bases, it.src);
-    uint8_t* sym_tab = smem + lane * 4;
-    uint8_t* nb_tab = smem + TANS_SYM_BYTES + lane * 4;
-    auto sym_at = [&](uint32_t u) -> uint8_t& { return sym_tab[((u >> 2) << 7) | (u & 3u)]; };
-    auto nb_at = [&](uint32_t u) -> uint16_t& { return *reinterpret_cast<uint16_t*>(nb_tab + (((u >> 1) << 7) | ((u & 1u) << 1))); };
+    uint8_t* sym_tab = smem + lane;
+    uint8_t* nb_tab = smem + TANS_SYM_BYTES + lane * 2;
+    auto sym_at = [&](uint32_t u) -> uint8_t& { return sym_tab[u << 5]; };
+    auto nb_at = [&](uint32_t u) -> uint16_t& { return *reinterpret_cast<uint16_t*>(nb_tab + (u << 6)); };
     uint32_t err = ST_OK;
 
     // header (mod.rs:388-425)
@@ -1119,23 +1121,28 @@ __global__ void __launch_bounds__(32) tans_decode_kernel(const DecodeItem* __res
         const uint64_t bslen = it.src_len - (3 + nsym * 3 + 8);
         if (total_bits > bslen * 8) err = ST_BAD_HEADER;
         else {
-            // LIFO reader (mod.rs:118-147): the stream is read from its last byte down; the `cnt` unread bits sit in
-            // the low end of `cont`, the next to be used on top.  A word read little-endian from below the read
-            // position has its bytes in exactly that order.
+            // LIFO reader (mod.rs:118-147): the stream is read from its last byte down, every byte from its high bit
+            // down.  The `cnt` unread bits sit at the top of `cont`, the next to be used highest, so taking n bits is
+            // one funnel shift; a word read little-endian from below the read position has its bytes in that order.
             uint32_t bi = uint32_t((total_bits + 7) >> 3);  // bytes that hold declared bits; the next to load is bs[bi-1]
             uint64_t cont = 0;
             int32_t cnt = 0;
             const uint32_t top = uint32_t(total_bits & 7);
-            if (top) { --bi; cont = bs[bi] & ((1u << top) - 1); cnt = int32_t(top); }
+            if (top) { --bi; cont = uint64_t(bs[bi] & ((1u << top) - 1)) << (64 - top); cnt = int32_t(top); }
             auto refill = [&]() {  // up to more than 32 bits, by bytes until the position is word aligned, then by words
-                while (cnt <= 32 && bi > 0) {
+                while (uint32_t(cnt) <= 32u && bi > 0) {  // (a negative count only occurs in a group that is about to be decoded again)
                     if (bi >= 4 && ((reinterpret_cast<uintptr_t>(bs) + bi) & 3) == 0) {
-                        cont = (cont << 32) | __ldg(reinterpret_cast<const uint32_t*>(bs + bi - 4));
+                        cont |= uint64_t(__ldg(reinterpret_cast<const uint32_t*>(bs + bi - 4))) << (32 - cnt);
                         cnt += 32; bi -= 4;
-                    } else { --bi; cont = (cont << 8) | bs[bi]; cnt += 8; }
+                    } else { --bi; cont |= uint64_t(bs[bi]) << (56 - cnt); cnt += 8; }
                 }
             };
-            auto take = [&](uint32_t nb) -> uint32_t { cnt -= int32_t(nb); return uint32_t(cont >> (cnt & 63)) & ((1u << nb) - 1u); };
+            auto take = [&](uint32_t nb) -> uint32_t {  // nb <= 11
+                const uint32_t hi = uint32_t(cont >> 32);
+                const uint32_t v = __funnelshift_l(hi, 0u, nb);  // the top nb bits; 0 for nb == 0
+                cont <<= nb; cnt -= int32_t(nb);
+                return v;
+            };
             refill();
             uint32_t state = 0;
             if (cnt < 11) err = ST_STREAM_UNDERRUN; else state = take(11);
