@@ -149,6 +149,17 @@ __global__ void __launch_bounds__(128) encode_kernel(const EncChunk* __restrict_
     const uint8_t* src = planes + c.plane_off + start;
     uint8_t* slot_end = slots + c.slot_off + uint64_t(s + 1) * c.slot_cap;
     uint8_t* w = slot_end;
+    // Bytes go out downward.  Single byte stores to global memory are what this kernel used to wait for, so
+    // once the write position is 8-byte aligned eight bytes are collected (the first produced ends up highest,
+    // as in memory) and stored as one word.
+    uint64_t acc = 0;
+    uint32_t have = 0;
+    auto put = [&](uint32_t b) {
+        if (have == 0 && (reinterpret_cast<uintptr_t>(w) & 7)) { *--w = uint8_t(b); return; }
+        acc = (acc << 8) | (b & 0xFFu);
+        if (++have == 8) { w -= 8; *reinterpret_cast<uint64_t*>(w) = acc; have = 0; acc = 0; }
+    };
+    auto flush = [&]() { while (have) { --have; *--w = uint8_t(acc >> (8 * have)); } };
     const uint8_t* tab = tables + uint64_t(ci) * ENC_TABLE_BYTES;
     if (codec == C_RANS) {
         const uint16_t* freqs = reinterpret_cast<const uint16_t*>(tab);
@@ -158,23 +169,23 @@ __global__ void __launch_bounds__(128) encode_kernel(const EncChunk* __restrict_
             uint32_t sym = src[k];
             uint32_t f = freqs[sym], cs = cum[sym];
             uint32_t max_state = ((1u << 12) << 8) * f;  // ((L >> 11) << 8) * freq
-            while (x >= max_state) { *--w = uint8_t(x); x >>= 8; }
+            while (x >= max_state) { put(x); x >>= 8; }
             x = (x / f) * 2048u + (x % f) + cs;
         }
-        w -= 4;
-        w[0] = uint8_t(x); w[1] = uint8_t(x >> 8); w[2] = uint8_t(x >> 16); w[3] = uint8_t(x >> 24);
+        put(x >> 24); put(x >> 16); put(x >> 8); put(x);  // the final state, little-endian, below the renormalisation bytes
     } else {
         const uint8_t* lengths = tab;
         const uint16_t* rev = reinterpret_cast<const uint16_t*>(tab + 512);
-        uint64_t acc = 0; uint32_t cnt = 0;
+        uint64_t bits = 0; uint32_t cnt = 0;
         for (uint32_t k = 0; k < len; ++k) {
             uint32_t sym = src[k];
-            acc |= uint64_t(rev[sym]) << cnt;
+            bits |= uint64_t(rev[sym]) << cnt;
             cnt += lengths[sym];
-            while (cnt >= 8) { *--w = uint8_t(acc); acc >>= 8; cnt -= 8; }
+            while (cnt >= 8) { put(uint32_t(bits)); bits >>= 8; cnt -= 8; }
         }
-        if (cnt) *--w = uint8_t(acc);
+        if (cnt) put(uint32_t(bits));
     }
+    flush();
     results[ci].stream_len[s] = uint32_t(slot_end - w);
 }
 
