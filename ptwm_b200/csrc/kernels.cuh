@@ -1213,7 +1213,7 @@ __global__ void __launch_bounds__(32) o1sac_decode_kernel(const DecodeItem* __re
     const uint8_t* st = rd(bases, it.state);
     uint32_t err = ST_OK;
     __shared__ uint8_t bitmap[32];
-    __shared__ uint8_t rank_of[256];
+    __shared__ uint16_t table_of[256];  // which cumulative table a previous byte selects: 0 = marginal, 1 + rank of the context otherwise
     if (it.state_version != 1 || it.state_len < 32 + 512) err = ST_BAD_STATE;
     uint32_t pop = 0;
     if (!err) {
@@ -1228,13 +1228,14 @@ __global__ void __launch_bounds__(32) o1sac_decode_kernel(const DecodeItem* __re
         uint32_t r = 0;
         for (uint32_t b = 0; b < (p >> 3); ++b) r += __popc(uint32_t(bitmap[b]));
         r += __popc(uint32_t(bitmap[p >> 3]) & ((1u << (p & 7)) - 1));
-        rank_of[p] = uint8_t(r);  // ranks 0..255 fit: a present context has rank <= 255
+        table_of[p] = ((bitmap[p >> 3] >> (p & 7)) & 1) ? uint16_t(1 + r) : uint16_t(0);
     }
-    // cumulative tables: table t (0 = marginal, 1+r = row r) = 257 u16 at work + t*514
+    // cumulative tables: table t (0 = marginal, 1+r = row r) = 256 u16 at work + t*512 (the count below each symbol;
+    // the total is 4096 by the check below)
     uint16_t* cum = reinterpret_cast<uint16_t*>(wr(bases, it.work));
     for (uint32_t t = lane; t < 1 + pop; t += 32) {
         const uint8_t* pm = st + 32 + t * 512;
-        uint16_t* ct = cum + t * 257;
+        uint16_t* ct = cum + t * 256;
         uint32_t acc = 0; bool zero = false;
         for (uint32_t i = 0; i < 256; ++i) {
             uint32_t v = uint32_t(pm[2 * i]) | uint32_t(pm[2 * i + 1]) << 8;
@@ -1242,7 +1243,6 @@ __global__ void __launch_bounds__(32) o1sac_decode_kernel(const DecodeItem* __re
             ct[i] = uint16_t(acc);
             acc += v;
         }
-        ct[256] = uint16_t(acc);
         if (zero || acc != 4096) err = ST_BAD_STATE;  // quantize.rs:53-71
     }
     err = __reduce_max_sync(0xFFFFFFFFu, err);
@@ -1251,8 +1251,8 @@ __global__ void __launch_bounds__(32) o1sac_decode_kernel(const DecodeItem* __re
     if (err) { if (lane == 0) atomicMax(&status[it.id], err); return; }
 
     // The stream is serial, so the warp shares it: every lane carries the same coder state, the search for the
-    // symbol (the largest index whose cumulative count is <= target, order1_scale_ac.rs:474-486) is two rounds of
-    // 32 and 8 parallel probes with a ballot instead of eight dependent loads, and lane 0 places the symbols.
+    // symbol (the largest index whose cumulative count is <= target, order1_scale_ac.rs:474-486) is 256 parallel
+    // probes and three warp reductions instead of eight dependent loads, and lane 0 places the symbols.
     Epilogue ep = make_epilogue(bases, it);
     const uint8_t* src = rd(bases, it.src);
     const uint32_t slen = it.src_len;
@@ -1266,30 +1266,43 @@ __global__ void __launch_bounds__(32) o1sac_decode_kernel(const DecodeItem* __re
     uint64_t pos = 0;
     uint32_t remaining = it.n;
     uint32_t g = remaining ? first_group(ep, pos, remaining) : 0;
+    // the next stream bytes, four at a time, so that renormalising does not wait for memory (zero past the end)
+    auto next_bytes = [&](uint32_t at) -> uint32_t {
+        uint32_t v = 0;
+        for (uint32_t k = 0; k < 4; ++k) if (at + k < slen) v |= uint32_t(src[at + k]) << (8 * k);
+        return v;
+    };
+    uint32_t ahead = next_bytes(rpos), ahead_left = 4;
     while (remaining) {
         uint64_t syms = 0;
         for (uint32_t j = 0; j < g; ++j) {
             if (row_pos == 0) prev = -1;
-            const uint16_t* ct = cum;
-            if (prev >= 0 && ((bitmap[prev >> 3] >> (prev & 7)) & 1)) ct = cum + (1 + rank_of[prev]) * 257;
-            uint32_t rpt = uint32_t(range >> 12);  // range / 4096
-            uint32_t offset = uint32_t(code) - low;
-            uint32_t target = offset / rpt;
-            if (target > 4095) target = 4095;
-            const uint32_t c1 = ct[lane * 8];                                          // entries 0, 8, ..., 248
-            const uint32_t blocks = __popc(__ballot_sync(0xFFFFFFFFu, c1 <= target));  // >= 1: entry 0 is 0
-            const uint32_t base = (blocks - 1) * 8;
-            const uint32_t c2 = ct[base + (lane & 7)];                                 // the block's eight entries (lanes 8.. repeat them)
-            const uint32_t within = __popc(__ballot_sync(0xFFFFFFFFu, c2 <= target) & 0xFFu);  // >= 1: the block's first entry is <= target
-            const uint32_t lo = base + within - 1;
-            const uint32_t cumv = __shfl_sync(0xFFFFFFFFu, c2, within - 1);
-            const uint32_t above_in = __shfl_sync(0xFFFFFFFFu, c2, within & 7), above_out = __shfl_sync(0xFFFFFFFFu, c1, blocks & 31);
-            const uint32_t next = within < 8 ? above_in : (blocks < 32 ? above_out : 4096u);  // entry lo + 1; entry 256 is the total
-            const uint32_t prob = next - cumv;
+            const uint16_t* ct = cum + (prev >= 0 ? uint32_t(table_of[prev]) * 256u : 0u);
+            const uint32_t rpt = uint32_t(range >> 12);  // range / 4096
+            const uint32_t offset = uint32_t(code) - low;
+            // target = min(offset / rpt, 4095) and "count <= target" is "count * rpt <= offset": no division
+            // (counts are below 4096, rpt < 2^20, so the products fit 32 bits).  One 16-byte load per lane brings
+            // the whole table; the symbol is the number of counts that qualify minus one, its count the largest
+            // that qualifies, the next count the smallest that does not (4096 when all do).
+            const uint4 q = *reinterpret_cast<const uint4*>(ct + lane * 8);
+            const uint32_t c[8] = {q.x & 0xFFFFu, q.x >> 16, q.y & 0xFFFFu, q.y >> 16, q.z & 0xFFFFu, q.z >> 16, q.w & 0xFFFFu, q.w >> 16};
+            uint32_t fit = 0, below = 0, above = 4096;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const bool ok = c[i] * rpt <= offset;
+                fit += ok;
+                below = ok ? max(below, c[i]) : below;
+                above = ok ? above : min(above, c[i]);
+            }
+            const uint32_t lo = __reduce_add_sync(0xFFFFFFFFu, fit) - 1;  // >= 0: entry 0 is 0
+            const uint32_t cumv = __reduce_max_sync(0xFFFFFFFFu, below);
+            const uint32_t prob = __reduce_min_sync(0xFFFFFFFFu, above) - cumv;
             low = low + cumv * rpt;  // & 0xFFFFFFFF by width
             range = uint64_t(prob) * rpt;
             while (range < (1ull << 24)) {
-                uint32_t b = rpos < slen ? src[rpos] : 0;
+                if (ahead_left == 0) { ahead = next_bytes(rpos); ahead_left = 4; }
+                const uint32_t b = ahead & 0xFFu;
+                ahead >>= 8; --ahead_left;
                 ++rpos;
                 code = ((code & 0xFFFFFFFFFFull) << 8) | b;
                 low = (low & 0x00FFFFFFu) << 8;
