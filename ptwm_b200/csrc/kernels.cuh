@@ -527,6 +527,8 @@ constexpr int RING_SMEM = 16 * 32 * 4;
 // How many distinct symbols a chunk may hold for the kernel that keeps a copy
 // of the symbol list per lane (two pad entries come on top).
 constexpr uint32_t RANS_NARROW_SYMBOLS = 38;
+// From this many distinct symbols on a chunk counts as nearly incompressible (packed fp4 values, mantissa-like bytes).
+constexpr uint32_t RANS_DENSE_SYMBOLS = 96;
 // Shared memory per chunk:
 //  * a rank table over the 2048 slots: 128 words of (16-bit boundary bitmap,
 //    boundaries before the word << 16).  Bit i of a bitmap is set when slot
@@ -590,17 +592,25 @@ __device__ __forceinline__ void rans_short_group(const uint32_t* tab, const uint
 // bytes sit big-endian in two registers behind the state; renormalising by
 // 0..3 bytes (the count follows from the leading zeros of the state) is a
 // funnel shift of state and window.  Eight bytes cover a group unless its
-// symbols average more than one byte each (frequencies below 8 in a row); the
-// total is checked once per group and such a group is decoded again byte-wise.
-template <int LS>
+// symbols average more than one byte each; the total is checked once per group
+// and a group that needed more is decoded again byte-wise.  On a plane of
+// nearly incompressible bytes (many symbols, close to a byte each) that would
+// happen in every other group, so a lane whose chunk has many distinct symbols
+// (`dense`, only where DENSE_OK) reloads the window after four symbols.
+template <int LS, bool DENSE_OK>
 __device__ __forceinline__ void rans_group8(const uint32_t* tab, const uint32_t* lst, const uint32_t* rw, uint32_t& x, uint32_t& rq, uint32_t& s_lo,
-                                            uint32_t& s_hi) {
-    uint32_t wh, wl, used = 0;
-    const uint32_t x0 = x;
+                                            uint32_t& s_hi, bool dense) {
+    uint32_t wh, wl, used = 0, over = 0;
+    const uint32_t x0 = x, rq0 = rq;
     ring_window_be(rw, rq, wh, wl);
     s_lo = 0; s_hi = 0;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
+        if (DENSE_OK && j == 4 && dense) {
+            over = used;  // the first half must have fit its window too
+            rq += used >> 3; used = 0;
+            ring_window_be(rw, rq, wh, wl);
+        }
         uint32_t e = rans_lookup<LS>(tab, lst, x);
         const uint32_t ins = (0x3210u & ~(0xFu << (4 * (j & 3)))) | (4u << (4 * (j & 3)));  // low byte of e into byte j & 3
         if (j < 4) s_lo = __byte_perm(s_lo, e, ins); else s_hi = __byte_perm(s_hi, e, ins);
@@ -611,8 +621,8 @@ __device__ __forceinline__ void rans_group8(const uint32_t* tab, const uint32_t*
         wl <<= sh;
         used += sh;
     }
-    if (used > 64) {
-        x = x0;
+    if (used > 64 || over > 64) {
+        x = x0; rq = rq0;
         rans_short_group<LS>(tab, lst, rw, x, rq, 8, s_lo, s_hi);
     } else {
         rq += used >> 3;
@@ -662,6 +672,7 @@ __global__ void __launch_bounds__(32, 20) rans_decode_kernel_t(const DecodeItem*
     }
 
     // tables: the whole warp builds one chunk's tables at a time
+    bool dense = false;  // this lane's chunk is close to incompressible (see rans_group8)
     for (uint32_t c2 = 0; c2 < RANS_WARP_CHUNKS; ++c2) {
         const uint32_t leader = c2 * 4;
         uintptr_t psrc = __shfl_sync(0xFFFFFFFFu, reinterpret_cast<uintptr_t>(src), leader);
@@ -686,6 +697,7 @@ __global__ void __launch_bounds__(32, 20) rans_decode_kernel_t(const DecodeItem*
         }
         uint32_t total = __shfl_sync(0xFFFFFFFFu, incl, 31), distinct = __shfl_sync(0xFFFFFFFFu, rincl, 31);
         bool bad = total != 2048;  // decompress.rs:49-55
+        if (!PER_LANE && c == c2) dense = distinct >= RANS_DENSE_SYMBOLS;
         if (distinct + 2 > l_entries) bad = true;  // the host sizes the list from the planned bytes; a blob that differs from them may not fit
         if (bad) { if (c == c2) err = ST_BAD_HEADER; continue; }
         uint32_t start = incl - sum, rank = rincl - present;
@@ -769,7 +781,7 @@ __global__ void __launch_bounds__(32, 20) rans_decode_kernel_t(const DecodeItem*
             }
             fast_groups(ep, it.n, pos, remaining, [&](uint32_t& s_lo, uint32_t& s_hi) {
                 top_up();
-                rans_group8<LS>(tab, lst, rw, x, rq, s_lo, s_hi);
+                rans_group8<LS, !PER_LANE>(tab, lst, rw, x, rq, s_lo, s_hi, dense);
             });
             // tail: whatever the fast loops left
             while (remaining) {
