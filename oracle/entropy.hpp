@@ -2,6 +2,16 @@
 // byte-alphabet entropy coders of ptwm-core.  Each function cites the
 // reference file:line (paths relative to crates/ptwm-core/src) it follows.
 // Only tests, the smoke check and the bench's CPU-baseline leg may use it.
+//
+// Pinned against the reference's own vectors (tests/golden/reference): Huffman,
+// tANS, Identity and the three merges through the legacy_trimmed table,
+// Order1ScaleAC (shared prelude state, rows) and a chunked tANS plane through
+// the legacy_v1_1_0 / legacy_v1_0_0 tables, the compact reader and writer
+// through ptwc_bound_source (byte-identical rewrite), 21 self-verifying
+// compact frames, XXH64 / CRC-32 against independent implementations.
+// rANS coded payloads: parity unpinned by a stored vector (the reference keeps
+// none); encoder and decoder are restated from entropy/rans/*.rs and checked by
+// round trips over the reference's unit-test inputs.
 #pragma once
 #include <algorithm>
 #include <cstdint>

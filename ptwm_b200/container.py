@@ -20,7 +20,8 @@ from ._config import DecompressionConfig, HeaderParseError, InvalidDTypeError
 
 MAGIC_PTWS = b"\x89PTWS"
 MAGIC_PTWC = b"\x89PTWC\r\n\x1a\n"
-MAGIC_PTWM = b"\x89PTWM"
+MAGIC_PTWM = b"\x89PTWM\r\n\x1a\n"
+MAGIC_PTWX = b"\x89PTWX\r\n\x1a\n"
 
 # public dtype codes (crates/ptwm-core/src/dtype.rs:25-50)
 _TORCH_DTYPES = {1: torch.float32, 2: torch.float32, 4: torch.float16, 5: torch.float16, 6: torch.bfloat16, 13: torch.uint8, 15: torch.uint32,
@@ -135,10 +136,9 @@ class ContainerHandle:
         if n < len(MAGIC_PTWS):
             raise HeaderParseError("too short to be a .ptwm container")
         head = bytes(self._host[:9].tolist())
-        if head.startswith(MAGIC_PTWM) and not head.startswith(MAGIC_PTWC) and not head.startswith(MAGIC_PTWS):
-            raise PtwmError("legacy \\x89PTWM layout is not read by the CUDA backend; transcode to the compact layout")
-        if not (head.startswith(MAGIC_PTWS) or head.startswith(MAGIC_PTWC)):
+        if not (head.startswith(MAGIC_PTWS) or head.startswith(MAGIC_PTWC) or head.startswith(MAGIC_PTWM) or head.startswith(MAGIC_PTWX)):
             raise HeaderParseError("not a .ptwm container")
+        self._layout = "compact" if (head.startswith(MAGIC_PTWS) or head.startswith(MAGIC_PTWC)) else "legacy"
         self._h = C.c_void_p()
         _check(_lib.lib().ptwm_b200_open(self._host.data_ptr(), n, C.byref(self._h)))
         self.device = torch.cuda.current_device() if device is None else int(device)
@@ -171,7 +171,7 @@ class ContainerHandle:
     # -- inspection (handle.rs:168-227) ---------------------------------------
     @property
     def layout(self) -> str:
-        return "compact"
+        return self._layout
 
     def names(self) -> list[str]:
         return [inf["name"] for inf in self._infos]

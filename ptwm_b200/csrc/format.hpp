@@ -135,6 +135,7 @@ struct ParsedFile {
     std::vector<TensorDesc> tensors;
     std::vector<SharedState> shared;
     bool single_frame = false;
+    bool legacy = false;      // read from the legacy \x89PTWM layout
 };
 
 namespace detail {
@@ -344,7 +345,10 @@ class FileReader {
         static const uint8_t PTWS[5] = {0x89, 'P', 'T', 'W', 'S'};
         if (n_ >= 5 && !std::memcmp(b_, PTWS, 5)) return parse_frame();
         if (n_ >= 9 && !std::memcmp(b_, PTWC, 9)) return parse_container();
-        throw FormatError("not a compact .ptwm container or frame (legacy \\x89PTWM layout is not read)");
+        static const uint8_t PTWM[9] = {0x89, 'P', 'T', 'W', 'M', '\r', '\n', 0x1a, '\n'};
+        static const uint8_t PTWX[9] = {0x89, 'P', 'T', 'W', 'X', '\r', '\n', 0x1a, '\n'};
+        if (n_ >= 9 && (!std::memcmp(b_, PTWM, 9) || !std::memcmp(b_, PTWX, 9))) return parse_legacy();
+        throw FormatError("not a .ptwm container or frame");
     }
 
   private:
@@ -580,7 +584,7 @@ class FileReader {
         return std::move(out_);
     }
 
-    void parse_prelude(size_t begin, size_t end) {  // prelude.rs:66-160
+    size_t parse_prelude(size_t begin, size_t end) {  // prelude.rs:66-160; returns where the entries end
         if (end - begin < 4) throw FormatError("prelude too short");
         size_t count = le32(b_ + begin);
         if (count > (end - begin - 4) / 22) throw FormatError("prelude count exceeds buffer capacity");
@@ -600,7 +604,298 @@ class FileReader {
             s.off = pos; pos += size_t(s.len);
             out_.shared.push_back(s);
         }
+        return pos;
     }
+
+    // ---- legacy container (\x89PTWM / \x89PTWX) --------------------------------------------------
+    // header.rs:112-200, extension/table.rs:95-110, prelude.rs:66-160, chain/wire.rs:146-300,
+    // tensor_record.rs:276-440, plane_record.rs:118-260, index.rs:29-70 of the reference.  Built-in entries are
+    // recognised by their label (io.ptwm.builtin.<name>@<version>): the blake3 hash of the Extension Table and the
+    // re-derivation of built-in ids are not checked here.
+    struct LegacyEntry { uint8_t tag; uint16_t id; };  // tag 1 op, 2 codec, 0x7F anything else
+    // One Extension Table starting at `pos`; returns the position after it.
+    size_t read_legacy_table(size_t pos, size_t end, std::vector<LegacyEntry>& out) {
+        Span r(b_, pos, end, "legacy extension table");
+        uint32_t count = r.u32();
+        if (count > 65536) r.bad("entry count too large");
+        static const struct { const char* name; uint8_t tag; uint16_t id; } known[] = {
+            {"identity", 2, C_IDENTITY}, {"huffman", 2, C_HUFFMAN}, {"rans", 2, C_RANS}, {"zstd", 2, C_ZSTD}, {"tans", 2, C_TANS}, {"order1_scale_ac", 2, C_O1SAC},
+            {"source", 1, detail::OP_SOURCE}, {"bit_reorder_ieee16", 1, detail::OP_R16}, {"bit_reorder_ieee32", 1, detail::OP_R32},
+            {"bit_reorder_fp8_e4m3", 1, detail::OP_RE4M3}, {"bit_reorder_fp8_e5m2", 1, detail::OP_RE5M2}, {"byte_split", 1, detail::OP_BYTESPLIT},
+            {"nibble_split", 1, detail::OP_NIBSPLIT}, {"byte_passthrough", 1, detail::OP_PASS}};
+        for (uint32_t i = 0; i < count; ++i) {
+            r.skip(32);                                              // canonical id
+            size_t ll = size_t(r.byte()); ll |= size_t(r.byte()) << 8;
+            std::string label(reinterpret_cast<const char*>(b_ + r.skip(ll)), ll);
+            uint16_t kind = uint16_t(r.byte()); kind |= uint16_t(r.byte()) << 8;
+            r.skip(2 + 1 + 1);                                       // abi_version, lifecycle, flavor_hints
+            uint32_t cap = r.u32();
+            if (cap > (1u << 20)) r.bad("capabilities too long");
+            r.skip(cap);
+            r.byte();                                                // attestation kind
+            size_t al = size_t(r.byte()); al |= size_t(r.byte()) << 8;
+            r.skip(al);
+            size_t hl = size_t(r.byte()); hl |= size_t(r.byte()) << 8;
+            r.skip(hl);
+            r.skip(16);                                              // embedded wasm offset and length
+            LegacyEntry e{0x7F, 0xFFFF};
+            static const std::string prefix = "io.ptwm.builtin.";
+            size_t at = label.rfind('@');
+            if (label.compare(0, prefix.size(), prefix) == 0 && at != std::string::npos && at > prefix.size()) {
+                std::string name = label.substr(prefix.size(), at - prefix.size());
+                // kind: 1 Transform, 2 PlaneCodec in the reference's numbering is not relied on; the name decides
+                bool hit = false;
+                for (auto& k : known) if (name == k.name) { e = LegacyEntry{k.tag, k.id}; hit = true; }
+                if (!hit) e = LegacyEntry{uint8_t(0x7E), 0xFFFF};      // a built-in outside the hot path
+            }
+            (void)kind;
+            out.push_back(e);
+        }
+        return r.pos();
+    }
+    static size_t legacy_role_len(Span& r) {  // types/role.rs:250-345
+        uint8_t t = r.byte();
+        switch (t) {
+            case 0x00: case 0x04: case 0x07: r.byte(); return 2;
+            case 0x01: { uint8_t f = r.byte(); if (f == 1) r.byte(); else if (f != 0) r.bad("unknown value format"); return 0; }
+            case 0x02: case 0x05: r.skip(2); return 3;
+            case 0x03: case 0x08: case 0x09: return 1;
+            case 0x06: { uint8_t f = r.byte(); if (f == 1) r.skip(2); else if (f != 0) r.bad("unknown residual format"); return 0; }
+            case 0xFF: { r.skip(2); size_t l = size_t(r.byte()); l |= size_t(r.byte()) << 8; r.skip(l); return 0; }
+            default: r.bad("unknown role tag");
+        }
+    }
+    // One chain in the legacy wire starting at `pos`; returns the position after it.
+    size_t read_legacy_chain(size_t pos, size_t end, const std::vector<LegacyEntry>& table, detail::RawChain& c) {
+        Span h(b_, pos, end, "legacy chain");
+        size_t nn = h.byte(), ne = h.byte(), nt = h.byte();
+        size_t nl = size_t(h.byte()); nl |= size_t(h.byte()) << 8;
+        size_t el = size_t(h.byte()); el |= size_t(h.byte()) << 8;
+        size_t tl = size_t(h.byte()); tl |= size_t(h.byte()) << 8;
+        size_t n0 = h.skip(nl), e0 = h.skip(el), t0 = h.skip(tl);
+        if (!nn) h.bad("chain has no nodes");
+        Span nr(b_, n0, n0 + nl, "legacy chain nodes");
+        for (size_t i = 0; i < nn; ++i) {
+            size_t idx = size_t(nr.byte()); idx |= size_t(nr.byte()) << 8;
+            if (idx >= table.size()) nr.bad("node op is outside the Extension Table");
+            if (table[idx].tag == 0x7E || table[idx].tag == 0x7F) throw FormatError("chain uses a transform outside the production split/passthrough set", true);
+            if (table[idx].tag != 1) nr.bad("node op names an entry that is not a transform");
+            uint32_t pl = nr.byte();
+            detail::Node n{table[idx].id, 0, pl, table[idx].id == detail::OP_SOURCE && pl == 0};
+            n.params_off = nr.skip(pl);
+            c.nodes.push_back(n);
+        }
+        Span er(b_, e0, e0 + el, "legacy chain edges");
+        c.n_edges = ne;
+        for (size_t i = 0; i < ne; ++i) {
+            uint8_t src = er.byte(), so = er.byte(), dst = er.byte(), di = er.byte(), has_role = er.byte();
+            if (has_role > 1) er.bad("edge role_present byte has an unknown value");
+            if (has_role) legacy_role_len(er);
+            size_t vl = size_t(er.byte()); vl |= size_t(er.byte()) << 8;
+            er.skip(vl);
+            if (vl) throw FormatError("chain edge with vendor bytes", true);  // a role override only relabels the plane: nothing to do at decode
+            if (src != i || so != 0 || dst != i + 1 || di != 0) c.spine = false;
+        }
+        Span tr(b_, t0, t0 + tl, "legacy chain terminals");
+        for (size_t i = 0; i < nt; ++i) {
+            uint8_t node = tr.byte(), out = tr.byte();
+            legacy_role_len(tr);
+            c.terms.push_back({node, out});
+        }
+        return h.pos();
+    }
+    // {"shape": [...], "dtype": "..."} (metadata.rs:54-190)
+    void read_shape_metadata(size_t begin, size_t end, TensorDesc& t) {
+        Span r(b_, begin, end, "shape metadata");
+        auto head = [&](uint8_t major) -> uint64_t {
+            uint8_t f = r.byte();
+            if ((f & 0xE0) != major) r.bad("unexpected CBOR major type");
+            uint8_t a = f & 0x1F;
+            if (a < 24) return a;
+            size_t n = a == 24 ? 1 : a == 25 ? 2 : a == 26 ? 4 : a == 27 ? 8 : 0;
+            if (!n) r.bad("unsupported CBOR argument");
+            uint64_t v = 0;
+            for (size_t i = 0; i < n; ++i) v = (v << 8) | r.byte();
+            return v;
+        };
+        auto text = [&]() { uint64_t l = head(0x60); if (l > r.left()) r.bad("text string truncated"); return std::string(reinterpret_cast<const char*>(b_ + r.skip(size_t(l))), size_t(l)); };
+        if (head(0xA0) != 2) r.bad("expected a map of two pairs");
+        bool got_shape = false, got_dtype = false;
+        for (int k = 0; k < 2; ++k) {
+            std::string key = text();
+            if (key == "shape") {
+                uint64_t n = head(0x80);
+                if (n > r.left()) r.bad("shape array truncated");
+                for (uint64_t i = 0; i < n; ++i) t.shape.push_back(head(0x00));
+                got_shape = true;
+            } else if (key == "dtype") { t.dtype_name = text(); got_dtype = true; }
+            else r.bad("unknown key");
+        }
+        if (!got_shape || !got_dtype) r.bad("missing shape or dtype");
+        t.has_shape = true;
+    }
+    PlaneDesc read_legacy_plane(Span& r, uint64_t plane_len, const std::vector<LegacyEntry>& table) {
+        PlaneDesc p;
+        p.role = r.byte();
+        uint8_t pf = r.byte();
+        r.skip(2);  // codec_id: duplicates the table entry, the reader dispatches on codec_table_idx (plane_record.rs:140-148)
+        size_t idx = size_t(r.byte()); idx |= size_t(r.byte()) << 8;
+        if (idx >= table.size()) r.bad("codec_table_idx is outside the Extension Table");
+        if (table[idx].tag == 1) r.bad("codec_table_idx names a transform");
+        bool outside = table[idx].tag != 2;
+        p.codec = table[idx].id;
+        p.state_source = r.byte();
+        if (p.state_source > 3) r.bad("unknown state_source");
+        uint8_t sv = r.byte();
+        uint16_t info = uint16_t(r.byte()); info |= uint16_t(r.byte()) << 8;
+        size_t inline_len = r.u32();
+        p.payload_len = r.u64();
+        if (pf & 0x02) { p.has_crc = true; p.crc = r.u32(); }
+        std::vector<std::pair<uint32_t, uint32_t>> entries;
+        if (pf & 0x01) {
+            p.chunked = true;
+            uint32_t cnt = r.u32();
+            if (cnt > r.left() / 8) r.bad("chunk_count exceeds remaining bytes");
+            for (uint32_t i = 0; i < cnt; ++i) { uint32_t off = r.u32(), sz = r.u32(); entries.push_back({off, sz}); }
+        }
+        if (p.state_source == 3) {
+            r.byte(); uint8_t fl = r.byte();
+            size_t rl = size_t(r.byte()); rl |= size_t(r.byte()) << 8;
+            r.skip(rl); r.byte();
+            if (fl & 1) r.skip(32);
+        }
+        uint8_t layout = r.byte();
+        if (layout == 1) { p.row_len = r.u32(); if (!p.row_len) r.bad("row_len 0"); }
+        else if (layout != 0) r.bad("unknown plane layout");
+        if (p.state_source != 1 && inline_len) r.bad("inline state bytes without an inline state source");
+        uint64_t inline_off = r.skip(inline_len);
+        if (p.payload_len > r.left()) r.bad("plane payload exceeds the record");
+        p.payload_off = r.skip(size_t(p.payload_len));
+        p.decoded_len = plane_len;
+        if (outside) throw FormatError("plane codec outside the hot path", true);
+        make_chunks(p, p.chunked, entries, inline_off, inline_len, sv, info);
+        return p;
+    }
+    TensorDesc read_legacy_record(size_t begin, size_t end, const std::vector<LegacyEntry>& table, const std::vector<std::pair<uint16_t, detail::RawChain>>& registry) {
+        Span r(b_, begin, end, "legacy tensor record");
+        TensorDesc t;
+        uint16_t chain_ref = uint16_t(r.byte()); chain_ref |= uint16_t(r.byte()) << 8;
+        t.dtype_code = uint16_t(r.byte()); t.dtype_code |= uint16_t(r.byte()) << 8;
+        r.byte();  // input_format
+        size_t np = r.byte();
+        uint8_t flags = r.byte();
+        r.byte();  // reserved
+        t.orig_size = r.u64();
+        size_t nl = size_t(r.byte()); nl |= size_t(r.byte()) << 8;
+        t.name.assign(reinterpret_cast<const char*>(b_ + r.skip(nl)), nl);
+        r.skip((4 - nl % 4) % 4);
+        if (flags & 0x04) { t.has_hash = true; t.hash = r.u64(); }
+        detail::RawChain local;
+        const detail::RawChain* chain = nullptr;
+        std::vector<LegacyEntry> inline_table;
+        const std::vector<LegacyEntry>* plane_table = &table;
+        std::string chain_problem;
+        try {
+            if (chain_ref & 0x8000) {
+                size_t after = read_legacy_table(r.pos(), end, inline_table);
+                r.skip(after - r.pos());
+                after = read_legacy_chain(r.pos(), end, inline_table, local);
+                r.skip(after - r.pos());
+                chain = &local;
+            } else {
+                for (auto& e : registry) if (e.first == chain_ref) chain = &e.second;
+                if (!chain) r.bad("chain id is not in the registry");
+            }
+        } catch (const FormatError& e) { if (!e.unsupported) throw; chain_problem = e.what(); }
+        if (!chain_problem.empty()) throw FormatError(chain_problem, true);
+        if (flags & 0x01) r.bad("tensor dependencies (delta against another tensor)", true);
+        if (flags & 0x02) { uint32_t ml = r.u32(); size_t mo = r.skip(ml); read_shape_metadata(mo, mo + ml, t); }
+        detail::ChainShape sh = detail::chain_shape(*chain, b_, t.has_shape ? &t.shape : nullptr, t.dtype_code);
+        if (sh.source_len != t.orig_size) r.bad("chain Source declares a different size than orig_size");
+        t.kind = sh.kind;
+        if (np != size_t(kind_planes(sh.kind))) r.bad("plane count differs from the chain's terminals");
+        for (size_t i = 0; i < np; ++i) t.planes.push_back(read_legacy_plane(r, sh.plane_len, *plane_table));
+        return t;
+    }
+    ParsedFile parse_legacy() {
+        static const uint8_t EOFS[8] = {0x89, 'T', 'W', 'M', 'E', 'O', 'F', 0x1a};
+        if (n_ < 91 + 8) throw FormatError("legacy container: file too short");
+        if (std::memcmp(b_ + n_ - 8, EOFS, 8)) throw FormatError("legacy container: missing EOF sentinel");
+        const size_t body_end = n_ - 8;
+        uint16_t flags = uint16_t(b_[9] | (b_[10] << 8));
+        if (bool(flags & 1) != (b_[4] == 'X')) throw FormatError("legacy container: PTWX flag does not match the magic");
+        uint64_t et_off = le64(b_ + 11), et_len = le64(b_ + 19), idx_off = le64(b_ + 59), idx_len = le64(b_ + 67), pre_off = le64(b_ + 75), pre_len = le64(b_ + 83);
+        auto inside = [&](uint64_t off, uint64_t len, const char* what) {
+            if (off < 91 || off > body_end || len > body_end - off) throw FormatError(std::string("legacy container: ") + what + " section exceeds the file");
+        };
+        inside(et_off, et_len, "extension table"); inside(idx_off, idx_len, "tensor index"); inside(pre_off, pre_len, "shared prelude");
+        std::vector<LegacyEntry> table;
+        read_legacy_table(size_t(et_off), size_t(et_off + et_len), table);
+        std::vector<std::pair<uint16_t, detail::RawChain>> registry;
+        {
+            const size_t end = size_t(pre_off + pre_len);
+            size_t pos = parse_prelude(size_t(pre_off), end);
+            Span r(b_, pos, end, "legacy chain registry");
+            size_t count = size_t(r.byte()); count |= size_t(r.byte()) << 8;
+            if (count > 0x8000) r.bad("too many chains");
+            for (size_t i = 0; i < count; ++i) {
+                uint16_t id = uint16_t(r.byte()); id |= uint16_t(r.byte()) << 8;
+                detail::RawChain c;
+                size_t after;
+                try { after = read_legacy_chain(r.pos(), end, table, c); registry.push_back({id, std::move(c)}); }
+                catch (const FormatError& e) {
+                    if (!e.unsupported) throw;
+                    // a chain outside the hot path: skip its bytes, tensors that use it are reported as unsupported
+                    Span h(b_, r.pos(), end, "legacy chain");
+                    h.skip(3);
+                    size_t a = size_t(h.byte()); a |= size_t(h.byte()) << 8;
+                    size_t b = size_t(h.byte()); b |= size_t(h.byte()) << 8;
+                    size_t d = size_t(h.byte()); d |= size_t(h.byte()) << 8;
+                    h.skip(a); h.skip(b); h.skip(d);
+                    after = h.pos();
+                    unsupported_chains_.push_back(id);
+                }
+                r.skip(after - r.pos());
+            }
+        }
+        if (idx_len < 8) throw FormatError("legacy container: index section too short");
+        uint64_t count = le64(b_ + idx_off);
+        if (count > (idx_len - 8) / 24) throw FormatError("legacy container: index count exceeds the section");
+        struct Rec { uint64_t off, len; };
+        std::vector<Rec> recs;
+        for (uint64_t i = 0; i < count; ++i) {
+            const uint8_t* e = b_ + idx_off + 8 + 24 * i;
+            uint64_t off = le64(e + 8), len = le64(e + 16);
+            if (off < 91 || off > body_end || len > body_end - off) throw FormatError("legacy container: index entry points outside the file");
+            recs.push_back(Rec{off, len});
+        }
+        std::sort(recs.begin(), recs.end(), [](const Rec& a, const Rec& b) { return a.off < b.off; });  // record (write) order
+        for (const Rec& rec : recs) {
+            TensorDesc t;
+            try {
+                // a record whose chain was skipped above is unsupported, not malformed
+                uint16_t chain_ref = uint16_t(b_[rec.off] | (b_[rec.off + 1] << 8));
+                bool skipped = false;
+                if (rec.len >= 2 && !(chain_ref & 0x8000)) for (uint16_t id : unsupported_chains_) skipped |= id == chain_ref;
+                if (skipped) throw FormatError("chain outside the production split/passthrough set", true);
+                t = read_legacy_record(size_t(rec.off), size_t(rec.off + rec.len), table, registry);
+            } catch (const FormatError& e) {
+                if (!e.unsupported) throw;
+                std::string name = legacy_record_name(size_t(rec.off), size_t(rec.off + rec.len));
+                t = TensorDesc{}; t.unsupported = e.what(); t.name = name;
+            }
+            out_.tensors.push_back(std::move(t));
+        }
+        out_.legacy = true;
+        return std::move(out_);
+    }
+    std::string legacy_record_name(size_t begin, size_t end) {
+        Span r(b_, begin, end, "legacy tensor record");
+        r.skip(16);
+        size_t nl = size_t(r.byte()); nl |= size_t(r.byte()) << 8;
+        return std::string(reinterpret_cast<const char*>(b_ + r.skip(nl)), nl);
+    }
+    std::vector<uint16_t> unsupported_chains_;
 
     ParsedFile parse_frame() {  // compact.rs:321-551
         out_.single_frame = true;

@@ -1000,7 +1000,13 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
         // (length << 8) | symbol of the next code, without consuming it
         auto peek = [&]() -> uint32_t {
             uint32_t e = lut[uint32_t(cont) & ((1u << HUF_LUT_BITS) - 1)];
+#ifdef PTWM_HUF_VOTE
+            if (__any_sync(__activemask(), e == 0)) {
+                if (e == 0) e = huff_canon_decode(hc, max_bits, uint32_t(cont) & mask, HUF_LUT_BITS + 1);
+            }
+#else
             if (e == 0) e = huff_canon_decode(hc, max_bits, uint32_t(cont) & mask, HUF_LUT_BITS + 1);  // the rarest symbols, or a window no code covers
+#endif
             return e;
         };
         // one symbol with the reference's checks (decompress.rs:176-196)

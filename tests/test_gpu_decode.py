@@ -276,3 +276,20 @@ def test_larger_mixed_model_runs_the_round_loops(case):
     specs = mixed_model(scale=4)
     blob = oracle.write_container(specs, **case)
     check_container(blob, {s.name: s.raw for s in specs})
+
+
+@pytest.mark.parametrize("fixture", ["legacy_v1_1_0", "legacy_v1_0_0", "legacy_v1_0_0_native"])
+def test_legacy_fixtures_decode_to_the_reference_hashes(fixture):
+    """crates/ptwm-core/tests/legacy_fixtures.rs:65-123: the tensors of the legacy fixtures that lie on the hot path
+    (Order1ScaleAC scale planes with a shared prelude state, a two-chunk tANS plane) against the reference's table."""
+    blob = open(os.path.join(GOLD, "reference", fixture + ".ptwm"), "rb").read()
+    exp = json.load(open(os.path.join(GOLD, "reference", "expected.json")))[fixture]
+    h = ptwm_b200.ContainerHandle(blob, device=0)
+    assert h.layout == "legacy"
+    names = [t["name"] for t in h.tensor_infos() if t["supported"]]
+    assert "model.layers.2.chunked.weight" in names and ("native" in fixture or "model.layers.0.q.scale" in names)
+    for name, t in h.decode_model(names):
+        raw = bytes_of(t)
+        n, want = exp[name]
+        assert len(raw) == n and oracle.xxh64(raw) == int(want, 16), name
+    assert list(h.decode("model.layers.2.chunked.weight").shape) == [16, 32]

@@ -135,6 +135,29 @@ def test_every_byte_mutation_is_survived(L):
         assert rc < 0
 
 
+def test_legacy_fixtures_open(L):
+    """The legacy \\x89PTWM layout: records in write order, shape metadata from the CBOR map, Zstd planes and the
+    delta-coded tensor flagged as outside the hot path, the Order1ScaleAC and tANS tensors plannable."""
+    for fixture in ("legacy_v1_1_0", "legacy_v1_0_0", "legacy_v1_0_0_native"):
+        blob = open(os.path.join(GOLD, "reference", fixture + ".ptwm"), "rb").read()
+        rc, h = _open(L, blob)
+        assert rc == 0, fixture
+        infos = _infos(L, h)
+        assert [t.name.decode() for t in infos] == ["model.layers.0.q.weight", "model.layers.0.k.weight", "model.norm.weight", "model.layers.0.mlp.fp8.weight",
+                                                    "model.embed.int8", "model.layers.0.q.scale", "model.layers.0.k.scale", "model.layers.1.q.weight",
+                                                    "model.layers.2.chunked.weight"]
+        ok = {t.name.decode(): t for t in infos if t.supported}
+        want = {"model.layers.2.chunked.weight"} | ({"model.layers.0.q.scale", "model.layers.0.k.scale"} if "native" not in fixture else set())
+        assert set(ok) == want, fixture
+        t = ok["model.layers.2.chunked.weight"]
+        assert t.orig_size == 1024 and t.kind == 1 and t.dtype_name == b"bfloat16" and [t.shape[d] for d in range(t.ndim)] == [16, 32]
+        idx = (C.c_uint32 * len(ok))(*[i for i, t in enumerate(infos) if t.supported])
+        p = C.c_void_p()
+        assert L.ptwm_b200_plan_create(h, idx, len(ok), C.byref(p)) == 0
+        L.ptwm_b200_plan_destroy(p)
+        L.ptwm_b200_close(h)
+
+
 def test_bad_magic_and_short_input(L):
     for blob in (b"", b"\x89PT", b"not a container at all", b"\x89PTWM\r\n\x1a\n" + b"\x00" * 64):
         rc, h = _open(L, blob if blob else b"\x00")

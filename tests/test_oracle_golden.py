@@ -179,3 +179,40 @@ def test_writer_reproduces_reference_container_bytes():
     specs = [oracle.TensorSpec(t["name"], t["dtype_code"], t["shape"], c.decode(i)) for i, t in enumerate(c.tensors)]
     again = oracle.write_container(specs, forced_codec=oracle.IDENTITY, emit_hash=True, emit_crc=True)
     assert again == blob
+
+
+LEGACY_FIXTURES = ("legacy_v1_1_0", "legacy_v1_0_0")
+
+
+@pytest.mark.parametrize("fixture", LEGACY_FIXTURES)
+def test_order1_scale_ac_and_chunked_tans_against_legacy_fixtures(fixture):
+    """The reference's legacy fixtures (crates/ptwm-core/tests/legacy_fixtures.rs:65-123): the two scale tensors are
+    Order1ScaleAC planes with a shared prelude state and rows of 32, the chunked tensor a bf16 split with a two-chunk
+    tANS exponent plane.  Decoding them here must give the hashes the reference's own test expects."""
+    import _legacy
+    blob = open(os.path.join(REF, fixture + ".ptwm"), "rb").read()
+    exp = json.load(open(os.path.join(REF, "expected.json")))[fixture]
+    shared, tens = _legacy.shared_states(blob), _legacy.tensors(blob)
+    for name in ("model.layers.0.q.scale", "model.layers.0.k.scale"):
+        p = tens[name]["planes"][0]
+        assert p["codec"] == oracle.O1SAC and p["state_source"] == 2 and p["row_len"] == 32
+        st = shared[p["state_info"]]
+        assert st["codec"] == oracle.O1SAC
+        raw = oracle.plane_decode(oracle.O1SAC, p["payload"], tens[name]["orig_size"], state=st["state"], state_version=st["version"], row_len=32)
+        n, h = exp[name]
+        assert len(raw) == n and xxhash.xxh64(raw).hexdigest() == h
+    t = tens["model.layers.2.chunked.weight"]
+    planes = []
+    for p in t["planes"]:
+        assert p["chunks"] is not None and len(p["chunks"]) == 2
+        out = b""
+        for k, (off, decoded) in enumerate(p["chunks"]):
+            end = p["chunks"][k + 1][0] if k + 1 < len(p["chunks"]) else len(p["payload"])
+            frame = p["payload"][off:end]
+            state_len = int.from_bytes(frame[1:5], "little")
+            out += oracle.plane_decode(p["codec"], frame[5 + state_len:], decoded, state=frame[5:5 + state_len], state_version=frame[0])
+        planes.append(out)
+    assert {p["codec"] for p in t["planes"]} == {oracle.IDENTITY, oracle.TANS}
+    raw = oracle.merge_inverse(oracle.M16, planes)
+    n, h = exp["model.layers.2.chunked.weight"]
+    assert len(raw) == n and xxhash.xxh64(raw).hexdigest() == h
