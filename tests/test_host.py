@@ -158,6 +158,29 @@ def test_legacy_fixtures_open(L):
         L.ptwm_b200_close(h)
 
 
+def test_legacy_reader_survives_mutations_and_truncation(L):
+    """Every byte of the header, tables, registry and index flipped, a sample of the record bytes flipped, and every
+    7th truncation: the legacy reader answers (error or success) and never reads outside the buffer."""
+    blob = bytearray(open(os.path.join(GOLD, "reference", "legacy_v1_0_0_native.ptwm"), "rb").read())
+    et_off, et_len = (int.from_bytes(blob[o:o + 8], "little") for o in (11, 19))
+    idx_off, pre_off, pre_len = (int.from_bytes(blob[o:o + 8], "little") for o in (59, 75, 83))
+    spots = set(range(0, 91)) | set(range(et_off, et_off + et_len, 3)) | set(range(pre_off, pre_off + pre_len)) | set(range(idx_off, len(blob)))
+    spots |= set(range(pre_off + pre_len, idx_off, 5))
+    rejected = 0
+    for i in sorted(spots):
+        m = bytearray(blob)
+        m[i] ^= 0xA5
+        rc, h = _open(L, bytes(m))
+        if rc < 0:
+            rejected += 1
+        else:
+            L.ptwm_b200_close(h)
+    assert rejected > 50
+    for cut in range(0, len(blob), 7):
+        rc, h = _open(L, bytes(blob[:cut]))
+        assert rc < 0
+
+
 def test_bad_magic_and_short_input(L):
     for blob in (b"", b"\x89PT", b"not a container at all", b"\x89PTWM\r\n\x1a\n" + b"\x00" * 64):
         rc, h = _open(L, blob if blob else b"\x00")
