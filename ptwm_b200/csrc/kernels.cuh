@@ -1147,14 +1147,26 @@ __global__ void __launch_bounds__(32) tans_decode_kernel(const DecodeItem* __res
             int32_t cnt = 0;
             const uint32_t top = uint32_t(total_bits & 7);
             if (top) { --bi; cont = uint64_t(bs[bi] & ((1u << top) - 1)) << (64 - top); cnt = int32_t(top); }
+            // Words are requested one refill ahead: with a single warp per SM nothing else would hide the latency of
+            // the load.  `ahead` holds the word below the read position whenever that position is word aligned and
+            // at least four bytes are left.
+            auto word_below = [&](uint32_t at) -> uint32_t {
+                return (at >= 4 && ((reinterpret_cast<uintptr_t>(bs) + at) & 3) == 0) ? __ldg(reinterpret_cast<const uint32_t*>(bs + at - 4)) : 0u;
+            };
+            uint32_t ahead = 0;
             auto refill = [&]() {  // up to more than 32 bits, by bytes until the position is word aligned, then by words
                 while (uint32_t(cnt) <= 32u && bi > 0) {  // (a negative count only occurs in a group that is about to be decoded again)
                     if (bi >= 4 && ((reinterpret_cast<uintptr_t>(bs) + bi) & 3) == 0) {
-                        cont |= uint64_t(__ldg(reinterpret_cast<const uint32_t*>(bs + bi - 4))) << (32 - cnt);
+                        cont |= uint64_t(ahead) << (32 - cnt);
                         cnt += 32; bi -= 4;
-                    } else { --bi; cont |= uint64_t(bs[bi]) << (56 - cnt); cnt += 8; }
+                        ahead = word_below(bi);
+                    } else {
+                        --bi; cont |= uint64_t(bs[bi]) << (56 - cnt); cnt += 8;
+                        ahead = word_below(bi);
+                    }
                 }
             };
+            ahead = word_below(bi);
             auto take = [&](uint32_t nb) -> uint32_t {  // nb <= 11
                 const uint32_t hi = uint32_t(cont >> 32);
                 const uint32_t v = __funnelshift_l(hi, 0u, nb);  // the top nb bits; 0 for nb == 0
@@ -1179,7 +1191,7 @@ __global__ void __launch_bounds__(32) tans_decode_kernel(const DecodeItem* __res
             auto dec8 = [&](uint32_t& s_lo, uint32_t& s_hi) {
                 const uint64_t cont0 = cont;
                 const int32_t cnt0 = cnt;
-                const uint32_t bi0 = bi, state0 = state;
+                const uint32_t bi0 = bi, state0 = state, ahead0 = ahead;
                 int32_t lowest = 0;
                 s_lo = 0; s_hi = 0;
 #pragma unroll
@@ -1192,7 +1204,7 @@ __global__ void __launch_bounds__(32) tans_decode_kernel(const DecodeItem* __res
                     if (j < 4) s_lo = __byte_perm(s_lo, sy, ins); else s_hi = __byte_perm(s_hi, sy, ins);
                 }
                 if (lowest < 0) {
-                    cont = cont0; cnt = cnt0; bi = bi0; state = state0;
+                    cont = cont0; cnt = cnt0; bi = bi0; state = state0; ahead = ahead0;
                     s_lo = 0; s_hi = 0;
                     for (uint32_t j = 0; j < 8 && !err; ++j) {
                         uint32_t sy = one_symbol();
