@@ -363,7 +363,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--chunk", type=int, default=65536, help="plane bytes per chunk")
+    ap.add_argument("--chunk", type=int, default=32768, help="plane bytes per chunk")
     ap.add_argument("--codec", choices=["rans", "huffman", "auto", "identity"], default="rans")
     ap.add_argument("--crc", action="store_true", help="write and verify plane CRC-32s")
     ap.add_argument("--pieces", type=int, default=8, help="runs of tensors the end-to-end path copies and decodes in a pipeline")
