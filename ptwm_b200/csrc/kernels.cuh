@@ -964,26 +964,36 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
         const uint16_t* lut = lut_all + c * (1 << HUF_LUT_BITS);
         const HuffCanon hc = canon_of(c);
         Epilogue ep = make_epilogue(bases, it);
-        const uintptr_t start = reinterpret_cast<uintptr_t>(src + my_off);
-        uintptr_t rp = start + my_len;  // one past the next byte to read (moves down)
+        // Stream positions are 32-bit offsets from `org`, a 16-byte aligned address two blocks below the stream's
+        // first byte (the look-ahead fetch reaches one block below the stream), so that the compares and steps of
+        // the loop are single instructions.
+        const uintptr_t org = (reinterpret_cast<uintptr_t>(src + my_off) & ~uintptr_t(15)) - 32;
+        const uint32_t start = uint32_t(reinterpret_cast<uintptr_t>(src + my_off) - org);
+        uint32_t rp = start + my_len;  // one past the next byte to read (moves down)
         const uintptr_t lo16 = (reinterpret_cast<uintptr_t>(bases.blob) + bases.blob_first) & ~uintptr_t(15);
         const uintptr_t hi16 = (reinterpret_cast<uintptr_t>(bases.blob) + bases.blob_end + 15) & ~uintptr_t(15);
         // ring holds [fetched, ...): blocks are fetched downward
-        uintptr_t fetched = (rp + 15) & ~uintptr_t(15);
-        for (int k = 0; k < 3; ++k) { fetched -= 16; ring.put(fetched, fetch16(fetched, lo16, hi16)); }
-        uint4 pending = fetch16(fetched - 16, lo16, hi16);
+        uint32_t fetched = (rp + 15) & ~15u;
+        for (int k = 0; k < 3; ++k) { fetched -= 16; ring.put(fetched, fetch16(org + fetched, lo16, hi16)); }
+        uint4 pending = fetch16(org + fetched - 16, lo16, hi16);
 
-        uint64_t cont = 0;
+        // bit container: 64 bits kept as two words so that every shift is one funnel shift (a code has at most 11 bits)
+        uint32_t c_lo = 0, c_hi = 0;
         int32_t cnt = 0;  // bits in the container
+        auto push = [&](uint32_t w) {  // w's bits go above the cnt (<= 32) bits held
+            c_lo |= __funnelshift_lc(0u, w, uint32_t(cnt));
+            c_hi |= __funnelshift_lc(w, 0u, uint32_t(cnt));
+        };
+        auto drop = [&](uint32_t nb) { c_lo = __funnelshift_r(c_lo, c_hi, nb); c_hi >>= nb; };
         // byte steps until the read position is word aligned
-        while ((rp & 3) && rp > start) { --rp; cont |= uint64_t(ring.byte(rp)) << cnt; cnt += 8; }
+        while ((rp & 3) && rp > start) { --rp; push(ring.byte(rp)); cnt += 8; }
         const uint32_t mask = (1u << max_bits) - 1;
         uint32_t pos = seg_start, remaining = seg_len;
         // The lanes of a warp drain at similar rates: when any active lane runs low, every lane with room refills,
         // so the refill code runs once per several groups instead of (for some lane) in every one.
         auto ring_top_up = [&]() {
             if (__any_sync(__activemask(), rp - fetched < 32 && fetched > start)) {
-                if (rp - fetched <= 48 && fetched > start) { fetched -= 16; ring.put(fetched, pending); pending = fetch16(fetched - 16, lo16, hi16); }
+                if (rp - fetched <= 48 && fetched > start) { fetched -= 16; ring.put(fetched, pending); pending = fetch16(org + fetched - 16, lo16, hi16); }
             }
         };
         // one aligned word (or the last partial one) into the bit container when it holds at most 32 bits
@@ -992,21 +1002,15 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
                 uint32_t w = __byte_perm(ring.word(rp - 4), 0, 0x0123);  // byte rp-1 becomes the lowest
                 uint32_t take = rp - start >= 4 ? 4u : uint32_t(rp - start);
                 if (take < 4) w &= (1u << (8 * take)) - 1;
-                cont |= uint64_t(w) << cnt;
+                push(w);
                 cnt += 8 * int32_t(take);
                 rp -= take;
             }
         };
         // (length << 8) | symbol of the next code, without consuming it
         auto peek = [&]() -> uint32_t {
-            uint32_t e = lut[uint32_t(cont) & ((1u << HUF_LUT_BITS) - 1)];
-#ifdef PTWM_HUF_VOTE
-            if (__any_sync(__activemask(), e == 0)) {
-                if (e == 0) e = huff_canon_decode(hc, max_bits, uint32_t(cont) & mask, HUF_LUT_BITS + 1);
-            }
-#else
-            if (e == 0) e = huff_canon_decode(hc, max_bits, uint32_t(cont) & mask, HUF_LUT_BITS + 1);  // the rarest symbols, or a window no code covers
-#endif
+            uint32_t e = lut[c_lo & ((1u << HUF_LUT_BITS) - 1)];
+            if (e == 0) e = huff_canon_decode(hc, max_bits, c_lo & mask, HUF_LUT_BITS + 1);  // the rarest symbols, or a window no code covers
             return e;
         };
         // one symbol with the reference's checks (decompress.rs:176-196)
@@ -1015,7 +1019,7 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
             uint32_t e = peek();
             int32_t nb = int32_t(e >> 8);
             if (nb > cnt) { err = ST_STREAM_UNDERRUN; nb = cnt; }
-            cont >>= nb; cnt -= nb;
+            drop(uint32_t(nb)); cnt -= nb;
             return e;
         };
         // Eight symbols in two halves.  After a refill the container holds more than 32 bits (unless the stream is
@@ -1024,9 +1028,9 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
         // decoded again one symbol at a time.
         auto dec8 = [&](uint32_t& s_lo, uint32_t& s_hi) {
             ring_top_up();
-            const uint64_t cont0 = cont;
+            const uint32_t lo0 = c_lo, hi0 = c_hi;
             const int32_t cnt0 = cnt;
-            const uintptr_t rp0 = rp;
+            const uint32_t rp0 = rp;
             int32_t lowest = 0;
             s_lo = 0; s_hi = 0;
 #pragma unroll
@@ -1034,12 +1038,12 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
                 if ((j & 3) == 0) take_word();
                 uint32_t e = peek();
                 const uint32_t nb = e >> 8;
-                cont >>= nb; cnt -= int32_t(nb); lowest |= cnt;
+                drop(nb); cnt -= int32_t(nb); lowest |= cnt;
                 const uint32_t ins = (0x3210u & ~(0xFu << (4 * (j & 3)))) | (4u << (4 * (j & 3)));  // low byte of e into byte j & 3
                 if (j < 4) s_lo = __byte_perm(s_lo, e, ins); else s_hi = __byte_perm(s_hi, e, ins);
             }
             if (lowest < 0) {
-                cont = cont0; cnt = cnt0; rp = rp0;
+                c_lo = lo0; c_hi = hi0; cnt = cnt0; rp = rp0;
                 s_lo = 0; s_hi = 0;
                 for (uint32_t j = 0; j < 8; ++j) {
                     uint32_t sym = one_symbol() & 0xFFu;
@@ -1063,11 +1067,11 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
         // every stream must end with no unread byte and only zero bits left
         // (decompress.rs:140-144, bitstream.rs:184-186)
         while (rp > start && !err) {
-            if (rp - fetched < 32 && fetched > start) { fetched -= 16; ring.put(fetched, pending); pending = fetch16(fetched - 16, lo16, hi16); }
+            if (rp - fetched < 32 && fetched > start) { fetched -= 16; ring.put(fetched, pending); pending = fetch16(org + fetched - 16, lo16, hi16); }
             --rp;
             if (ring.byte(rp)) err = ST_NOT_CONSUMED;
         }
-        if (!err && cont != 0) err = ST_NOT_CONSUMED;
+        if (!err && (c_lo | c_hi) != 0) err = ST_NOT_CONSUMED;
     }
     if (err) atomicMax(&status[it.id], err);
 }
