@@ -300,6 +300,33 @@ def run_ours(args):
         del decoded, h2
     e2e_s = statistics.mean(e2e_times)
 
+    # ---- optional: the same container as a file (page cache warm) -> load_file --------------------------------
+    file_load = None
+    if args.file_dir and world == 1:
+        path = os.path.join(args.file_dir, f"ptwm_b200_bench_{os.getpid()}.ptwm")
+        try:
+            with open(path, "wb") as f:
+                f.write(memoryview(host_blob.numpy()))
+            times, info = [], {}
+            for it in range(args.warmup + args.steps):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                state = ptwm_b200.load_file(path, local, pieces=args.pieces, verify=bool(args.crc), threads=args.file_threads, timings=info)
+                torch.cuda.synchronize()
+                if it >= args.warmup:
+                    times.append(time.perf_counter() - t0)
+                if it == 0 and not args.no_check:
+                    probe = infos[len(infos) // 2]["name"]
+                    if not torch.equal(state[probe].view(torch.uint8).reshape(-1), plan.views(out)[mine.index(len(infos) // 2)].view(torch.uint8).reshape(-1)):
+                        raise SystemExit("load_file: decoded tensor differs from the device-resident decode")
+                del state
+            sec = statistics.mean(times)
+            file_load = {"value": my_raw / sec / 1e9, "unit": "GB/s", "ms": sec * 1e3, "parse_ms": info.get("parse_ms"), "threads": args.file_threads,
+                         "file_bytes": int(compressed), "includes": "load_file(path): file -> pinned staging -> GPU in 128 MiB slices, started before the parse of the mapped file; arrived pieces are decoded while the rest is read"}
+        finally:
+            if os.path.exists(path):
+                os.remove(path)
+
     totals = torch.tensor([float(my_raw), float(hi - lo), float(plan.bytes_read), float(plan.launches)], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(totals, op=dist.ReduceOp.SUM)
@@ -331,6 +358,8 @@ def run_ours(args):
                         "includes": "ContainerHandle(pinned host bytes).decode_model_streamed: parse, then per piece plan + H2D copy + decode + status read-back, copies overlapping the rest"},
                 "gpu_launches": int(total_launches) * args.steps, "setup_s": round(setup_s, 1),
                 "plane_codecs": sorted({str(v) for v in codecs.values()})}
+        if file_load:
+            line["file_load"] = file_load
         if args.workload != "llama8b":
             line["config"]["workload"] = "16 x bf16 [4096,4096] (profiling case)"
         if world == 1 and not args.no_cpu and args.workload == "llama8b":
@@ -370,6 +399,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer transformer layers than 32 (for quick checks; not the benchmark workload)")
     ap.add_argument("--cpu-layers", type=int, default=4, help="layers in the CPU baseline sample")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--file-dir", default="", help="also write the container to a file in this directory and time ptwm_b200.load_file on it (extra key file_load; N=1 only)")
+    ap.add_argument("--file-threads", type=int, default=16, help="reader threads of load_file")
     ap.add_argument("--no-check", action="store_true", help="skip the parity check (only for timing experimental kernel builds; never for a reported number)")
     ap.add_argument("--workload", choices=["llama8b", "c1x16"], default="llama8b", help="c1x16: small case for profiler captures, not a benchmark line")
     args = ap.parse_args()

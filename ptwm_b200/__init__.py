@@ -7,7 +7,9 @@ sm_100a plus the host container parser and planner).  See
 from ._config import DecompressionConfig, HeaderParseError, InvalidDTypeError
 from ._lib import EXPORTED_SYMBOLS, LIB_PATH, build
 from .compressor import CompressionConfig, EncodedContainer, compress_model
+from .loader import PtwmIndex, SafeOpen, load_file, plan_shards, read_sharded_ptwm, save_sharded, shard_filename, write_mode_b_shell
 from .container import NO_SYNC, TIME_KERNELS, VERIFY_CRC, VERIFY_HASH, ContainerHandle, DecodePlan, Decompressor, PtwmError, TensorIndex
 
 __all__ = ["CompressionConfig", "EncodedContainer", "compress_model", "DecompressionConfig", "HeaderParseError", "InvalidDTypeError", "EXPORTED_SYMBOLS", "LIB_PATH", "build", "ContainerHandle",
-           "DecodePlan", "Decompressor", "PtwmError", "TensorIndex", "VERIFY_CRC", "VERIFY_HASH", "NO_SYNC", "TIME_KERNELS"]
+           "DecodePlan", "Decompressor", "PtwmError", "TensorIndex", "PtwmIndex", "SafeOpen", "load_file", "plan_shards", "read_sharded_ptwm", "save_sharded",
+           "shard_filename", "write_mode_b_shell", "VERIFY_CRC", "VERIFY_HASH", "NO_SYNC", "TIME_KERNELS"]

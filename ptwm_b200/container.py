@@ -162,6 +162,23 @@ class ContainerHandle:
         self._blob_dev: Optional[torch.Tensor] = None
         self._plans: dict = {}
 
+    @classmethod
+    def from_file(cls, path, skip_missing: bool = False, device: Optional[int] = None, verify: bool = True) -> "ContainerHandle":
+        """Open a container file through a private read-only mapping: the
+        parser reads the page cache in place, nothing is copied until a decode
+        sends the bytes it needs to the GPU."""
+        import mmap
+        with open(path, "rb") as f:
+            size = f.seek(0, 2)
+            if size == 0:
+                raise HeaderParseError("too short to be a .ptwm container")
+            # ACCESS_COPY gives the writable buffer torch.frombuffer asks for; no page is ever written
+            mm = mmap.mmap(f.fileno(), 0, access=mmap.ACCESS_COPY)
+        self = cls(torch.frombuffer(mm, dtype=torch.uint8), skip_missing, device, verify)
+        self._mmap = mm
+        self.path = Path(path)
+        return self
+
     def __del__(self):
         self._plans = {}
         if getattr(self, "_h", None):
@@ -339,10 +356,11 @@ class TensorIndex:
 
     def __init__(self, path, device: Optional[int] = None, verify: bool = True) -> None:
         self._path = Path(path)
-        blob = self._path.read_bytes()
-        if not (blob.startswith(MAGIC_PTWC) or blob.startswith(MAGIC_PTWM)):
+        with open(self._path, "rb") as f:
+            head = f.read(9)
+        if not (head.startswith(MAGIC_PTWC) or head.startswith(MAGIC_PTWM) or head.startswith(MAGIC_PTWX)):
             raise ValueError(f"{self._path} is not a .ptwm container")
-        self._handle = ContainerHandle(blob, device=device, verify=verify)
+        self._handle = ContainerHandle.from_file(self._path, device=device, verify=verify)
         self._names = self._handle.names()
 
     @classmethod
