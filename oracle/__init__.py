@@ -231,6 +231,7 @@ def role_mantissa(i, of):
 
 # Op wire ids (transforms/op.rs:11-36)
 OP_SOURCE, OP_R16, OP_R32, OP_RE4M3, OP_RE5M2, OP_BSPLIT, OP_NSPLIT, OP_PASS = 0, 0x10, 0x11, 0x12, 0x13, 0x20, 0x21, 0x30
+OP_INTDELTA, OP_MZS = 0x52, 0x64
 
 # Record role byte per terminal role (compressor.rs:124-147)
 _PLANE_ROLE = {ROLE_SCALE_E8M0: 2, ROLE_SCALE_E4M3: 2, ROLE_GLOBAL_F32: 2, ROLE_NIB_EXP: 3, ROLE_NIB_SM: 4, ROLE_FP4: 1, ROLE_EXP: 3, ROLE_INT8: 1}
@@ -253,6 +254,9 @@ class TensorSpec:
     raw: bytes
     usage: str = "standard"
     input_format: int = 2  # Format.TORCH (python/ptwm/_config.py)
+    # per-plane op between a byte split and its terminal, {plane: ("intdelta",) | ("mzs", k)}
+    # (python/ptwm/preprocessing/_chains.py:360-389,486-560)
+    post: Optional[dict] = None
 
 
 def source_params(shape, chain_dtype) -> bytes:
@@ -292,20 +296,55 @@ def bound_params(shape, dtype_code) -> Optional[bytes]:
     return source_params(shape, cd)
 
 
-def write_cw2(nodes, roles, term_node, bound: Optional[bytes], deferred: bool, op_ref) -> bytes:
-    """chain/wire_compact.rs:140-245 for a linear spine chain."""
-    n = len(nodes)
-    out = bytearray(varint(n) + varint(n - 1) + varint(len(roles)))
+def chain_graph(spec: TensorSpec):
+    """chain_for plus the spec's per-plane ops -> (kind, nodes, edges [(src, out, dst, in)], terminals [(node, out, role)])."""
+    kind, nodes, roles = chain_for(spec)
+    nodes = list(nodes)
+    edges = [(i, 0, i + 1, 0) for i in range(len(nodes) - 1)]
+    terms = [(len(nodes) - 1, i, role) for i, role in enumerate(roles)]
+    for plane in sorted(spec.post or {}):
+        op = spec.post[plane]
+        if kind not in (M16, M32) or not 0 <= plane < len(roles):
+            raise ValueError("per-plane ops go on the planes of a byte split")
+        nodes.append((OP_INTDELTA, b"") if op[0] == "intdelta" else (OP_MZS, bytes([op[1]])))
+        edges.append((2, plane, len(nodes) - 1, 0))
+        terms[plane] = (len(nodes) - 1, 0, roles[plane])
+    return kind, nodes, edges, terms
+
+
+def post_forward(spec: TensorSpec, plane_index: int, plane: bytes) -> bytes:
+    """transforms/int_delta.rs:36-44 (byte width) and transforms/mantissa_zero.rs forward on one terminal plane."""
+    op = (spec.post or {}).get(plane_index)
+    if op is None:
+        return plane
+    import numpy as np
+    a = np.frombuffer(plane, dtype=np.uint8)
+    if op[0] == "intdelta":
+        return np.diff(a, prepend=np.uint8(0)).astype(np.uint8).tobytes()
+    k = int(op[1])
+    if (a & ((1 << k) - 1)).any():
+        raise ValueError("MantissaZeroStrip: plane has a byte with non-zero low bits")
+    return (a >> k).astype(np.uint8).tobytes()
+
+
+def write_cw2(nodes, terms, edges, bound: Optional[bytes], deferred: bool, op_ref) -> bytes:
+    """chain/wire_compact.rs:140-245: leading edges of the form (i, 0) -> (i + 1, 0) are the spine and only counted."""
+    out = bytearray(varint(len(nodes)) + varint(len(edges)) + varint(len(terms)))
     for op, params in nodes:
         out += varint(op_ref(op))
         if op == OP_SOURCE and ((deferred and params == b"") or (not deferred and bound is not None and params == bound)):
             out += varint(0)
             continue
         out += varint(len(params)) + params
-    if n - 1 > 0:
-        out += varint(n - 1)  # every edge is a spine edge
-    for i, role in enumerate(roles):
-        out += bytes([(term_node << 4) | i, role])
+    if edges:
+        spine = 0
+        while spine < len(edges) and tuple(edges[spine]) == (spine, 0, spine + 1, 0):
+            spine += 1
+        out += varint(spine)
+        for e in edges[spine:]:
+            out += b"".join(varint(v) for v in e) + b"\x00"
+    for node, o, role in terms:
+        out += bytes([(node << 4) | o, role])
     return bytes(out)
 
 
@@ -352,16 +391,17 @@ def write_container(specs: Sequence[TensorSpec], *, chunk_size: Optional[int] = 
     plans = []
     registry: list = []  # [(nodes, roles)] after binding
     for s in specs:
-        kind, nodes, roles = chain_for(s)
+        kind, nodes, edges, terms = chain_graph(s)
+        roles = [t[2] for t in terms]
         if len(s.raw) != int.__mul__(_ELEM[s.dtype_code], _prod(s.shape)):
             raise ValueError(f"{s.name}: raw length does not match shape × dtype")
         bp = bound_params(s.shape, s.dtype_code)
         if bp is not None and nodes[0][1] == bp:
             nodes = [(OP_SOURCE, b"")] + nodes[1:]
-        key = (tuple(nodes), tuple(roles))
+        key = (tuple(nodes), tuple(edges), tuple(terms))
         if key not in registry:
             registry.append(key)
-        planes = split_forward(kind, s.raw)
+        planes = [post_forward(s, i, p) for i, p in enumerate(split_forward(kind, s.raw))]
         src_row = s.shape[-1] if len(s.shape) else 0
         chosen = []
         for plane, role in zip(planes, roles):
@@ -376,7 +416,7 @@ def write_container(specs: Sequence[TensorSpec], *, chunk_size: Optional[int] = 
 
     # Extension Table: chain ops in registry order, then the used codecs in built-in order (container.rs:167-223).
     table: list = []
-    for nodes, _ in registry:
+    for nodes, _e, _t in registry:
         for op, _p in nodes:
             if (1, op) not in table:
                 table.append((1, op))
@@ -389,8 +429,8 @@ def write_container(specs: Sequence[TensorSpec], *, chunk_size: Optional[int] = 
         et += bytes([tag]) + varint(wid)
     prelude = (0).to_bytes(4, "little")
     reg = bytearray(varint(len(registry)))
-    for nodes, roles in registry:
-        cb = write_cw2(list(nodes), list(roles), len(nodes) - 1, None, True, lambda op: table.index((1, op)))
+    for nodes, edges, terms in registry:
+        cb = write_cw2(list(nodes), list(terms), list(edges), None, True, lambda op: table.index((1, op)))
         reg += varint(len(cb)) + cb
 
     body, index = bytearray(), bytearray(varint(len(plans)))
@@ -448,7 +488,8 @@ def _prod(shape):
 def write_compact(spec: TensorSpec, *, menu: Sequence[int] = (IDENTITY, HUFFMAN, RANS, TANS, O1SAC), forced_codec: Optional[int] = None,
                   emit_hash: bool = False, emit_crc: bool = False) -> bytes:
     """compress_compact (compact.rs:175-312): one tensor as a \\x89PTWS frame."""
-    kind, nodes, roles = chain_for(spec)
+    kind, nodes, edges, terms = chain_graph(spec)
+    roles = [t[2] for t in terms]
     raw = spec.raw
     out = bytearray(b"\x89PTWS")
     flags = 0x04
@@ -459,9 +500,9 @@ def write_compact(spec: TensorSpec, *, menu: Sequence[int] = (IDENTITY, HUFFMAN,
         hdr += xxh64(raw).to_bytes(8, "little")
     plane_crc = emit_crc and not emit_hash
     bp = bound_params(spec.shape, spec.dtype_code)
-    body = bytearray(write_cw2(nodes, roles, len(nodes) - 1, bp, False, lambda op: op))
+    body = bytearray(write_cw2(nodes, terms, edges, bp, False, lambda op: op))
     src_row = spec.shape[-1] if len(spec.shape) else 0
-    for plane, role in zip(split_forward(kind, raw), roles):
+    for plane, role in zip([post_forward(spec, i, p) for i, p in enumerate(split_forward(kind, raw))], roles):
         row_len = src_row if kind == PASS else 0
         if forced_codec is not None:
             codec = forced_codec

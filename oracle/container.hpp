@@ -67,7 +67,7 @@ inline void write_varint(Bytes& out, uint64_t v) {  // varint.rs:17-23
 
 // transforms/op.rs:11-36
 enum OpId : uint16_t { OP_SOURCE = 0x0000, OP_REORDER16 = 0x0010, OP_REORDER32 = 0x0011, OP_REORDER_E4M3 = 0x0012, OP_REORDER_E5M2 = 0x0013,
-                      OP_BYTESPLIT = 0x0020, OP_NIBBLESPLIT = 0x0021, OP_PASSTHROUGH = 0x0030 };
+                      OP_BYTESPLIT = 0x0020, OP_NIBBLESPLIT = 0x0021, OP_PASSTHROUGH = 0x0030, OP_INTDELTA = 0x0052, OP_MANTISSA_ZERO_STRIP = 0x0064 };
 
 struct ChainNode { uint16_t op; Bytes params; };
 struct ChainEdge { uint8_t src, src_out, dst, dst_in; };
@@ -164,11 +164,35 @@ inline bool bound_source_params(const std::vector<uint64_t>& shape, uint16_t dty
     return true;
 }
 
-struct ChainInfo { MergeKind kind; uint64_t source_len; uint64_t plane_len; uint64_t row_len; /* Source last dim, 0 = scalar */ };
+// A per-plane op between the split and the terminal (python/ptwm/preprocessing/_chains.py:360-389,486-534).
+enum PostOp : uint8_t { POST_NONE = 0, POST_INTDELTA = 1, POST_MZS = 2 };
+struct ChainInfo {
+    MergeKind kind; uint64_t source_len; uint64_t plane_len; uint64_t row_len; /* Source last dim, 0 = scalar */
+    uint8_t post[4] = {0, 0, 0, 0};    // PostOp of terminal plane i
+    uint8_t post_k[4] = {0, 0, 0, 0};  // MantissaZeroStrip: bits stripped
+};
+
+// transforms/int_delta.rs:36-44 at byte width (the split planes are byte planes): out[i] = in[i] - in[i-1], wrapping.
+inline void int_delta_forward_u8(Bytes& b) { uint8_t prev = 0; for (auto& v : b) { uint8_t cur = v; v = uint8_t(cur - prev); prev = cur; } }
+inline void int_delta_inverse_u8(Bytes& b) { uint8_t acc = 0; for (auto& v : b) { acc = uint8_t(acc + v); v = acc; } }
+// transforms/mantissa_zero.rs:38-44: forward shifts every byte right by k (all low k bits must be zero), inverse shifts left.
+inline void mzs_forward(Bytes& b, unsigned k) {
+    for (auto v : b) if (v & ((1u << k) - 1)) throw Error("MantissaZeroStrip.forward: plane has a byte with non-zero low bits");
+    for (auto& v : b) v = uint8_t(v >> k);
+}
+inline void mzs_inverse(Bytes& b, unsigned k) { for (auto& v : b) v = uint8_t(v << k); }
+inline void post_forward(const ChainInfo& info, size_t plane, Bytes& b) {
+    if (info.post[plane] == POST_INTDELTA) int_delta_forward_u8(b); else if (info.post[plane] == POST_MZS) mzs_forward(b, info.post_k[plane]);
+}
+inline void post_inverse(const ChainInfo& info, size_t plane, Bytes& b) {
+    if (info.post[plane] == POST_INTDELTA) int_delta_inverse_u8(b); else if (info.post[plane] == POST_MZS) mzs_inverse(b, info.post_k[plane]);
+}
 
 // Source params (transforms/source.rs:120-178) + the descriptor walk of
 // chain/runtime.rs:359-439 restricted to the production chains
-// (python/ptwm/preprocessing/_chains.py:320-357,610-727).
+// (python/ptwm/preprocessing/_chains.py:320-357,610-727) and their variants
+// with IntDelta or MantissaZeroStrip on single planes of a byte split
+// (_chains.py:360-389,486-560).
 inline ChainInfo analyse_chain(const Chain& c) {
     if (c.nodes.empty() || c.nodes[0].op != OP_SOURCE) throw Error("chain: node[0] must be Source");
     const Bytes& sp = c.nodes[0].params;
@@ -181,26 +205,48 @@ inline ChainInfo analyse_chain(const Chain& c) {
     }
     uint16_t cd = uint16_t(sp[sp.size() - 2] | (sp[sp.size() - 1] << 8));
     ChainInfo info{PASS, n_elem * chain_dtype_bytes(cd), 0, sp[0] ? last : 0};
-    for (size_t i = 0; i < c.edges.size(); ++i) {
+    if (c.edges.size() + 1 != c.nodes.size()) throw Error("unsupported: chain is not a tree over its nodes");
+    const size_t nn = c.nodes.size();
+    // nodes after a byte split: each takes one output of the split (node 2) and feeds one terminal
+    const bool split16 = nn >= 3 && c.nodes[1].op == OP_REORDER16 && c.nodes[2].op == OP_BYTESPLIT && c.nodes[2].params == Bytes{2};
+    const bool split32 = nn >= 3 && c.nodes[1].op == OP_REORDER32 && c.nodes[2].op == OP_BYTESPLIT && c.nodes[2].params == Bytes{4};
+    const size_t spine = (split16 || split32) ? 2 : c.edges.size();
+    for (size_t i = 0; i < spine; ++i) {
         const ChainEdge& e = c.edges[i];
         if (e.src != i || e.src_out != 0 || e.dst != i + 1 || e.dst_in != 0) throw Error("unsupported: chain is not a linear spine");
     }
-    if (c.edges.size() + 1 != c.nodes.size()) throw Error("unsupported: chain is not a linear spine");
     auto terms_are = [&](size_t node, size_t n) {
         if (c.terms.size() != n) return false;
         for (size_t i = 0; i < n; ++i) if (c.terms[i].node != node || c.terms[i].out != i) return false;
         return true;
     };
-    size_t nn = c.nodes.size();
+    if (split16 || split32) {
+        const size_t np = split16 ? 2 : 4;
+        if (info.source_len % np) throw Error(split16 ? "chain: 16-bit split of an odd length" : "chain: 32-bit split of a length not divisible by 4");
+        info.kind = split16 ? M16 : M32; info.plane_len = info.source_len / np;
+        int node_of_plane[4] = {-1, -1, -1, -1};
+        for (size_t i = 2; i < c.edges.size(); ++i) {
+            const ChainEdge& e = c.edges[i];
+            if (e.src != 2 || e.src_out >= np || e.dst < 3 || e.dst >= nn || e.dst_in != 0 || node_of_plane[e.src_out] >= 0)
+                throw Error("unsupported: chain outside the production split/passthrough set");
+            for (size_t j = 2; j < i; ++j) if (c.edges[j].dst == e.dst) throw Error("unsupported: chain outside the production split/passthrough set");
+            const ChainNode& nd = c.nodes[e.dst];
+            if (nd.op == OP_INTDELTA && nd.params.empty()) info.post[e.src_out] = POST_INTDELTA;
+            else if (nd.op == OP_MANTISSA_ZERO_STRIP && nd.params.size() == 1 && nd.params[0] >= 1 && nd.params[0] <= 7) { info.post[e.src_out] = POST_MZS; info.post_k[e.src_out] = nd.params[0]; }
+            else throw Error("unsupported: chain outside the production split/passthrough set");
+            node_of_plane[e.src_out] = e.dst;
+        }
+        if (c.terms.size() != np) throw Error("unsupported: chain outside the production split/passthrough set");
+        for (size_t i = 0; i < np; ++i) {
+            const bool direct = node_of_plane[i] < 0 && c.terms[i].node == 2 && c.terms[i].out == i;
+            const bool via = node_of_plane[i] >= 0 && c.terms[i].node == node_of_plane[i] && c.terms[i].out == 0;
+            if (!direct && !via) throw Error("unsupported: chain outside the production split/passthrough set");
+        }
+        return info;
+    }
     if (nn == 1 && terms_are(0, 1)) { info.kind = PASS; info.plane_len = info.source_len; }
     else if (nn == 2 && c.nodes[1].op == OP_PASSTHROUGH && terms_are(1, 1)) { info.kind = PASS; info.plane_len = info.source_len; }
-    else if (nn == 3 && c.nodes[1].op == OP_REORDER16 && c.nodes[2].op == OP_BYTESPLIT && c.nodes[2].params == Bytes{2} && terms_are(2, 2)) {
-        if (info.source_len % 2) throw Error("chain: 16-bit split of an odd length");
-        info.kind = M16; info.plane_len = info.source_len / 2;
-    } else if (nn == 3 && c.nodes[1].op == OP_REORDER32 && c.nodes[2].op == OP_BYTESPLIT && c.nodes[2].params == Bytes{4} && terms_are(2, 4)) {
-        if (info.source_len % 4) throw Error("chain: 32-bit split of a length not divisible by 4");
-        info.kind = M32; info.plane_len = info.source_len / 4;
-    } else if (nn == 3 && c.nodes[1].op == OP_REORDER_E4M3 && c.nodes[2].op == OP_NIBBLESPLIT && terms_are(2, 2)) { info.kind = FP8_E4M3; info.plane_len = info.source_len; }
+    else if (nn == 3 && c.nodes[1].op == OP_REORDER_E4M3 && c.nodes[2].op == OP_NIBBLESPLIT && terms_are(2, 2)) { info.kind = FP8_E4M3; info.plane_len = info.source_len; }
     else if (nn == 3 && c.nodes[1].op == OP_REORDER_E5M2 && c.nodes[2].op == OP_NIBBLESPLIT && terms_are(2, 2)) { info.kind = FP8_E5M2; info.plane_len = info.source_len; }
     else throw Error("unsupported: chain outside the production split/passthrough set");
     return info;
@@ -519,7 +565,8 @@ inline Bytes decode_record(const Container& c, const TensorRec& t, bool verify =
             out = plane_decode(cid, sv, state, sl, p.payload, p.payload_len, p.row_len, size_t(info.plane_len), size_t(info.plane_len));
             if (out.size() != info.plane_len) throw Error("decoded plane length differs from its descriptor");
         }
-        if (verify && p.has_crc && crc32(out.data(), out.size()) != p.crc) throw Error("plane CRC mismatch");
+        if (verify && p.has_crc && crc32(out.data(), out.size()) != p.crc) throw Error("plane CRC mismatch");  // of the terminal's bytes
+        post_inverse(info, pi, out);
     }
     Bytes raw = merge_inverse(info.kind, planes);
     if (raw.size() != t.orig_size) throw Error("decode_tensor: chain decoded a different length than orig_size");
@@ -596,6 +643,7 @@ inline CompactTensor decode_compact(const uint8_t* buf, size_t len) {
             Bytes d = plane_decode(cid, sv, st, sl, payload, pl, row_len, size_t(info.plane_len), size_t(info.plane_len));
             if (d.size() != info.plane_len) r.fail("plane decoded to a different length than the chain says");
             if (has_crc && crc32(d.data(), d.size()) != crc) r.fail("plane CRC mismatch");
+            post_inverse(info, size_t(pi), d);
             planes.push_back(std::move(d));
         }
         t.raw = merge_inverse(info.kind, planes);

@@ -104,6 +104,7 @@ struct PlaneDesc {
     uint16_t codec = 0;
     uint8_t role = 0;
     uint8_t state_source = 0;
+    uint8_t post = 0, post_k = 0;  // op between the split and this terminal (detail::POST_*), bits stripped by MantissaZeroStrip
     uint64_t row_len = 0;
     bool has_crc = false;
     uint32_t crc = 0;
@@ -141,16 +142,19 @@ struct ParsedFile {
 namespace detail {
 
 struct Node { uint16_t op; uint64_t params_off; uint32_t params_len; bool bound; };
-struct ChainShape { uint8_t kind; uint64_t source_len, plane_len, row_len; };
+// A plane may pass through one more op between the split and its terminal (python/ptwm/preprocessing/_chains.py:360-389,
+// 486-560): IntDelta (transforms/int_delta.rs, byte width on split planes) or MantissaZeroStrip(k) (transforms/mantissa_zero.rs).
+struct ChainShape { uint8_t kind; uint64_t source_len, plane_len, row_len; uint8_t post[4] = {0, 0, 0, 0}; uint8_t post_k[4] = {0, 0, 0, 0}; };
 
 // transforms/op.rs:11-36
-enum : uint16_t { OP_SOURCE = 0, OP_R16 = 0x10, OP_R32 = 0x11, OP_RE4M3 = 0x12, OP_RE5M2 = 0x13, OP_BYTESPLIT = 0x20, OP_NIBSPLIT = 0x21, OP_PASS = 0x30 };
+enum : uint16_t { OP_SOURCE = 0, OP_R16 = 0x10, OP_R32 = 0x11, OP_RE4M3 = 0x12, OP_RE5M2 = 0x13, OP_BYTESPLIT = 0x20, OP_NIBSPLIT = 0x21, OP_PASS = 0x30,
+                  OP_INTDELTA = 0x52, OP_MZS = 0x64 };
 
 struct RawChain {
     std::vector<Node> nodes;
     std::vector<std::pair<uint8_t, uint8_t>> terms;  // (node, output)
-    bool spine = true;
-    size_t n_edges = 0;
+    struct Edge { uint8_t src, src_out, dst, dst_in; };
+    std::vector<Edge> edges;  // spine edges written out like the others
 };
 
 // chain/wire_compact.rs:258-372.  resolve(op_ref) -> op wire id.
@@ -169,9 +173,9 @@ RawChain read_cw2(Span& r, F resolve) {
         n.params_off = r.skip(pl);
         c.nodes.push_back(n);
     }
-    c.n_edges = ne;
     if (ne) {
         size_t spine = size_t(r.var_max(ne, "chain spine edge count"));
+        for (size_t i = 0; i < spine; ++i) c.edges.push_back({uint8_t(i), 0, uint8_t(i + 1), 0});
         for (size_t i = spine; i < ne; ++i) {
             uint8_t idx[4];
             for (auto& v : idx) v = uint8_t(r.var_max(255, "chain edge index"));
@@ -179,7 +183,7 @@ RawChain read_cw2(Span& r, F resolve) {
             if (etag & ~3u) r.bad("chain edge tag has unknown bits");
             if (etag) r.bad("chain edge with a role override or vendor bytes", true);
             if (i == spine && idx[0] == i && idx[1] == 0 && idx[2] == i + 1 && idx[3] == 0) r.bad("chain spine edge stored explicitly (non-canonical)");
-            c.spine = false;
+            c.edges.push_back({idx[0], idx[1], idx[2], idx[3]});
         }
     }
     for (size_t i = 0; i < nt; ++i) {
@@ -253,24 +257,49 @@ inline ChainShape chain_shape(const RawChain& c, const uint8_t* base, const std:
         cd = uint16_t(p[s.params_len - 2] | (p[s.params_len - 1] << 8));
     }
     ChainShape sh{K_PASS, n * chain_dtype_bytes(cd), 0, ndim ? last : 0};
-    if (!c.spine || c.n_edges + 1 != c.nodes.size()) throw FormatError("chain is not a linear spine", true);
+    const size_t nn = c.nodes.size();
+    if (c.edges.size() + 1 != nn) throw FormatError("chain is not a tree over its nodes", true);
+    auto param1 = [&](const Node& nd, uint8_t v) { return nd.params_len == 1 && base[nd.params_off] == v; };
+    const bool split16 = nn >= 3 && c.nodes[1].op == OP_R16 && c.nodes[2].op == OP_BYTESPLIT && param1(c.nodes[2], 2);
+    const bool split32 = nn >= 3 && c.nodes[1].op == OP_R32 && c.nodes[2].op == OP_BYTESPLIT && param1(c.nodes[2], 4);
+    // the leading nodes form a spine; after a byte split further nodes each hang off one output of the split
+    const size_t spine = (split16 || split32) ? 2 : c.edges.size();
+    for (size_t i = 0; i < spine; ++i) {
+        const RawChain::Edge& e = c.edges[i];
+        if (e.src != i || e.src_out != 0 || e.dst != i + 1 || e.dst_in != 0) throw FormatError("chain is not a linear spine", true);
+    }
     auto terms = [&](size_t node, size_t cnt) {
         if (c.terms.size() != cnt) return false;
         for (size_t i = 0; i < cnt; ++i) if (c.terms[i].first != node || c.terms[i].second != i) return false;
         return true;
     };
-    auto param1 = [&](const Node& nd, uint8_t v) { return nd.params_len == 1 && base[nd.params_off] == v; };
-    size_t nn = c.nodes.size();
-    if ((nn == 1 && terms(0, 1)) || (nn == 2 && c.nodes[1].op == OP_PASS && terms(1, 1))) { sh.kind = K_PASS; sh.plane_len = sh.source_len; }
-    else if (nn == 3 && c.nodes[1].op == OP_R16 && c.nodes[2].op == OP_BYTESPLIT && param1(c.nodes[2], 2) && terms(2, 2)) {
-        if (sh.source_len & 1) throw FormatError("16-bit split of an odd length");
-        sh.kind = K_M16; sh.plane_len = sh.source_len / 2;
-    } else if (nn == 3 && c.nodes[1].op == OP_R32 && c.nodes[2].op == OP_BYTESPLIT && param1(c.nodes[2], 4) && terms(2, 4)) {
-        if (sh.source_len & 3) throw FormatError("32-bit split of a length not divisible by 4");
-        sh.kind = K_M32; sh.plane_len = sh.source_len / 4;
-    } else if (nn == 3 && c.nodes[1].op == OP_RE4M3 && c.nodes[2].op == OP_NIBSPLIT && terms(2, 2)) { sh.kind = K_E4M3; sh.plane_len = sh.source_len; }
+    const char* outside = "chain outside the production split/passthrough set";
+    if (split16 || split32) {
+        const size_t np = split16 ? 2 : 4;
+        if (sh.source_len % np) throw FormatError(split16 ? "16-bit split of an odd length" : "32-bit split of a length not divisible by 4");
+        sh.kind = split16 ? K_M16 : K_M32; sh.plane_len = sh.source_len / np;
+        int via[4] = {-1, -1, -1, -1};  // node between output p of the split and its terminal
+        for (size_t i = 2; i < c.edges.size(); ++i) {
+            const RawChain::Edge& e = c.edges[i];
+            if (e.src != 2 || e.src_out >= np || e.dst < 3 || e.dst >= nn || e.dst_in != 0 || via[e.src_out] >= 0) throw FormatError(outside, true);
+            for (size_t j = 2; j < i; ++j) if (c.edges[j].dst == e.dst) throw FormatError(outside, true);
+            const Node& nd = c.nodes[e.dst];
+            if (nd.op == OP_INTDELTA && nd.params_len == 0) sh.post[e.src_out] = POST_INTDELTA;
+            else if (nd.op == OP_MZS && nd.params_len == 1 && base[nd.params_off] >= 1 && base[nd.params_off] <= 7) { sh.post[e.src_out] = POST_MZS; sh.post_k[e.src_out] = base[nd.params_off]; }
+            else throw FormatError(outside, true);
+            via[e.src_out] = e.dst;
+        }
+        if (c.terms.size() != np) throw FormatError(outside, true);
+        for (size_t i = 0; i < np; ++i) {
+            const bool direct = via[i] < 0 && c.terms[i].first == 2 && c.terms[i].second == i;
+            const bool through = via[i] >= 0 && c.terms[i].first == via[i] && c.terms[i].second == 0;
+            if (!direct && !through) throw FormatError(outside, true);
+        }
+    }
+    else if ((nn == 1 && terms(0, 1)) || (nn == 2 && c.nodes[1].op == OP_PASS && terms(1, 1))) { sh.kind = K_PASS; sh.plane_len = sh.source_len; }
+    else if (nn == 3 && c.nodes[1].op == OP_RE4M3 && c.nodes[2].op == OP_NIBSPLIT && terms(2, 2)) { sh.kind = K_E4M3; sh.plane_len = sh.source_len; }
     else if (nn == 3 && c.nodes[1].op == OP_RE5M2 && c.nodes[2].op == OP_NIBSPLIT && terms(2, 2)) { sh.kind = K_E5M2; sh.plane_len = sh.source_len; }
-    else throw FormatError("chain outside the production split/passthrough set", true);
+    else throw FormatError(outside, true);
     return sh;
 }
 
@@ -491,7 +520,7 @@ class FileReader {
         uint64_t np = r.var_max(255, "plane count");
         if (np > r.left() / 4) r.bad("plane count exceeds the record");
         if (np != uint64_t(kind_planes(sh.kind))) r.bad("plane count differs from the chain's terminals");
-        for (uint64_t i = 0; i < np; ++i) t.planes.push_back(read_plane(r, sh.plane_len));
+        for (uint64_t i = 0; i < np; ++i) { t.planes.push_back(read_plane(r, sh.plane_len)); t.planes.back().post = sh.post[i]; t.planes.back().post_k = sh.post_k[i]; }
         r.done("the last plane");
         return t;
     }
@@ -622,7 +651,8 @@ class FileReader {
             {"identity", 2, C_IDENTITY}, {"huffman", 2, C_HUFFMAN}, {"rans", 2, C_RANS}, {"zstd", 2, C_ZSTD}, {"tans", 2, C_TANS}, {"order1_scale_ac", 2, C_O1SAC},
             {"source", 1, detail::OP_SOURCE}, {"bit_reorder_ieee16", 1, detail::OP_R16}, {"bit_reorder_ieee32", 1, detail::OP_R32},
             {"bit_reorder_fp8_e4m3", 1, detail::OP_RE4M3}, {"bit_reorder_fp8_e5m2", 1, detail::OP_RE5M2}, {"byte_split", 1, detail::OP_BYTESPLIT},
-            {"nibble_split", 1, detail::OP_NIBSPLIT}, {"byte_passthrough", 1, detail::OP_PASS}};
+            {"nibble_split", 1, detail::OP_NIBSPLIT}, {"byte_passthrough", 1, detail::OP_PASS}, {"int_delta", 1, detail::OP_INTDELTA},
+            {"mantissa_zero_strip", 1, detail::OP_MZS}};
         for (uint32_t i = 0; i < count; ++i) {
             r.skip(32);                                              // canonical id
             size_t ll = size_t(r.byte()); ll |= size_t(r.byte()) << 8;
@@ -686,7 +716,6 @@ class FileReader {
             c.nodes.push_back(n);
         }
         Span er(b_, e0, e0 + el, "legacy chain edges");
-        c.n_edges = ne;
         for (size_t i = 0; i < ne; ++i) {
             uint8_t src = er.byte(), so = er.byte(), dst = er.byte(), di = er.byte(), has_role = er.byte();
             if (has_role > 1) er.bad("edge role_present byte has an unknown value");
@@ -694,7 +723,7 @@ class FileReader {
             size_t vl = size_t(er.byte()); vl |= size_t(er.byte()) << 8;
             er.skip(vl);
             if (vl) throw FormatError("chain edge with vendor bytes", true);  // a role override only relabels the plane: nothing to do at decode
-            if (src != i || so != 0 || dst != i + 1 || di != 0) c.spine = false;
+            c.edges.push_back({src, so, dst, di});
         }
         Span tr(b_, t0, t0 + tl, "legacy chain terminals");
         for (size_t i = 0; i < nt; ++i) {
@@ -814,7 +843,7 @@ class FileReader {
         if (sh.source_len != t.orig_size) r.bad("chain Source declares a different size than orig_size");
         t.kind = sh.kind;
         if (np != size_t(kind_planes(sh.kind))) r.bad("plane count differs from the chain's terminals");
-        for (size_t i = 0; i < np; ++i) t.planes.push_back(read_legacy_plane(r, sh.plane_len, *plane_table));
+        for (size_t i = 0; i < np; ++i) { t.planes.push_back(read_legacy_plane(r, sh.plane_len, *plane_table)); t.planes.back().post = sh.post[i]; t.planes.back().post_k = sh.post_k[i]; }
         return t;
     }
     ParsedFile parse_legacy() {
@@ -956,6 +985,7 @@ class FileReader {
                     if (flags & 0x02) { p.has_crc = true; p.crc = r.u32(); }
                     p.payload_off = r.skip(size_t(p.payload_len));
                     p.decoded_len = sh.plane_len;
+                    p.post = sh.post[pi]; p.post_k = sh.post_k[pi];
                     p.row_len = sh.kind == K_PASS ? sh.row_len : 0;  // the frame stores no layout: it follows the chain (compact.rs:500-503)
                     make_chunks(p, false, {}, so, sl, sv, 0);
                     t.planes.push_back(std::move(p));

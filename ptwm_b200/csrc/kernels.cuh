@@ -1383,6 +1383,120 @@ __global__ void __launch_bounds__(256) merge_kernel(const MergeItem* __restrict_
     }
 }
 
+// ---- per-plane ops between the split and a terminal, undone in scratch -------
+// A CTA of 256 threads owns one tile of POST_TILE bytes; thread t owns the 64
+// bytes from 64 t on.  Tiles of all items are numbered through `tile_first`
+// like the merge tiles.  IntDelta (transforms/int_delta.rs:36-44, byte width)
+// takes three launches: the byte sum of every tile, an exclusive scan of the
+// sums per plane, then the running sum inside every tile started from the
+// tile's carry.  All arithmetic is modulo 256 per byte (__vadd4).
+struct PostTile { PostItem it; uint64_t base; uint32_t n; uint32_t local; };
+__device__ __forceinline__ PostTile post_tile_of(const PostItem* items, const uint32_t* tile_first, uint32_t n_items) {
+    uint32_t tile = blockIdx.x, lo = 0, hi = n_items;
+    while (lo + 1 < hi) { uint32_t mid = (lo + hi) >> 1; if (tile_first[mid] <= tile) lo = mid; else hi = mid; }
+    PostTile t;
+    t.it = items[lo];
+    t.local = tile - tile_first[lo];
+    t.base = uint64_t(t.local) * POST_TILE;
+    t.n = t.it.n - t.base < POST_TILE ? uint32_t(t.it.n - t.base) : POST_TILE;
+    return t;
+}
+// The thread's 64 bytes as sixteen words, zero beyond the plane's end.  The plane starts on a 256-byte boundary of the scratch arena.
+__device__ __forceinline__ void post_load64(const uint8_t* tile, uint32_t n, uint32_t w[16]) {
+    const uint32_t at = threadIdx.x * 64;
+    if (at + 64 <= n) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { uint4 v = *reinterpret_cast<const uint4*>(tile + at + 16 * q); w[4 * q] = v.x; w[4 * q + 1] = v.y; w[4 * q + 2] = v.z; w[4 * q + 3] = v.w; }
+    } else {
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            uint32_t v = 0;
+            for (int i = 0; i < 4; ++i) if (at + 4 * k + i < n) v |= uint32_t(tile[at + 4 * k + i]) << (8 * i);
+            w[k] = v;
+        }
+    }
+}
+__device__ __forceinline__ void post_store64(uint8_t* tile, uint32_t n, const uint32_t w[16]) {
+    const uint32_t at = threadIdx.x * 64;
+    if (at + 64 <= n) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(tile + at + 16 * q) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+    } else {
+        for (int k = 0; k < 16; ++k) for (int i = 0; i < 4; ++i) if (at + 4 * k + i < n) tile[at + 4 * k + i] = uint8_t(w[k] >> (8 * i));
+    }
+}
+// Sum over the block of one byte-sized value per thread; with `exclusive`, every thread gets the sum of the threads before it.
+__device__ __forceinline__ uint32_t post_block_sum(uint32_t v, uint32_t* exclusive) {
+    __shared__ uint32_t warp_total[8];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) { uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, d); if (lane >= d) incl += t; }
+    __syncthreads();  // the array may still be read from an earlier call
+    if (lane == 31) warp_total[warp] = incl;
+    __syncthreads();
+    uint32_t before = 0, total = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { if (k < int(warp)) before += warp_total[k]; total += warp_total[k]; }
+    if (exclusive) *exclusive = (before + incl - v) & 0xFFu;
+    return total & 0xFFu;
+}
+__global__ void __launch_bounds__(256) post_tile_sums_kernel(const PostItem* __restrict__ items, const uint32_t* __restrict__ tile_first, uint32_t n_items, Bases bases) {
+    const PostTile t = post_tile_of(items, tile_first, n_items);
+    if (t.it.op != POST_INTDELTA) return;
+    uint32_t w[16], acc = 0;
+    post_load64(wr(bases, t.it.plane) + t.base, t.n, w);
+#pragma unroll
+    for (int k = 0; k < 16; ++k) acc = __vadd4(acc, w[k]);
+    acc = (acc + (acc >> 8) + (acc >> 16) + (acc >> 24)) & 0xFFu;
+    const uint32_t total = post_block_sum(acc, nullptr);
+    if (threadIdx.x == 0) reinterpret_cast<uint32_t*>(wr(bases, t.it.sums))[t.local] = total;
+}
+// One CTA per plane: the tile sums become the sum of all tiles before each.
+__global__ void __launch_bounds__(256) post_scan_sums_kernel(const PostItem* __restrict__ items, uint32_t n_items, Bases bases) {
+    const PostItem it = items[blockIdx.x];
+    if (it.op != POST_INTDELTA) return;
+    uint32_t* sums = reinterpret_cast<uint32_t*>(wr(bases, it.sums));
+    const uint64_t tiles = (it.n + POST_TILE - 1) / POST_TILE;
+    uint32_t carry = 0;
+    for (uint64_t first = 0; first < tiles; first += 256) {
+        const uint64_t i = first + threadIdx.x;
+        const uint32_t v = i < tiles ? sums[i] : 0u;
+        uint32_t excl;
+        const uint32_t total = post_block_sum(v, &excl);
+        if (i < tiles) sums[i] = (carry + excl) & 0xFFu;
+        carry = (carry + total) & 0xFFu;
+    }
+}
+__global__ void __launch_bounds__(256) post_apply_kernel(const PostItem* __restrict__ items, const uint32_t* __restrict__ tile_first, uint32_t n_items, Bases bases) {
+    const PostTile t = post_tile_of(items, tile_first, n_items);
+    uint8_t* tile = wr(bases, t.it.plane) + t.base;
+    uint32_t w[16];
+    post_load64(tile, t.n, w);
+    if (t.it.op == POST_MZS) {  // transforms/mantissa_zero.rs: inverse shifts every byte left by k
+        const uint32_t keep = 0x01010101u * (0xFFu >> t.it.k);
+#pragma unroll
+        for (int k = 0; k < 16; ++k) w[k] = (w[k] & keep) << t.it.k;
+    } else if (t.it.op == POST_INTDELTA) {
+        uint32_t run = 0;  // sum of the thread's earlier words, in every byte
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            uint32_t v = w[k];
+            v = __vadd4(v, v << 8);
+            v = __vadd4(v, v << 16);  // running sum inside the word
+            v = __vadd4(v, run);
+            run = (v >> 24) * 0x01010101u;
+            w[k] = v;
+        }
+        uint32_t excl;
+        post_block_sum(run & 0xFFu, &excl);
+        const uint32_t carry = ((reinterpret_cast<const uint32_t*>(rd(bases, t.it.sums))[t.local] + excl) & 0xFFu) * 0x01010101u;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) w[k] = __vadd4(w[k], carry);
+    }
+    post_store64(tile, t.n, w);
+}
+
 // ---- integrity -------------------------------------------------------------
 // CRC-32/IEEE in the reflected form (poly 0xEDB88320).  Each thread takes the
 // remainder of one run of plane bytes from state 0, multiplies it by
@@ -1405,6 +1519,20 @@ __host__ __device__ __forceinline__ uint32_t x_pow_8n(const uint32_t* x2n, uint6
     return p;
 }
 
+// Plane bytes of one element (byte p = plane p) as their terminals hold them: the forward direction of the per-plane
+// ops, from this element's and the previous element's plane bytes.
+__device__ __forceinline__ uint32_t terminal_bytes(uint32_t cur, uint32_t prev, uint32_t post, uint32_t post_k, int planes) {
+    uint32_t r = 0;
+    for (int p = 0; p < planes; ++p) {
+        const uint32_t op = (post >> (8 * p)) & 0xFFu, k = (post_k >> (8 * p)) & 0xFFu;
+        uint32_t b = (cur >> (8 * p)) & 0xFFu;
+        if (op == POST_INTDELTA) b = (b - ((prev >> (8 * p)) & 0xFFu)) & 0xFFu;
+        else if (op == POST_MZS) b >>= k;
+        r |= b << (8 * p);
+    }
+    return r;
+}
+
 __global__ void __launch_bounds__(128) crc_planes_kernel(const VerifyTensor* __restrict__ tensors, uint32_t n_tensors, uint64_t n_runs, Bases bases,
                                                          const CrcTables* __restrict__ tabs, uint32_t* __restrict__ acc) {
     __shared__ uint32_t T[256];
@@ -1425,22 +1553,34 @@ __global__ void __launch_bounds__(128) crc_planes_kernel(const VerifyTensor* __r
         case K_PASS:
             for (uint32_t i = 0; i < n; ++i) c[0] = T[(c[0] ^ out[first + i]) & 0xFF] ^ (c[0] >> 8);
             break;
-        case K_M16:
+        case K_M16: {
+            auto planes_of = [&](uint64_t e) {
+                uint32_t v = uint32_t(out[2 * e]) | uint32_t(out[2 * e + 1]) << 8;
+                return ((v << 1) & 0xFF00u) | ((v >> 8) & 0x0080u) | (v & 0x007Fu);
+            };
+            uint32_t prev = (t.post && first) ? planes_of(first - 1) : 0u;
             for (uint32_t i = 0; i < n; ++i) {
-                uint32_t v = uint32_t(out[2 * (first + i)]) | uint32_t(out[2 * (first + i) + 1]) << 8;
-                uint32_t r = ((v << 1) & 0xFF00u) | ((v >> 8) & 0x0080u) | (v & 0x007Fu);
+                uint32_t r = planes_of(first + i);
+                if (t.post) { uint32_t cur = r; r = terminal_bytes(r, prev, t.post, t.post_k, 2); prev = cur; }
                 c[0] = T[(c[0] ^ r) & 0xFF] ^ (c[0] >> 8);
                 c[1] = T[(c[1] ^ (r >> 8)) & 0xFF] ^ (c[1] >> 8);
             }
             break;
-        case K_M32:
+        }
+        case K_M32: {
+            auto planes_of = [&](uint64_t e) {
+                uint32_t v = ld_u32_unaligned(out + 4 * e);
+                return ((v << 1) & 0xFF000000u) | ((v >> 8) & 0x00800000u) | (v & 0x007FFFFFu);
+            };
+            uint32_t prev = (t.post && first) ? planes_of(first - 1) : 0u;
             for (uint32_t i = 0; i < n; ++i) {
-                uint32_t v = ld_u32_unaligned(out + 4 * (first + i));
-                uint32_t r = ((v << 1) & 0xFF000000u) | ((v >> 8) & 0x00800000u) | (v & 0x007FFFFFu);
+                uint32_t r = planes_of(first + i);
+                if (t.post) { uint32_t cur = r; r = terminal_bytes(r, prev, t.post, t.post_k, 4); prev = cur; }
 #pragma unroll
                 for (int p = 0; p < 4; ++p) c[p] = T[(c[p] ^ (r >> (8 * p))) & 0xFF] ^ (c[p] >> 8);
             }
             break;
+        }
         default:
             for (uint32_t i = 0; i < n; ++i) {
                 uint32_t v = out[first + i];

@@ -63,7 +63,24 @@ struct VerifyTensor {
     uint64_t first_run;  // index of this tensor's first run among all runs of the launch
     uint32_t kind;
     uint32_t acc_base;
+    uint32_t post;       // byte p: op between the split and terminal p (POST_*); the CRC covers the terminal's bytes
+    uint32_t post_k;     // byte p: bits stripped by MantissaZeroStrip
 };
+
+// A plane in scratch that passed through one more op on the way from the split
+// to its terminal: undo it in place before the planes are recombined.
+// IntDelta (byte width): running sum modulo 256 over the whole plane, done in
+// tiles of POST_TILE bytes with one word per tile at `sums`.
+// MantissaZeroStrip(k): every byte shifted left by k.
+enum : uint32_t { POST_NONE = 0, POST_INTDELTA = 1, POST_MZS = 2 };
+struct PostItem {
+    Ref plane;
+    uint64_t n;
+    uint32_t op;
+    uint32_t k;
+    Ref sums;
+};
+constexpr uint32_t POST_TILE = 16384;
 constexpr uint32_t VERIFY_RUN = 2048;
 
 struct HashItem {

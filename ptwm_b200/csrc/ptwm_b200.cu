@@ -78,6 +78,8 @@ struct DevicePlan {
     DecodeItem* items = nullptr;       // all decode lists back to back
     MergeItem* merges = nullptr;
     uint32_t* tiles = nullptr;
+    PostItem* posts = nullptr;
+    uint32_t* post_tiles = nullptr;
     VerifyTensor* verify = nullptr;
     HashItem* hashes = nullptr;
     uint32_t* status = nullptr;        // [0] = summary, [1 + id] per item
@@ -87,7 +89,7 @@ struct DevicePlan {
     bool timed[12] = {false};
     void release() {
         for (auto& e : ev) if (e) cudaEventDestroy(e);
-        cudaFree(items); cudaFree(merges); cudaFree(tiles); cudaFree(verify); cudaFree(hashes); cudaFree(status); cudaFree(acc); cudaFree(hash_out);
+        cudaFree(items); cudaFree(merges); cudaFree(tiles); cudaFree(posts); cudaFree(post_tiles); cudaFree(verify); cudaFree(hashes); cudaFree(status); cudaFree(acc); cudaFree(hash_out);
         *this = DevicePlan{};
     }
 };
@@ -104,6 +106,9 @@ struct ptwm_b200_plan {
     // merge lists: [0] copies into scratch, [1] final recombination
     std::vector<MergeItem> merges[2];
     std::vector<uint32_t> tiles[2];
+    // planes in scratch with an IntDelta or MantissaZeroStrip to undo between the two phases, and the first tile of each
+    std::vector<PostItem> posts;
+    std::vector<uint32_t> post_tiles;
     std::vector<VerifyTensor> verify;
     uint64_t n_runs = 0;
     std::vector<CrcExpect> crc_expect;
@@ -169,7 +174,9 @@ void plan_tensor(ptwm_b200_plan& pl, uint32_t ti, const TensorDesc& t, uint64_t 
         if (t.planes[size_t(p)].chunks.size() != t.planes[0].chunks.size()) aligned = false;
         else for (size_t k = 0; k < t.planes[0].chunks.size(); ++k) if (t.planes[size_t(p)].chunks[k].decoded != t.planes[0].chunks[k].decoded) { aligned = false; break; }
     }
-    if (aligned) {
+    bool has_post = false;
+    for (const PlaneDesc& pd : t.planes) has_post |= pd.post != POST_NONE;
+    if (aligned && !has_post) {
         for (size_t k = 0; k < t.planes[0].chunks.size(); ++k) {
             const uint32_t n = t.planes[0].chunks[k].decoded;
             if (!n) continue;
@@ -211,7 +218,7 @@ void plan_tensor(ptwm_b200_plan& pl, uint32_t ti, const TensorDesc& t, uint64_t 
             }
         }
     } else {
-        // planes chunked differently: materialise every plane in scratch, then recombine once
+        // planes chunked differently, or a plane with an op to undo first: materialise every plane in scratch, then recombine once
         Ref srcs[4] = {REF_NONE, REF_NONE, REF_NONE, REF_NONE};
         for (int p = 0; p < np; ++p) {
             const PlaneDesc& pd = t.planes[size_t(p)];
@@ -222,6 +229,15 @@ void plan_tensor(ptwm_b200_plan& pl, uint32_t ti, const TensorDesc& t, uint64_t 
                 Ref dst = make_ref(SP_SCRATCH, base + ch.plane_off);
                 if (ch.raw) { span(ch.data_off, ch.data_len); pl.merges[0].push_back(MergeItem{{make_ref(SP_BLOB, ch.data_off), REF_NONE, REF_NONE, REF_NONE}, dst, ch.decoded, K_PASS}); }
                 else { DecodeItem it = decode_item(pd, ch); it.dst = dst; pl.dec[0][codec_class(pd.codec)].push_back(it); }
+            }
+            if (pd.post != POST_NONE && pd.decoded_len) {
+                PostItem po{srcs[p], pd.decoded_len, pd.post, pd.post_k, REF_NONE};
+                if (pd.post == POST_INTDELTA) {
+                    pl.scratch_bytes = align_up(pl.scratch_bytes, 16);
+                    po.sums = make_ref(SP_SCRATCH, pl.scratch_bytes);
+                    pl.scratch_bytes += align_up(4 * ((pd.decoded_len + POST_TILE - 1) / POST_TILE), 16);
+                }
+                pl.posts.push_back(po);
             }
         }
         uint64_t n = t.planes[0].decoded_len;
@@ -269,6 +285,12 @@ void finish_lists(ptwm_b200_plan& pl) {
         pl.tiles[ph].push_back(tile);
         if (!m.empty()) pl.launches++;
     }
+    pl.post_tiles.clear();
+    uint32_t tile = 0;
+    bool delta = false;
+    for (auto& po : pl.posts) { pl.post_tiles.push_back(tile); tile += uint32_t((po.n + POST_TILE - 1) / POST_TILE); delta |= po.op == POST_INTDELTA; }
+    pl.post_tiles.push_back(tile);
+    if (!pl.posts.empty()) pl.launches += delta ? 3 : 1;
 }
 
 template <class T>
@@ -290,7 +312,8 @@ int64_t device_plan(ptwm_b200_plan& pl, int dev, DevicePlan** out) {
     std::vector<uint32_t> allt;
     for (int ph = 0; ph < 2; ++ph) { allm.insert(allm.end(), pl.merges[ph].begin(), pl.merges[ph].end()); allt.insert(allt.end(), pl.tiles[ph].begin(), pl.tiles[ph].end()); }
     int64_t rc;
-    if ((rc = upload(&d.items, all)) < 0 || (rc = upload(&d.merges, allm)) < 0 || (rc = upload(&d.tiles, allt)) < 0 || (rc = upload(&d.verify, pl.verify)) < 0 ||
+    if ((rc = upload(&d.items, all)) < 0 || (rc = upload(&d.merges, allm)) < 0 || (rc = upload(&d.tiles, allt)) < 0 || (rc = upload(&d.posts, pl.posts)) < 0 || (rc = upload(&d.post_tiles, pl.post_tiles)) < 0 ||
+        (rc = upload(&d.verify, pl.verify)) < 0 ||
         (rc = upload(&d.hashes, pl.hashes)) < 0) { d.release(); return rc; }
     CUDA_TRY(cudaMalloc(&d.status, (pl.item_tensor.size() + 1) * sizeof(uint32_t)));
     CUDA_TRY(cudaMalloc(&d.acc, (pl.n_acc + 1) * sizeof(uint32_t)));
@@ -353,8 +376,24 @@ int64_t enqueue(ptwm_b200_plan& pl, DevicePlan& d, const Bases& bases, uint32_t 
         }
         return 0;
     };
+    // planes in scratch are complete after the first phase: undo IntDelta / MantissaZeroStrip in place before anything reads them
+    auto launch_posts = [&]() -> int64_t {
+        if (pl.posts.empty()) return 0;
+        const uint32_t n = uint32_t(pl.posts.size()), tiles = pl.post_tiles.back();
+        bool delta = false;
+        for (auto& po : pl.posts) delta |= po.op == POST_INTDELTA;
+        if (delta) {
+            post_tile_sums_kernel<<<tiles, 256, 0, st>>>(d.posts, d.post_tiles, n, bases);
+            CUDA_TRY(cudaGetLastError());
+            post_scan_sums_kernel<<<n, 256, 0, st>>>(d.posts, n, bases);
+            CUDA_TRY(cudaGetLastError());
+        }
+        post_apply_kernel<<<tiles, 256, 0, st>>>(d.posts, d.post_tiles, n, bases);
+        CUDA_TRY(cudaGetLastError());
+        return 0;
+    };
     int64_t rc;
-    if ((rc = launch_decodes(0)) < 0 || (rc = launch_merges(0)) < 0 || (rc = launch_decodes(1)) < 0 || (rc = launch_merges(1)) < 0) return rc;
+    if ((rc = launch_decodes(0)) < 0 || (rc = launch_merges(0)) < 0 || (rc = launch_posts()) < 0 || (rc = launch_decodes(1)) < 0 || (rc = launch_merges(1)) < 0) return rc;
     if ((flags & PTWM_B200_VERIFY_CRC) && !pl.verify.empty()) {
         CUDA_TRY(cudaMemsetAsync(d.acc, 0, (pl.n_acc + 1) * sizeof(uint32_t), st));
         uint64_t blocks = (pl.n_runs + 127) / 128;
@@ -635,7 +674,8 @@ int64_t ptwm_b200_plan_create(const ptwm_b200_container* c, const uint32_t* indi
             bool any_crc = false;
             for (const PlaneDesc& p : t.planes) any_crc |= p.has_crc;
             if (any_crc && t.planes[0].decoded_len) {
-                VerifyTensor v{make_ref(SP_OUT, off), t.planes[0].decoded_len, pl->n_runs, t.kind, pl->n_acc};
+                VerifyTensor v{make_ref(SP_OUT, off), t.planes[0].decoded_len, pl->n_runs, t.kind, pl->n_acc, 0, 0};
+                for (size_t p = 0; p < t.planes.size() && p < 4; ++p) { v.post |= uint32_t(t.planes[p].post) << (8 * p); v.post_k |= uint32_t(t.planes[p].post_k) << (8 * p); }
                 pl->n_runs += (v.n_elems + VERIFY_RUN - 1) / VERIFY_RUN;
                 for (size_t p = 0; p < t.planes.size(); ++p) if (t.planes[p].has_crc) pl->crc_expect.push_back({pl->n_acc + uint32_t(p), t.planes[p].crc, t.planes[p].decoded_len, ti});
                 pl->n_acc += uint32_t(t.planes.size());

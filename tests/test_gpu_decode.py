@@ -183,17 +183,18 @@ def test_reference_fixtures_on_gpu():
     for i, (name, t) in enumerate(h.decode_model()):
         assert bytes_of(t) == oc.decode(i)
     assert xxhash.xxh64(bytes_of(h.decode("t1"))).hexdigest() == json.load(open(os.path.join(ref, "expected.json")))["ptwc_bound_source"]["t1"][1]
-    done = 0
+    done, delta = 0, 0
     for f in sorted(os.listdir(os.path.join(ref, "compact_decode"))):
         frame = b"\x89PTWS" + open(os.path.join(ref, "compact_decode", f), "rb").read()
         try:
             want, _ = oracle.decode_compact(frame)
         except oracle.OracleError:
-            continue  # zstd planes or IntDelta chains: outside the hot path
+            continue  # zstd planes: outside the hot path
         got = ptwm_b200.Decompressor(ptwm_b200.DecompressionConfig(device=0)).decompress(frame)
         assert bytes_of(got) == want, f
         done += 1
-    assert done >= 9
+        delta += "smooth" in f or "byte_bf16" in f
+    assert done >= 16 and delta == 7  # the seven split + IntDelta seeds carry the reference's own hashes and plane CRCs
 
 
 def test_integrity_checks_fire():
@@ -293,3 +294,40 @@ def test_legacy_fixtures_decode_to_the_reference_hashes(fixture):
         n, want = exp[name]
         assert len(raw) == n and oracle.xxh64(raw) == int(want, 16), name
     assert list(h.decode("model.layers.2.chunked.weight").shape) == [16, 32]
+
+
+def _post_specs(n: int):
+    rng = np.random.default_rng(n)
+    smooth = (np.cumsum(rng.standard_normal(n)) * 0.01).astype(np.float32)
+    bf = (smooth.view(np.uint32) >> 16).astype(np.uint16)
+    quant = (bf & 0xFFF8).astype(np.uint16)  # three low mantissa bits zero, as after dequantising a 4-bit mantissa
+    return [oracle.TensorSpec("delta.bf16", oracle.DT_BF16, [n], bf.tobytes(), post={1: ("intdelta",)}),
+            oracle.TensorSpec("strip.bf16", oracle.DT_BF16, [n // 4, 4], quant.tobytes(), post={0: ("mzs", 3)}),
+            oracle.TensorSpec("delta.f32", oracle.DT_F32, [n], smooth.tobytes(), post={3: ("intdelta",)}),
+            oracle.TensorSpec("both.f32", oracle.DT_F32, [n], (smooth.view(np.uint32) & 0xFFFFFF00).astype(np.uint32).tobytes(), post={0: ("mzs", 7), 3: ("intdelta",)}),
+            oracle.TensorSpec("two.bf16", oracle.DT_BF16, [n], quant.tobytes(), post={0: ("mzs", 2), 1: ("intdelta",)}),
+            oracle.TensorSpec("plain.bf16", oracle.DT_BF16, [n], bf.tobytes())]
+
+
+@pytest.mark.parametrize("n,opts", [(5000, dict()), (5000, dict(chunk_size=1000, emit_crc=True, emit_hash=True)),
+                                    (100_004, dict(forced_codec=oracle.RANS, chunk_size=8192, emit_crc=True)),
+                                    (100_004, dict(forced_codec=oracle.HUFFMAN, chunk_size=32768, emit_crc=True, emit_hash=True)),
+                                    (70_000, dict(forced_codec=oracle.TANS, chunk_size=65536, emit_crc=True)),
+                                    (4_300_000, dict(forced_codec=oracle.IDENTITY, emit_crc=True, emit_hash=True))])
+def test_per_plane_ops_match_oracle(n, opts):
+    # IntDelta on the exponent plane, MantissaZeroStrip on a mantissa plane (python/ptwm/preprocessing/_chains.py:360-389,486-560);
+    # the largest case spans more than 256 tiles of the running sum
+    specs = _post_specs(n)
+    blob = oracle.write_container(specs, **opts)
+    h, got = check_container(blob, {s.name: s.raw for s in specs})
+    # a wrong CRC of a terminal plane is noticed
+    if opts.get("emit_crc") and n <= 5000:
+        oc = oracle.Container(blob)
+        p = oc.tensors[0]["planes"][1]
+        bad = bytearray(blob)
+        bad[p["payload_off"] + p["payload_len"] - 1] ^= 0x10
+        with pytest.raises(ptwm_b200.PtwmError):
+            ptwm_b200.ContainerHandle(bytes(bad), device=0).decode_model()
+    for s in specs[:3]:
+        frame = oracle.write_compact(s, emit_hash=True)
+        assert bytes_of(ptwm_b200.Decompressor(ptwm_b200.DecompressionConfig(device=0)).decompress(frame)) == s.raw

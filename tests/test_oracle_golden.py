@@ -56,20 +56,48 @@ def test_ptwc_trimmed_matches_legacy_fixture_table():
 
 
 def test_compact_frames_self_check():
-    # fuzz/corpus/compact_decode: *_hash carry xxh64, *_crc carry plane CRC-32s
-    ok = 0
+    # fuzz/corpus/compact_decode: *_hash carry xxh64, *_crc carry plane CRC-32s.  The *_smooth and byte_bf16 seeds
+    # use the split + IntDelta chains (python/ptwm/preprocessing/_chains.py:360-389): their hashes pin the inverse
+    # delta, their CRCs that the checksum covers the terminal's bytes (before the inverse).
+    have_zstd = oracle.install_zstd()
+    ok, delta = 0, 0
     for f in sorted(glob.glob(os.path.join(REF, "compact_decode", "*"))):
         blob = b"\x89PTWS" + open(f, "rb").read()
         try:
             raw, d = oracle.decode_compact(blob)
         except oracle.OracleError as e:
-            assert "unsupported" in str(e), (f, e)  # IntDelta chains (bf16_smooth, fp32_smooth, byte_bf16)
+            assert not have_zstd and "zstd" in str(e), (f, e)
             continue
         ok += 1
+        delta += "smooth" in f or "byte_bf16" in f
         with pytest.raises(oracle.OracleError):
             oracle.decode_compact(blob + b"\x00")  # fuzz_targets/compact_decode.rs:50-55
-    oracle.install_zstd()
-    assert ok >= 9
+    assert delta == 7 and ok >= 16
+    if have_zstd:
+        assert ok == 28
+
+
+def test_per_plane_ops_round_trip_through_the_writer():
+    # IntDelta on the exponent plane and MantissaZeroStrip on a mantissa plane, both layouts of the writer
+    import numpy as np
+    rng = np.random.default_rng(3)
+    smooth = (np.cumsum(rng.standard_normal(5000)) * 0.01).astype(np.float32)
+    bf = (smooth.view(np.uint32) >> 16).astype(np.uint16)
+    quant = (bf & 0xFFF8).astype(np.uint16)  # three low mantissa bits zero, as after dequantising a 4-bit mantissa
+    specs = [oracle.TensorSpec("a", oracle.DT_BF16, [5000], bf.tobytes(), post={1: ("intdelta",)}),
+             oracle.TensorSpec("b", oracle.DT_BF16, [50, 100], quant.tobytes(), post={0: ("mzs", 3)}),
+             oracle.TensorSpec("c", oracle.DT_F32, [5000], smooth.tobytes(), post={3: ("intdelta",)}),
+             oracle.TensorSpec("d", oracle.DT_F32, [5000], (smooth.view(np.uint32) & 0xFFFFFF00).tobytes(), post={0: ("mzs", 7), 3: ("intdelta",)}),
+             oracle.TensorSpec("e", oracle.DT_BF16, [5000], bf.tobytes())]
+    for opts in (dict(), dict(chunk_size=1000, emit_crc=True, emit_hash=True), dict(forced_codec=oracle.RANS, chunk_size=4096, emit_crc=True)):
+        c = oracle.Container(oracle.write_container(specs, **opts))
+        for i, s in enumerate(specs):
+            assert c.decode(i) == s.raw, (s.name, opts)
+    for s in specs:
+        raw, _ = oracle.decode_compact(oracle.write_compact(s, emit_hash=True))
+        assert raw == s.raw
+    with pytest.raises(ValueError):
+        oracle.write_container([oracle.TensorSpec("x", oracle.DT_BF16, [5000], bf.tobytes(), post={0: ("mzs", 3)})])
 
 
 def test_huffman_weight_header_bytes():
