@@ -88,6 +88,11 @@ typedef struct ptwm_b200_plan ptwm_b200_plan;
 /* Message of the last failure on the calling thread. */
 const char* ptwm_b200_last_error(void);
 
+/* BLAKE3 (unkeyed, 32 bytes) of a host buffer: the hash the legacy layout's
+ * header holds of its Extension Table (extension/table.rs:136-141) and the
+ * derivation of built-in ids (extension/id.rs:21-31).  Host code. */
+void ptwm_b200_blake3(const uint8_t* data, size_t len, uint8_t out[32]);
+
 /* Parse a \x89PTWC container or a \x89PTWS frame held in host memory
  * (ContainerReader::open, container.rs:1395-1626; compact.rs:321-405).  The
  * bytes are only read during this call.  A frame opens as a container with one

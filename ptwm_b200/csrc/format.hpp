@@ -17,6 +17,7 @@
 #include <unordered_set>
 #include <vector>
 
+#include "blake3.hpp"
 #include "plan.h"
 
 namespace ptwm {
@@ -654,7 +655,7 @@ class FileReader {
             {"nibble_split", 1, detail::OP_NIBSPLIT}, {"byte_passthrough", 1, detail::OP_PASS}, {"int_delta", 1, detail::OP_INTDELTA},
             {"mantissa_zero_strip", 1, detail::OP_MZS}};
         for (uint32_t i = 0; i < count; ++i) {
-            r.skip(32);                                              // canonical id
+            const uint8_t* canonical = b_ + r.skip(32);             // canonical id
             size_t ll = size_t(r.byte()); ll |= size_t(r.byte()) << 8;
             std::string label(reinterpret_cast<const char*>(b_ + r.skip(ll)), ll);
             uint16_t kind = uint16_t(r.byte()); kind |= uint16_t(r.byte()) << 8;
@@ -670,13 +671,28 @@ class FileReader {
             r.skip(16);                                              // embedded wasm offset and length
             LegacyEntry e{0x7F, 0xFFFF};
             static const std::string prefix = "io.ptwm.builtin.";
-            size_t at = label.rfind('@');
+            size_t at = label.find('@', std::min(prefix.size(), label.size()));
             if (label.compare(0, prefix.size(), prefix) == 0 && at != std::string::npos && at > prefix.size()) {
-                std::string name = label.substr(prefix.size(), at - prefix.size());
-                // kind: 1 Transform, 2 PlaneCodec in the reference's numbering is not relied on; the name decides
-                bool hit = false;
-                for (auto& k : known) if (name == k.name) { e = LegacyEntry{k.tag, k.id}; hit = true; }
-                if (!hit) e = LegacyEntry{uint8_t(0x7E), 0xFFFF};      // a built-in outside the hot path
+                // A built-in of any release is io.ptwm.builtin.<name>@<version> whose id is
+                // blake3(author key || 0 || name || 0 || version) under the built-in author key
+                // (extension/builtins.rs:283-333, extension/id.rs:21-31); anything else with such a label is
+                // somebody else's entry, i.e. an extension that is not installed.
+                const std::string name = label.substr(prefix.size(), at - prefix.size()), version = label.substr(at + 1);
+                bool genuine = !version.empty() && version.size() <= 64 && version.find('@') == std::string::npos;
+                if (genuine) {
+                    std::vector<uint8_t> msg(32, 0xBB);
+                    msg.push_back(0); msg.insert(msg.end(), name.begin(), name.end());
+                    msg.push_back(0); msg.insert(msg.end(), version.begin(), version.end());
+                    uint8_t id[32];
+                    blake3_hash(msg.data(), msg.size(), id);
+                    genuine = std::memcmp(id, canonical, 32) == 0;
+                }
+                if (genuine) {
+                    // kind: 1 Transform, 2 PlaneCodec in the reference's numbering is not relied on; the name decides
+                    bool hit = false;
+                    for (auto& k : known) if (name == k.name) { e = LegacyEntry{k.tag, k.id}; hit = true; }
+                    if (!hit) e = LegacyEntry{uint8_t(0x7E), 0xFFFF};  // a built-in outside the hot path
+                }
             }
             (void)kind;
             out.push_back(e);
@@ -859,7 +875,12 @@ class FileReader {
         };
         inside(et_off, et_len, "extension table"); inside(idx_off, idx_len, "tensor index"); inside(pre_off, pre_len, "shared prelude");
         std::vector<LegacyEntry> table;
-        read_legacy_table(size_t(et_off), size_t(et_off + et_len), table);
+        if (et_len) {  // container.rs:1283-1304: the header commits to the table bytes
+            uint8_t h[32];
+            blake3_hash(b_ + et_off, size_t(et_len), h);
+            if (std::memcmp(h, b_ + 27, 32)) throw FormatError("legacy container: extension table hash mismatch");
+            read_legacy_table(size_t(et_off), size_t(et_off + et_len), table);
+        }
         std::vector<std::pair<uint16_t, detail::RawChain>> registry;
         {
             const size_t end = size_t(pre_off + pre_len);

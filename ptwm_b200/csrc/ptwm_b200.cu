@@ -547,6 +547,7 @@ uint64_t stream_handle(uint32_t device) {
 extern "C" {
 
 const char* ptwm_b200_last_error(void) { return last_error_ref().c_str(); }
+void ptwm_b200_blake3(const uint8_t* data, size_t len, uint8_t out[32]) { blake3_hash(data, len, out); }
 
 uint64_t ptwm_hardware_backend_v1_cuda_stream_handle(uint32_t device_ordinal) { return stream_handle(device_ordinal); }
 uint64_t ptwm_plane_codec_v1_cuda_stream_handle(uint32_t device_ordinal) { return stream_handle(device_ordinal); }

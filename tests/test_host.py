@@ -158,6 +158,38 @@ def test_legacy_fixtures_open(L):
         L.ptwm_b200_close(h)
 
 
+def test_blake3_and_the_legacy_table_commitment(L):
+    """BLAKE3 against the Python package at every tree shape up to a few chunks; the legacy header's hash of the
+    Extension Table (container.rs:1299-1301) is checked; a built-in label over a foreign id is not a built-in
+    (extension/builtins.rs:283-333)."""
+    import blake3
+    for n in [0, 1, 63, 64, 65, 1023, 1024, 1025, 2048, 2049, 3073, 4096, 5000, 8193, 100000]:
+        data = bytes((i * 7 + 3) & 0xFF for i in range(n))
+        out = C.create_string_buffer(32)
+        L.ptwm_b200_blake3(data, n, out)
+        assert out.raw == blake3.blake3(data).digest(), n
+    blob = bytearray(open(os.path.join(GOLD, "reference", "legacy_v1_1_0.ptwm"), "rb").read())
+    et_off, et_len = int.from_bytes(blob[11:19], "little"), int.from_bytes(blob[19:27], "little")
+    assert bytes(blob[27:59]) == blake3.blake3(bytes(blob[et_off:et_off + et_len])).digest()
+    first_label = bytes(blob[et_off + 4 + 34:et_off + 4 + 34 + 16])
+    assert first_label == b"io.ptwm.builtin.", first_label
+    assert bytes(blob[et_off + 4:et_off + 36]) == blake3.blake3(b"\xBB" * 32 + b"\x00source\x00" + b"1.1.0").digest()
+    # a flipped table byte breaks the commitment
+    bad = bytearray(blob)
+    bad[et_off + 40] ^= 1
+    rc, h = _open(L, bytes(bad))
+    assert rc < 0 and b"extension table hash mismatch" in L.ptwm_b200_last_error()
+    # a foreign id under a built-in label (hash recomputed so that only the id is wrong): every chain uses the
+    # first entry (source), so no tensor can be planned any more
+    bad = bytearray(blob)
+    bad[et_off + 4] ^= 1
+    bad[27:59] = blake3.blake3(bytes(bad[et_off:et_off + et_len])).digest()
+    rc, h = _open(L, bytes(bad))
+    assert rc == 0
+    assert not any(t.supported for t in _infos(L, h))
+    L.ptwm_b200_close(h)
+
+
 def test_legacy_reader_survives_mutations_and_truncation(L):
     """Every byte of the header, tables, registry and index flipped, a sample of the record bytes flipped, and every
     7th truncation: the legacy reader answers (error or success) and never reads outside the buffer."""
