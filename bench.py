@@ -286,7 +286,7 @@ def run_ours(args):
     for it in range(args.warmup + args.steps):
         barrier()
         t0 = time.perf_counter()
-        h2 = ptwm_b200.ContainerHandle(host_blob, device=local, verify=bool(args.crc))
+        h2 = ptwm_b200.ContainerHandle(host_blob, device=local, verify=bool(args.crc), prefetch=(world == 1))  # one rank needs every byte: start the copy before the parse
         t1 = time.perf_counter()
         decoded = h2.decode_model_streamed(indices=mine, pieces=args.pieces)
         t2 = time.perf_counter()
@@ -355,7 +355,7 @@ def run_ours(args):
                         "ms_per_step": e2e_s * 1e3,
                         "parts_ms": {"parse": 1e3 * statistics.mean(p[0] for p in e2e_parts), "plan_copy_decode": 1e3 * statistics.mean(p[1] for p in e2e_parts)},
                         "pieces": args.pieces,
-                        "includes": "ContainerHandle(pinned host bytes).decode_model_streamed: parse, then per piece plan + H2D copy + decode + status read-back, copies overlapping the rest"},
+                        "includes": "ContainerHandle(pinned host bytes).decode_model_streamed: parse, per piece plan + H2D copy + decode + status read-back, the copies overlapping the rest (at one GPU the copy starts before the parse)"},
                 "gpu_launches": int(total_launches) * args.steps, "setup_s": round(setup_s, 1),
                 "plane_codecs": sorted({str(v) for v in codecs.values()})}
         if file_load:

@@ -128,10 +128,15 @@ class ContainerHandle:
     """An opened container: parsed once on the host, decoded on the GPU.
 
     ``device`` is the CUDA ordinal; the compressed bytes are copied there on
-    first use and stay resident for later random-access decodes."""
+    first use and stay resident for later random-access decodes.  With
+    ``prefetch`` (and a buffer in pinned host memory) the copy of the whole
+    container to the GPU is started before the container is parsed, in slices
+    on a stream of its own, so that the parse costs no time on the way to
+    ``decode_model_streamed``."""
 
-    def __init__(self, buffer, skip_missing: bool = False, device: Optional[int] = None, verify: bool = True):
+    def __init__(self, buffer, skip_missing: bool = False, device: Optional[int] = None, verify: bool = True, prefetch: bool = False):
         self._host = _as_u8_tensor(buffer)
+        self._prefetch = None
         n = self._host.numel()
         if n < len(MAGIC_PTWS):
             raise HeaderParseError("too short to be a .ptwm container")
@@ -139,9 +144,11 @@ class ContainerHandle:
         if not (head.startswith(MAGIC_PTWS) or head.startswith(MAGIC_PTWC) or head.startswith(MAGIC_PTWM) or head.startswith(MAGIC_PTWX)):
             raise HeaderParseError("not a .ptwm container")
         self._layout = "compact" if (head.startswith(MAGIC_PTWS) or head.startswith(MAGIC_PTWC)) else "legacy"
+        self.device = torch.cuda.current_device() if device is None else int(device)
+        if prefetch and self._host.is_pinned():
+            self._start_prefetch()
         self._h = C.c_void_p()
         _check(_lib.lib().ptwm_b200_open(self._host.data_ptr(), n, C.byref(self._h)))
-        self.device = torch.cuda.current_device() if device is None else int(device)
         self.verify = verify
         self.skip_missing = skip_missing
         self._infos = []
@@ -222,9 +229,32 @@ class ContainerHandle:
             raise KeyError(name) from None
 
     # -- device residency -------------------------------------------------------
+    def _start_prefetch(self, slices: int = 16) -> None:
+        dev = torch.device("cuda", self.device)
+        n = self._host.numel()
+        blob = torch.empty(n, dtype=torch.uint8, device=dev)
+        copier = torch.cuda.Stream(dev)
+        copier.wait_stream(torch.cuda.current_stream(dev))  # the buffer may be recycled memory that earlier work still reads
+        step = max(-(-n // slices), 32 << 20)
+        marks = []  # (file offset reached, event recorded after the copy that reached it)
+        with torch.cuda.stream(copier):
+            for a in range(0, n, step):
+                b = min(a + step, n)
+                blob[a:b].copy_(self._host[a:b], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(copier)
+                marks.append((b, ev))
+        self._prefetch = (blob, copier, marks)
+
     def blob_on_device(self) -> torch.Tensor:
         if self._blob_dev is None:
-            self._blob_dev = self._host.to(torch.device("cuda", self.device))
+            if self._prefetch is not None:
+                blob, copier, marks = self._prefetch
+                torch.cuda.current_stream(blob.device).wait_stream(copier)
+                blob.record_stream(torch.cuda.current_stream(blob.device))
+                self._blob_dev = blob
+            else:
+                self._blob_dev = self._host.to(torch.device("cuda", self.device))
         return self._blob_dev
 
     def plan(self, indices: Optional[Sequence[int]] = None) -> DecodePlan:
@@ -287,7 +317,8 @@ class ContainerHandle:
         the GPU on a copy stream while run k is planned on the host and decoded
         on the current stream, so only the first plan and the last decode are
         not hidden behind the PCIe copy.  Nothing of the container stays
-        resident afterwards."""
+        resident afterwards, unless the handle was opened with ``prefetch``:
+        then the copy is already under way and only waited for here."""
         from .sharding import contiguous_shards
         if indices is None:
             indices = list(range(len(self._infos))) if names is None else [self._idx(n) for n in names]
@@ -298,12 +329,17 @@ class ContainerHandle:
         costs = [self._infos[i]["compressed"] for i in indices]
         runs = [[indices[j] for j in r] for r in contiguous_shards(costs, max(1, min(pieces, len(indices)))) if len(r)]
         compute = torch.cuda.current_stream(dev)
-        copier = torch.cuda.Stream(dev)
         flags = self._flags()
         # one buffer for the compressed bytes and one arena for the tensors; the pieces are slices of them
         first = min(self._infos[i]["first_byte"] for i in indices)
         last = max(self._infos[i]["end_byte"] for i in indices)
-        blob = torch.empty(max(last - first, 1), dtype=torch.uint8, device=dev)
+        prefetched = self._prefetch
+        if prefetched is not None:
+            blob, copier, marks = prefetched
+            first = 0
+        else:
+            copier = torch.cuda.Stream(dev)
+            blob = torch.empty(max(last - first, 1), dtype=torch.uint8, device=dev)
         arena_bytes = [sum((self._infos[i]["orig_size"] + 255) // 256 * 256 for i in run) for run in runs]
         arena = torch.empty(max(sum(arena_bytes), 1), dtype=torch.uint8, device=dev)
         copier.wait_stream(compute)  # the buffers may be recycled memory that earlier work on this stream still reads
@@ -313,10 +349,13 @@ class ContainerHandle:
             lo, hi = plan.blob_span
             if plan.out_bytes != nbytes or lo < first or hi > last:
                 raise PtwmError("internal: plan layout differs from the tensor infos")
-            with torch.cuda.stream(copier):
-                blob[lo - first:hi - first].copy_(self._host[lo:hi], non_blocking=True)
-                arrived = torch.cuda.Event()
-                arrived.record(copier)
+            if prefetched is not None:
+                arrived = next(ev for end, ev in marks if end >= hi) if hi > 0 else marks[0][1]
+            else:
+                with torch.cuda.stream(copier):
+                    blob[lo - first:hi - first].copy_(self._host[lo:hi], non_blocking=True)
+                    arrived = torch.cuda.Event()
+                    arrived.record(copier)
             out = arena[at:at + nbytes]
             at += nbytes
             scratch = torch.empty(plan.scratch_bytes, dtype=torch.uint8, device=dev) if plan.scratch_bytes else None

@@ -1088,7 +1088,7 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
 constexpr int TANS_CTA_CHUNKS = 32;
 constexpr int TANS_SYM_BYTES = 2048 * 32;      // [state][lane] of u8
 constexpr int TANS_NB_BYTES = 2048 * 2 * 32;   // [state][lane] of u16
-constexpr int TANS_SMEM = TANS_SYM_BYTES + TANS_NB_BYTES;
+constexpr int TANS_SMEM = TANS_SYM_BYTES + TANS_NB_BYTES + RING_SMEM;  // and the per-lane ring of stream bytes
 
 __global__ void __launch_bounds__(32) tans_decode_kernel(const DecodeItem* __restrict__ items, uint32_t n_items, Bases bases, uint32_t* __restrict__ status) {
     extern __shared__ __align__(16) uint8_t smem[];
@@ -1099,6 +1099,7 @@ __global__ void __launch_bounds__(32) tans_decode_kernel(const DecodeItem* __res
     const uint8_t* src = rd(bases, it.src);
     uint8_t* sym_tab = smem + lane;
     uint8_t* nb_tab = smem + TANS_SYM_BYTES + lane * 2;
+    Ring ring{reinterpret_cast<uint32_t*>(smem + TANS_SYM_BYTES + TANS_NB_BYTES) + lane};
     auto sym_at = [&](uint32_t u) -> uint8_t& { return sym_tab[u << 5]; };
     auto nb_at = [&](uint32_t u) -> uint16_t& { return *reinterpret_cast<uint16_t*>(nb_tab + (u << 6)); };
     uint32_t err = ST_OK;
@@ -1131,7 +1132,7 @@ __global__ void __launch_bounds__(32) tans_decode_kernel(const DecodeItem* __res
                 uint32_t sy = sym_at(u);
                 uint32_t x = norm[sy]++;
                 uint32_t nb = 11 - (31 - __clz(x));
-                nb_at(u) = uint16_t(((x << nb) - 2048) | (nb << 11));
+                nb_at(u) = uint16_t((((x << nb) - 2048) << 5) | nb);  // baseline above the bit count: a shift by the entry takes its low five bits
             }
         }
     }
@@ -1144,37 +1145,53 @@ __global__ void __launch_bounds__(32) tans_decode_kernel(const DecodeItem* __res
         if (total_bits > bslen * 8) err = ST_BAD_HEADER;
         else {
             // LIFO reader (mod.rs:118-147): the stream is read from its last byte down, every byte from its high bit
-            // down.  The `cnt` unread bits sit at the top of `cont`, the next to be used highest, so taking n bits is
+            // down.  The `cnt` unread bits sit at the top of the 64-bit container c_hi:c_lo, the next to be used highest, so taking n bits is
             // one funnel shift; a word read little-endian from below the read position has its bytes in that order.
             uint32_t bi = uint32_t((total_bits + 7) >> 3);  // bytes that hold declared bits; the next to load is bs[bi-1]
-            uint64_t cont = 0;
+            // (the container is two words, so that every shift on the way of a symbol is one funnel shift)
+            uint32_t c_hi = 0, c_lo = 0;
             int32_t cnt = 0;
             const uint32_t top = uint32_t(total_bits & 7);
-            if (top) { --bi; cont = uint64_t(bs[bi] & ((1u << top) - 1)) << (64 - top); cnt = int32_t(top); }
-            // Words are requested one refill ahead: with a single warp per SM nothing else would hide the latency of
-            // the load.  `ahead` holds the word below the read position whenever that position is word aligned and
-            // at least four bytes are left.
-            auto word_below = [&](uint32_t at) -> uint32_t {
-                return (at >= 4 && ((reinterpret_cast<uintptr_t>(bs) + at) & 3) == 0) ? __ldg(reinterpret_cast<const uint32_t*>(bs + at - 4)) : 0u;
+            if (top) { --bi; c_hi = (bs[bi] & ((1u << top) - 1)) << (32 - top); cnt = int32_t(top); }
+            // Stream bytes pass through a 64-byte ring per lane in shared memory, filled downward in aligned 16-byte
+            // blocks that are requested one step ahead (`pending`).  Positions are 32-bit offsets from `org`, a
+            // 16-byte aligned address two blocks below the stream.  A lane's loads must not be waited for by the other
+            // lanes of the warp (the scoreboard is per warp), so blocks are taken by all lanes with room at once, when
+            // any lane runs low, every few groups.
+            const uintptr_t lo16 = (reinterpret_cast<uintptr_t>(bases.blob) + bases.blob_first) & ~uintptr_t(15);
+            const uintptr_t hi16 = (reinterpret_cast<uintptr_t>(bases.blob) + bases.blob_end + 15) & ~uintptr_t(15);
+            const uintptr_t org = (reinterpret_cast<uintptr_t>(bs) & ~uintptr_t(15)) - 32;
+            const uint32_t start = uint32_t(reinterpret_cast<uintptr_t>(bs) - org);
+            uint32_t rp = start + bi;  // one past the next byte to read (moves down)
+            uint32_t fetched = (rp + 15) & ~15u;
+            for (int k = 0; k < 3; ++k) { fetched -= 16; ring.put(fetched, fetch16(org + fetched, lo16, hi16)); }
+            uint4 pending = fetch16(org + fetched - 16, lo16, hi16);
+            auto ring_top_up = [&]() {
+                if (__any_sync(__activemask(), rp - fetched < 32 && fetched > start)) {
+                    if (rp - fetched <= 48 && fetched > start) { fetched -= 16; ring.put(fetched, pending); pending = fetch16(org + fetched - 16, lo16, hi16); }
+                }
             };
-            uint32_t ahead = 0;
             auto refill = [&]() {  // up to more than 32 bits, by bytes until the position is word aligned, then by words
-                while (uint32_t(cnt) <= 32u && bi > 0) {  // (a negative count only occurs in a group that is about to be decoded again)
-                    if (bi >= 4 && ((reinterpret_cast<uintptr_t>(bs) + bi) & 3) == 0) {
-                        cont |= uint64_t(ahead) << (32 - cnt);
-                        cnt += 32; bi -= 4;
-                        ahead = word_below(bi);
+                while (uint32_t(cnt) <= 32u && rp > start) {  // (a negative count only occurs in a group that is about to be decoded again)
+                    if (rp - start >= 4 && (rp & 3) == 0) {
+                        const uint32_t word = ring.word(rp - 4);
+                        const uint32_t s = uint32_t(32 - cnt);  // 0..32: the word goes below the cnt bits held
+                        c_hi |= __funnelshift_lc(word, 0u, s);
+                        c_lo |= __funnelshift_lc(0u, word, s);
+                        cnt += 32; rp -= 4;
                     } else {
-                        --bi; cont |= uint64_t(bs[bi]) << (56 - cnt); cnt += 8;
-                        ahead = word_below(bi);
+                        --rp;
+                        const uint64_t t = uint64_t(ring.byte(rp)) << (56 - cnt);
+                        c_hi |= uint32_t(t >> 32); c_lo |= uint32_t(t);
+                        cnt += 8;
                     }
                 }
             };
-            ahead = word_below(bi);
-            auto take = [&](uint32_t nb) -> uint32_t {  // nb <= 11
-                const uint32_t hi = uint32_t(cont >> 32);
-                const uint32_t v = __funnelshift_l(hi, 0u, nb);  // the top nb bits; 0 for nb == 0
-                cont <<= nb; cnt -= int32_t(nb);
+            auto take = [&](uint32_t e) -> uint32_t {  // the bit count (<= 11) is the low five bits of e, which is all a funnel shift looks at
+                const uint32_t v = __funnelshift_l(c_hi, 0u, e);  // the top bits; 0 for a count of 0
+                c_hi = __funnelshift_l(c_lo, c_hi, e);
+                c_lo = __funnelshift_l(0u, c_lo, e);
+                cnt -= int32_t(e & 31u);
                 return v;
             };
             refill();
@@ -1183,9 +1200,9 @@ __global__ void __launch_bounds__(32) tans_decode_kernel(const DecodeItem* __res
             // one symbol with the reference's checks
             auto one_symbol = [&]() -> uint32_t {
                 refill();
-                const uint32_t sy = sym_at(state), e = nb_at(state), nb = e >> 11;
+                const uint32_t sy = sym_at(state), e = nb_at(state), nb = e & 31u;
                 if (int32_t(nb) > cnt) { err = ST_STREAM_UNDERRUN; return sy; }
-                state = (e & 2047u) + take(nb);
+                state = (e >> 5) + take(e);
                 if (state >= 2048) { err = ST_STREAM_UNDERRUN; state = 0; }
                 return sy;
             };
@@ -1193,22 +1210,23 @@ __global__ void __launch_bounds__(32) tans_decode_kernel(const DecodeItem* __res
             // stream is at its end) and four symbols take at most 44, around ten on an exponent plane, so the
             // halves run unchecked; a group that ran out of bits is decoded again one symbol at a time.
             auto dec8 = [&](uint32_t& s_lo, uint32_t& s_hi) {
-                const uint64_t cont0 = cont;
+                const uint32_t hi0 = c_hi, lo0 = c_lo;
                 const int32_t cnt0 = cnt;
-                const uint32_t bi0 = bi, state0 = state, ahead0 = ahead;
+                ring_top_up();
+                const uint32_t rp0 = rp, state0 = state;
                 int32_t lowest = 0;
                 s_lo = 0; s_hi = 0;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     if ((j & 3) == 0) refill();
                     const uint32_t sy = sym_at(state), e = nb_at(state);
-                    state = ((e & 2047u) + take(e >> 11)) & 2047u;
+                    state = (e >> 5) + take(e);  // below 2048 whatever the stream holds: the baseline has its low bits clear and the stream adds fewer than 2^count
                     lowest |= cnt;
                     const uint32_t ins = (0x3210u & ~(0xFu << (4 * (j & 3)))) | (4u << (4 * (j & 3)));
                     if (j < 4) s_lo = __byte_perm(s_lo, sy, ins); else s_hi = __byte_perm(s_hi, sy, ins);
                 }
                 if (lowest < 0) {
-                    cont = cont0; cnt = cnt0; bi = bi0; state = state0; ahead = ahead0;
+                    c_hi = hi0; c_lo = lo0; cnt = cnt0; rp = rp0; state = state0;
                     s_lo = 0; s_hi = 0;
                     for (uint32_t j = 0; j < 8 && !err; ++j) {
                         uint32_t sy = one_symbol();
@@ -1219,6 +1237,7 @@ __global__ void __launch_bounds__(32) tans_decode_kernel(const DecodeItem* __res
             uint32_t pos = 0, remaining = it.n;
             auto short_group = [&](uint32_t g) {
                 uint64_t syms = 0;
+                ring_top_up();
                 for (uint32_t j = 0; j < g && !err; ++j) syms |= uint64_t(one_symbol()) << (8 * j);
                 emit(ep, pos, g, syms);
                 pos += g; remaining -= g;
@@ -1229,7 +1248,7 @@ __global__ void __launch_bounds__(32) tans_decode_kernel(const DecodeItem* __res
             }
             if (!err) fast_groups(ep, it.n, pos, remaining, dec8);
             while (remaining && !err) short_group(remaining < 8 ? remaining : 8);
-            if (!err && (cnt != 0 || bi != 0 || state != 0)) err = ST_NOT_CONSUMED;  // mod.rs:442-449
+            if (!err && (cnt != 0 || rp != start || state != 0)) err = ST_NOT_CONSUMED;  // mod.rs:442-449
         }
     }
     if (err) atomicMax(&status[it.id], err);

@@ -331,3 +331,23 @@ def test_per_plane_ops_match_oracle(n, opts):
     for s in specs[:3]:
         frame = oracle.write_compact(s, emit_hash=True)
         assert bytes_of(ptwm_b200.Decompressor(ptwm_b200.DecompressionConfig(device=0)).decompress(frame)) == s.raw
+
+
+def test_prefetched_handle_decodes_the_same():
+    # the copy of a pinned container to the GPU starts before the parse; streamed and random-access decodes use it
+    specs = mixed_model()
+    blob = oracle.write_container(specs, chunk_size=4096, emit_crc=True, emit_hash=True)
+    pinned = torch.empty(len(blob), dtype=torch.uint8, pin_memory=True)
+    pinned.copy_(torch.frombuffer(bytearray(blob), dtype=torch.uint8))
+    for pieces in (1, 4):
+        h = ptwm_b200.ContainerHandle(pinned, device=0, prefetch=True)
+        assert h._prefetch is not None
+        got = dict(h.decode_model_streamed(pieces=pieces))
+        assert all(bytes_of(got[s.name]) == s.raw for s in specs)
+        some = [specs[2].name, specs[5].name]
+        part = dict(h.decode_model_streamed(names=some, pieces=2))
+        assert all(bytes_of(part[n]) == next(s.raw for s in specs if s.name == n) for n in some)
+    h = ptwm_b200.ContainerHandle(pinned, device=0, prefetch=True)
+    assert bytes_of(h.decode(specs[0].name)) == specs[0].raw
+    # pageable memory: the option is ignored
+    assert ptwm_b200.ContainerHandle(blob, device=0, prefetch=True)._prefetch is None
