@@ -1216,12 +1216,23 @@ __global__ void __launch_bounds__(32) tans_decode_kernel(const DecodeItem* __res
                 const uint32_t rp0 = rp, state0 = state;
                 int32_t lowest = 0;
                 s_lo = 0; s_hi = 0;
+                // Away from the stream's first bytes the read position is word aligned and stays so: a refill is then
+                // one word, taken or not, with no loop and no byte steps.  `lowest` starts negative otherwise, which
+                // sends the group down the checked path.
+                const bool words = (rp & 3) == 0 && rp - start >= 8;
+                if (!words) lowest = -1;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    if ((j & 3) == 0) refill();
+                    if ((j & 3) == 0 && cnt <= 32) {
+                        const uint32_t word = ring.word(rp - 4);
+                        const uint32_t s = uint32_t(32 - cnt);
+                        c_hi |= __funnelshift_lc(word, 0u, s);
+                        c_lo |= __funnelshift_lc(0u, word, s);
+                        cnt += 32; rp -= 4;
+                    }
                     const uint32_t sy = sym_at(state), e = nb_at(state);
                     state = (e >> 5) + take(e);  // below 2048 whatever the stream holds: the baseline has its low bits clear and the stream adds fewer than 2^count
-                    lowest |= cnt;
+                    if ((j & 3) == 3) lowest |= cnt;  // the count only falls between two refills
                     const uint32_t ins = (0x3210u & ~(0xFu << (4 * (j & 3)))) | (4u << (4 * (j & 3)));
                     if (j < 4) s_lo = __byte_perm(s_lo, sy, ins); else s_hi = __byte_perm(s_hi, sy, ins);
                 }
