@@ -1031,14 +1031,21 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
             const uint32_t lo0 = c_lo, hi0 = c_hi;
             const int32_t cnt0 = cnt;
             const uint32_t rp0 = rp;
-            int32_t lowest = 0;
+            // With eight or more stream bytes left both refills of the group are whole aligned words: one conditional
+            // word each, no partial-word handling.  Otherwise the group starts with a negative `lowest` and goes down
+            // the checked path.
+            int32_t lowest = rp - start >= 8 ? 0 : -1;
             s_lo = 0; s_hi = 0;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                if ((j & 3) == 0) take_word();
+                if ((j & 3) == 0 && cnt <= 32) {
+                    push(__byte_perm(ring.word(rp - 4), 0, 0x0123));  // byte rp-1 becomes the lowest
+                    cnt += 32; rp -= 4;
+                }
                 uint32_t e = peek();
                 const uint32_t nb = e >> 8;
-                drop(nb); cnt -= int32_t(nb); lowest |= cnt;
+                drop(nb); cnt -= int32_t(nb);
+                if ((j & 3) == 3) lowest |= cnt;  // the count only falls between two refills
                 const uint32_t ins = (0x3210u & ~(0xFu << (4 * (j & 3)))) | (4u << (4 * (j & 3)));  // low byte of e into byte j & 3
                 if (j < 4) s_lo = __byte_perm(s_lo, e, ins); else s_hi = __byte_perm(s_hi, e, ins);
             }
