@@ -210,6 +210,8 @@ def run_ours(args):
     if args.layers:
         cfg["layers"] = args.layers
     shapes = model_shapes(**cfg)
+    if not args.pieces:
+        args.pieces = 1 if world == 1 else 8
     if args.workload == "c1x16":  # profiling-sized stand-in: sixteen bf16 [4096,4096] tensors (0.54 GB), same recipe
         shapes = [(f"w{i}.weight", (4096, 4096), False) for i in range(16)]
         cfg["layers"] = 0
@@ -311,7 +313,7 @@ def run_ours(args):
             for it in range(args.warmup + args.steps):
                 torch.cuda.synchronize()
                 t0 = time.perf_counter()
-                state = ptwm_b200.load_file(path, local, pieces=args.pieces, verify=bool(args.crc), threads=args.file_threads, timings=info)
+                state = ptwm_b200.load_file(path, local, pieces=8, verify=bool(args.crc), threads=args.file_threads, timings=info)
                 torch.cuda.synchronize()
                 if it >= args.warmup:
                     times.append(time.perf_counter() - t0)
@@ -395,7 +397,7 @@ def main():
     ap.add_argument("--chunk", type=int, default=32768, help="plane bytes per chunk")
     ap.add_argument("--codec", choices=["rans", "huffman", "auto", "identity"], default="rans")
     ap.add_argument("--crc", action="store_true", help="write and verify plane CRC-32s")
-    ap.add_argument("--pieces", type=int, default=8, help="runs of tensors the end-to-end path copies and decodes in a pipeline")
+    ap.add_argument("--pieces", type=int, default=0, help="runs of tensors the end-to-end path decodes one after the other as their bytes arrive; 0 = 1 at one GPU, where the whole copy is started before the parse and a decode beside it only stretched the copy (213 ms with 1 piece, 219 with 4, 227 with 8), else 8")
     ap.add_argument("--layers", type=int, default=0, help="fewer transformer layers than 32 (for quick checks; not the benchmark workload)")
     ap.add_argument("--cpu-layers", type=int, default=4, help="layers in the CPU baseline sample")
     ap.add_argument("--no-cpu", action="store_true")

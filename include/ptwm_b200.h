@@ -149,6 +149,10 @@ void ptwm_b200_plan_stats(const ptwm_b200_plan* p, uint64_t* bytes_read, uint64_
 int64_t ptwm_b200_plan_run(ptwm_b200_plan* p, uint64_t blob_dev_ptr, uint64_t blob_first, uint64_t blob_len, uint64_t out_dev_ptr, uint64_t out_cap,
                            uint64_t scratch_dev_ptr, uint64_t scratch_cap, uint32_t flags, uint32_t device_ordinal, uint64_t stream);
 /* Wait for an enqueued run and evaluate decode status and integrity checks. */
+/* Copy the plan's work lists to the device now instead of in the first
+ * ptwm_b200_plan_run.  The copies are synchronous: a pipeline that enqueues large
+ * transfers prepares its plans first, so that no run waits behind them. */
+int64_t ptwm_b200_plan_prepare(ptwm_b200_plan* p, uint32_t device_ordinal);
 int64_t ptwm_b200_plan_finish(ptwm_b200_plan* p, uint32_t flags, uint32_t device_ordinal, uint64_t stream);
 
 

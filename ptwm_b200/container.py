@@ -108,6 +108,10 @@ class DecodePlan:
         _check(_lib.lib().ptwm_b200_plan_run(self._p, (blob_dev.data_ptr() - blob_first) if blob_dev.numel() else 0, blob_first, blob_dev.numel(),
                                              out.data_ptr() if out.numel() else 0, out.numel(), sp, sc, flags, dev, stream))
 
+    def prepare(self, device: int) -> None:
+        """Send the work lists to the device now rather than in the first run."""
+        _check(_lib.lib().ptwm_b200_plan_prepare(self._p, device))
+
     def finish(self, device: int, flags: int = 0, stream: Optional[int] = None) -> None:
         if stream is None:
             stream = stream_handle(device)
@@ -229,13 +233,13 @@ class ContainerHandle:
             raise KeyError(name) from None
 
     # -- device residency -------------------------------------------------------
-    def _start_prefetch(self, slices: int = 16) -> None:
+    def _start_prefetch(self, slice_bytes: int = 64 << 20) -> None:
         dev = torch.device("cuda", self.device)
         n = self._host.numel()
         blob = torch.empty(n, dtype=torch.uint8, device=dev)
         copier = torch.cuda.Stream(dev)
         copier.wait_stream(torch.cuda.current_stream(dev))  # the buffer may be recycled memory that earlier work still reads
-        step = max(-(-n // slices), 32 << 20)
+        step = slice_bytes  # small enough that nothing else queued on the copy engine waits long behind one
         marks = []  # (file offset reached, event recorded after the copy that reached it)
         with torch.cuda.stream(copier):
             for a in range(0, n, step):
@@ -344,8 +348,12 @@ class ContainerHandle:
         arena = torch.empty(max(sum(arena_bytes), 1), dtype=torch.uint8, device=dev)
         copier.wait_stream(compute)  # the buffers may be recycled memory that earlier work on this stream still reads
         jobs, result, at = [], [], 0
-        for run, nbytes in zip(runs, arena_bytes):
-            plan = DecodePlan(self, run)
+        # every plan is made and sent to the device before the first launch: its small synchronous copies would
+        # otherwise queue behind the container's slices on the copy engine and hold back the launches of later pieces
+        plans = [DecodePlan(self, run) for run in runs]
+        for plan in plans:
+            plan.prepare(self.device)
+        for plan, nbytes in zip(plans, arena_bytes):
             lo, hi = plan.blob_span
             if plan.out_bytes != nbytes or lo < first or hi > last:
                 raise PtwmError("internal: plan layout differs from the tensor infos")

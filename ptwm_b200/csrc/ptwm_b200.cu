@@ -724,6 +724,18 @@ int64_t ptwm_b200_plan_run(ptwm_b200_plan* p, uint64_t blob_dev_ptr, uint64_t bl
     return evaluate(*p, *d, flags, st);
 }
 
+int64_t ptwm_b200_plan_prepare(ptwm_b200_plan* p, uint32_t device_ordinal) {
+    if (!p) return fail(PTWM_RC_INVALID_INPUT, "null plan");
+    DeviceGuard guard{int(device_ordinal)};
+    if (guard.err != cudaSuccess) return fail(PTWM_RC_CUDA, std::string("cudaSetDevice: ") + cudaGetErrorString(guard.err));
+    DeviceState* ds;
+    int64_t rc = device_state(int(device_ordinal), &ds);
+    if (rc < 0) return rc;
+    std::lock_guard<std::mutex> lock(p->mu);
+    DevicePlan* d;
+    return device_plan(*p, int(device_ordinal), &d);
+}
+
 int64_t ptwm_b200_plan_finish(ptwm_b200_plan* p, uint32_t flags, uint32_t device_ordinal, uint64_t stream) {
     if (!p) return fail(PTWM_RC_INVALID_INPUT, "null plan");
     DeviceGuard guard{int(device_ordinal)};

@@ -215,8 +215,11 @@ def _decode_stream(handle: ContainerHandle, stream: _FileStream, indices: Sequen
     arena = torch.empty(max(sum(arena_bytes), 1), dtype=torch.uint8, device=dev)
     first = stream.first
     jobs, at = [], 0
-    for run, nbytes in zip(runs, arena_bytes):
-        plan = DecodePlan(handle, run)
+    # plans first: their small synchronous copies to the device would otherwise queue behind the file's slices
+    plans = [DecodePlan(handle, run) for run in runs]
+    for plan in plans:
+        plan.prepare(handle.device)
+    for plan, nbytes in zip(plans, arena_bytes):
         lo, hi = plan.blob_span
         if plan.out_bytes != nbytes or (hi > lo and (lo < first or hi > stream.last)):
             raise PtwmError("internal: plan layout differs from the tensor infos")
