@@ -351,3 +351,17 @@ def test_prefetched_handle_decodes_the_same():
     assert bytes_of(h.decode(specs[0].name)) == specs[0].raw
     # pageable memory: the option is ignored
     assert ptwm_b200.ContainerHandle(blob, device=0, prefetch=True)._prefetch is None
+
+
+def test_tans_full_size_planes():
+    # four bf16 [4096,4096] tensors (BASELINE config C1's shape) with tANS forced on every plane, 64 KiB chunks:
+    # 1024 tANS streams of 65536 symbols, the case the tANS profile summary was captured on
+    specs = []
+    for i in range(4):
+        w = (torch.randn(4096, 4096, generator=torch.Generator().manual_seed(i)) * 0.02).to(torch.bfloat16)
+        specs.append(oracle.TensorSpec(f"w{i}", oracle.DT_BF16, [4096, 4096], w.view(torch.uint8).numpy().tobytes()))
+    blob = oracle.write_container(specs, chunk_size=65536, forced_codec=oracle.TANS)
+    h = ptwm_b200.ContainerHandle(blob, device=0, verify=False)
+    assert any(c == oracle.TANS for t in oracle.Container(blob).tensors for c in [p["codec"] for p in t["planes"]])
+    for (name, t), s in zip(h.decode_model(), specs):
+        assert name == s.name and bytes_of(t) == s.raw
