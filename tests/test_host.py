@@ -236,3 +236,40 @@ def test_missing_library_fails_loudly(tmp_path, monkeypatch):
     monkeypatch.setattr(_lib, "_lib", None)
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         _lib.lib()
+
+
+def test_malformed_per_plane_op_chains_are_rejected(L, monkeypatch):
+    """Chains that hang IntDelta / MantissaZeroStrip nodes off a byte split in ways the production builders never do:
+    both the oracle and the library's parser refuse them (an error or an unsupported tensor), neither guesses."""
+    import numpy as np
+    import oracle
+    raw = (np.arange(4096, dtype=np.uint16) & 0xFFF0).tobytes()
+    spec = oracle.TensorSpec("_", oracle.DT_BF16, [4096], raw, post={1: ("intdelta",)})
+    kind, nodes, edges, terms = oracle.chain_graph(spec)
+    good = oracle.write_compact(spec, emit_hash=True)
+    assert oracle.decode_compact(good)[0] == raw
+    rc, h = _open(L, good)
+    assert rc == 0 and _infos(L, h)[0].supported
+    L.ptwm_b200_close(h)
+    split = 2
+    cases = {
+        "plane out of range": (nodes, edges[:2] + [(split, 5, 3, 0)], terms),
+        "op fed from before the split": (nodes, edges[:2] + [(1, 0, 3, 0)], terms),
+        "terminal skips the op": (nodes, edges, [terms[0], (split, 1, terms[1][2])]),
+        "terminal on the wrong output": (nodes, edges, [terms[0], (3, 1, terms[1][2])]),
+        "two ops on one plane": (nodes + [(oracle.OP_INTDELTA, b"")], edges + [(split, 1, 4, 0)], terms),
+        "op chained on an op": (nodes + [(oracle.OP_INTDELTA, b"")], edges + [(3, 0, 4, 0)], [terms[0], (4, 0, terms[1][2])]),
+        "strip of zero bits": (nodes[:3] + [(oracle.OP_MZS, b"\x00")], edges, terms),
+        "strip of eight bits": (nodes[:3] + [(oracle.OP_MZS, b"\x08")], edges, terms),
+        "strip without its parameter": (nodes[:3] + [(oracle.OP_MZS, b"")], edges, terms),
+        "delta with a parameter": (nodes[:3] + [(oracle.OP_INTDELTA, b"\x01")], edges, terms),
+    }
+    for what, graph in cases.items():
+        monkeypatch.setattr(oracle, "chain_graph", lambda s, g=graph: (kind, list(g[0]), list(g[1]), list(g[2])))
+        frame = oracle.write_compact(spec, emit_hash=True)
+        with pytest.raises(oracle.OracleError):
+            oracle.decode_compact(frame)
+        rc, h = _open(L, frame)
+        if rc == 0:
+            assert not _infos(L, h)[0].supported, what
+            L.ptwm_b200_close(h)
