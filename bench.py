@@ -288,9 +288,15 @@ def run_ours(args):
     for it in range(args.warmup + args.steps):
         barrier()
         t0 = time.perf_counter()
-        h2 = ptwm_b200.ContainerHandle(host_blob, device=local, verify=bool(args.crc), prefetch=(world == 1))  # one rank needs every byte: start the copy before the parse
+        if world == 1:  # one rank needs every byte: start the copy before the parse
+            h2 = ptwm_b200.ContainerHandle(host_blob, device=local, verify=bool(args.crc), prefetch=True)
+            share = mine
+        else:  # a rank reads only the records of its shard (a contiguous run cut by record bytes; the shards partition the container)
+            h2 = ptwm_b200.ContainerHandle(host_blob, device=local, verify=bool(args.crc), shard=(rank, world))
+            share = h2.shard_indices()
         t1 = time.perf_counter()
-        decoded = h2.decode_model_streamed(indices=mine, pieces=args.pieces)
+        decoded = h2.decode_model_streamed(indices=share, pieces=args.pieces)
+        e2e_tensors = len(decoded)
         t2 = time.perf_counter()
         torch.cuda.synchronize()
         dt = torch.tensor([time.perf_counter() - t0], device=device, dtype=torch.float64)
@@ -329,10 +335,12 @@ def run_ours(args):
             if os.path.exists(path):
                 os.remove(path)
 
-    totals = torch.tensor([float(my_raw), float(hi - lo), float(plan.bytes_read), float(plan.launches)], device=device, dtype=torch.float64)
+    totals = torch.tensor([float(my_raw), float(hi - lo), float(plan.bytes_read), float(plan.launches), float(e2e_tensors)], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(totals, op=dist.ReduceOp.SUM)
-    total_raw, total_h2d, total_read, total_launches = (float(x) for x in totals.tolist())
+    total_raw, total_h2d, total_read, total_launches, total_e2e_tensors = (float(x) for x in totals.tolist())
+    if int(total_e2e_tensors) != len(infos):
+        raise SystemExit(f"end-to-end leg decoded {int(total_e2e_tensors)} tensors over all ranks, the container holds {len(infos)}")
 
     if rank == 0:
         peak, peak_kind = peak_hbm_gbs()
@@ -357,7 +365,7 @@ def run_ours(args):
                         "ms_per_step": e2e_s * 1e3,
                         "parts_ms": {"parse": 1e3 * statistics.mean(p[0] for p in e2e_parts), "plan_copy_decode": 1e3 * statistics.mean(p[1] for p in e2e_parts)},
                         "pieces": args.pieces,
-                        "includes": "ContainerHandle(pinned host bytes).decode_model_streamed: parse, per piece plan + H2D copy + decode + status read-back, the copies overlapping the rest (at one GPU the copy starts before the parse)"},
+                        "includes": "ContainerHandle(pinned host bytes).decode_model_streamed: parse, per piece plan + H2D copy + decode + status read-back, the copies overlapping the rest (at one GPU the copy starts before the parse; at more a rank opens the container with shard=(rank, world) and reads only its own records)"},
                 "gpu_launches": int(total_launches) * args.steps, "setup_s": round(setup_s, 1),
                 "plane_codecs": sorted({str(v) for v in codecs.values()})}
         if file_load:

@@ -98,6 +98,13 @@ void ptwm_b200_blake3(const uint8_t* data, size_t len, uint8_t out[32]);
  * bytes are only read during this call.  A frame opens as a container with one
  * tensor named "_". */
 int64_t ptwm_b200_open(const uint8_t* blob, size_t blob_len, ptwm_b200_container** out);
+/* ptwm_b200_open for one rank of a multi-GPU load: header, tables and index are
+ * read whole, tensor records only for shard `rank` of `world`, a contiguous run
+ * of records cut by record bytes (the same cut on every rank; the shards
+ * partition the container).  The other tensors are listed with supported = 0
+ * and their record size as `compressed`.  Compact layout only; the legacy
+ * layout and single frames are read whole. */
+int64_t ptwm_b200_open_shard(const uint8_t* blob, size_t blob_len, uint32_t rank, uint32_t world, ptwm_b200_container** out);
 void ptwm_b200_close(ptwm_b200_container* c);
 
 typedef struct ptwm_b200_tensor_info {

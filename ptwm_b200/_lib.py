@@ -64,6 +64,7 @@ _SIGNATURES = {
     "ptwm_b200_last_error": (C.c_char_p, []),
     "ptwm_b200_blake3": (None, [C.c_char_p, C.c_size_t, C.c_char_p]),
     "ptwm_b200_open": (C.c_int64, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
+    "ptwm_b200_open_shard": (C.c_int64, [C.c_void_p, C.c_size_t, C.c_uint32, C.c_uint32, C.POINTER(C.c_void_p)]),
     "ptwm_b200_close": (None, [C.c_void_p]),
     "ptwm_b200_tensor_count": (C.c_size_t, [C.c_void_p]),
     "ptwm_b200_tensor_info_get": (C.c_int64, [C.c_void_p, C.c_size_t, C.POINTER(TensorInfo)]),

@@ -136,9 +136,13 @@ class ContainerHandle:
     ``prefetch`` (and a buffer in pinned host memory) the copy of the whole
     container to the GPU is started before the container is parsed, in slices
     on a stream of its own, so that the parse costs no time on the way to
-    ``decode_model_streamed``."""
+    ``decode_model_streamed``.  ``shard=(rank, world)`` reads only that rank's
+    share of the tensor records (a contiguous run cut by record bytes; the
+    shards of all ranks partition the container), which is what a rank of a
+    multi-GPU load needs and costs a world-th of the parse."""
 
-    def __init__(self, buffer, skip_missing: bool = False, device: Optional[int] = None, verify: bool = True, prefetch: bool = False):
+    def __init__(self, buffer, skip_missing: bool = False, device: Optional[int] = None, verify: bool = True, prefetch: bool = False,
+                 shard: Optional[tuple] = None):
         self._host = _as_u8_tensor(buffer)
         self._prefetch = None
         n = self._host.numel()
@@ -152,7 +156,11 @@ class ContainerHandle:
         if prefetch and self._host.is_pinned():
             self._start_prefetch()
         self._h = C.c_void_p()
-        _check(_lib.lib().ptwm_b200_open(self._host.data_ptr(), n, C.byref(self._h)))
+        if shard is None:
+            _check(_lib.lib().ptwm_b200_open(self._host.data_ptr(), n, C.byref(self._h)))
+        else:  # (rank, world): only this rank's records are read, see shard_indices()
+            _check(_lib.lib().ptwm_b200_open_shard(self._host.data_ptr(), n, int(shard[0]), int(shard[1]), C.byref(self._h)))
+        self.shard = shard
         self.verify = verify
         self.skip_missing = skip_missing
         self._infos = []
@@ -220,6 +228,11 @@ class ContainerHandle:
     def shape(self, name: str):
         inf = self._infos[self._idx(name)]
         return None if inf["shape"] is None else (list(inf["shape"]), inf["dtype_name"])
+
+    def shard_indices(self) -> list[int]:
+        """Tensors this handle can decode: all supported ones, which for a handle opened with
+        ``shard=(rank, world)`` are the supported tensors of that rank's contiguous run of records."""
+        return [i for i, inf in enumerate(self._infos) if inf["supported"]]
 
     def tensor_infos(self) -> list[dict]:
         return [dict(i) for i in self._infos]

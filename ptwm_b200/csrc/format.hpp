@@ -129,6 +129,7 @@ struct TensorDesc {
     uint64_t stored_off = 0;
     std::vector<PlaneDesc> planes;
     std::string unsupported;  // non-empty: outside the hot path (reason)
+    uint64_t record_len = 0;  // compact layout: bytes of the tensor record (known from the index even when the record was not read)
 };
 
 struct SharedState { uint16_t id, codec; uint8_t version, mask; uint64_t hash; uint64_t off, len; bool checked = false; };
@@ -370,6 +371,8 @@ inline void check_o1sac(const uint8_t* state, uint64_t state_len, uint8_t versio
 class FileReader {
   public:
     FileReader(const uint8_t* buf, size_t len) : b_(buf), n_(len) {}
+    // Only the records of shard `rank` of `world` are read (compact layout; the other layouts are read whole).
+    void set_shard(uint32_t rank, uint32_t world) { shard_rank_ = rank; shard_world_ = world; }
     ParsedFile parse() {
         static const uint8_t PTWC[9] = {0x89, 'P', 'T', 'W', 'C', '\r', '\n', 0x1a, '\n'};
         static const uint8_t PTWS[5] = {0x89, 'P', 'T', 'W', 'S'};
@@ -388,6 +391,7 @@ class FileReader {
     std::vector<detail::RawChain> registry_;
     ParsedFile out_;
     std::mutex shared_mu_;
+    uint32_t shard_rank_ = 0, shard_world_ = 0;
 
     void make_chunks(PlaneDesc& p, bool chunked, const std::vector<std::pair<uint32_t, uint32_t>>& entries, uint64_t inline_off, uint64_t inline_len,
                      uint8_t state_version, uint16_t state_info) {
@@ -587,14 +591,38 @@ class FileReader {
         out_.tensors.resize(recs.size());
         std::vector<std::string> failed(recs.size());
         std::vector<uint8_t> has_failed(recs.size(), 0);
+        // A rank of a multi-GPU load reads only the records of its own shard: a contiguous run chosen by record
+        // bytes, the same cut on every rank (rank r ends at the first record where the running size reaches
+        // (r + 1) / world of the total, a record counting where its middle falls).
+        size_t shard_lo = 0, shard_hi = recs.size();
+        if (shard_world_ > 1) {
+            double total = 0;
+            for (auto& r : recs) total += double(r.len);
+            std::vector<size_t> bounds{0};
+            double run = 0;
+            size_t i = 0;
+            for (uint32_t r = 1; r < shard_world_; ++r) {
+                const double target = total * r / shard_world_;
+                while (i < recs.size() && run + double(recs[i].len) / 2 <= target) { run += double(recs[i].len); ++i; }
+                bounds.push_back(i);
+            }
+            bounds.push_back(recs.size());
+            shard_lo = bounds[shard_rank_]; shard_hi = bounds[shard_rank_ + 1];
+        }
         auto read_one = [&](size_t i) {
             TensorDesc t;
+            if (i < shard_lo || i >= shard_hi) {
+                t.unsupported = "record not read: it belongs to another rank's shard";
+                t.name = recs[i].name; t.record_len = recs[i].len;
+                out_.tensors[i] = std::move(t);
+                return;
+            }
             try { t = read_record(recs[i].off, recs[i].off + recs[i].len); }
             catch (const FormatError& e) {
                 if (!e.unsupported) { failed[i] = e.what(); has_failed[i] = 1; return; }
                 t = TensorDesc{}; t.unsupported = e.what();
             }
-            t.name = recs[i].name;
+            t.name = recs[i].name; t.record_len = recs[i].len;
             out_.tensors[i] = std::move(t);
         };
         size_t workers = std::thread::hardware_concurrency();

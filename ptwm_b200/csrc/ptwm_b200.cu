@@ -618,11 +618,16 @@ int64_t ptwm_plane_codec_v1_decode(const uint8_t* in, size_t in_len, uint8_t* ou
     return ptwm_plane_codec_v1_decode_stateful(0, nullptr, 0, in, in_len, out, out_len);
 }
 
-int64_t ptwm_b200_open(const uint8_t* blob, size_t blob_len, ptwm_b200_container** out) {
+int64_t ptwm_b200_open(const uint8_t* blob, size_t blob_len, ptwm_b200_container** out) { return ptwm_b200_open_shard(blob, blob_len, 0, 1, out); }
+
+int64_t ptwm_b200_open_shard(const uint8_t* blob, size_t blob_len, uint32_t rank, uint32_t world, ptwm_b200_container** out) {
     if (!blob || !out) return fail(PTWM_RC_INVALID_INPUT, "null argument");
+    if (!world || rank >= world) return fail(PTWM_RC_INVALID_INPUT, "rank must be below world");
     try {
         std::unique_ptr<ptwm_b200_container> c(new ptwm_b200_container);
-        c->file = FileReader(blob, blob_len).parse();
+        FileReader reader(blob, blob_len);
+        reader.set_shard(rank, world);
+        c->file = reader.parse();
         c->blob_len = blob_len;
         for (const TensorDesc& t : c->file.tensors) {
             uint64_t comp = 0, lo = UINT64_MAX, hi = 0; uint8_t crc = 0;
@@ -633,6 +638,7 @@ int64_t ptwm_b200_open(const uint8_t* blob, size_t blob_len, ptwm_b200_container
                 for (const ChunkDesc& ch : p.chunks) if (ch.state_len) { lo = std::min(lo, ch.state_off); hi = std::max(hi, ch.state_off + ch.state_len); }
             }
             if (lo == UINT64_MAX) lo = hi = 0;
+            if (!comp && t.record_len && !t.unsupported.empty()) comp = t.record_len;  // a record that was not read: its size from the index
             c->compressed.push_back(comp); c->first_byte.push_back(lo); c->end_byte.push_back(hi); c->has_crc.push_back(crc);
         }
         *out = c.release();

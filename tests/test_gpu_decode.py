@@ -365,3 +365,19 @@ def test_tans_full_size_planes():
     assert any(c == oracle.TANS for t in oracle.Container(blob).tensors for c in [p["codec"] for p in t["planes"]])
     for (name, t), s in zip(h.decode_model(), specs):
         assert name == s.name and bytes_of(t) == s.raw
+
+
+def test_sharded_handles_decode_their_share():
+    # every rank opens the container with shard=(rank, world): together they decode every tensor once
+    specs = mixed_model()
+    blob = oracle.write_container(specs, chunk_size=4096, emit_crc=True, emit_hash=True)
+    want = {s.name: s.raw for s in specs}
+    for world in (2, 3):
+        got = {}
+        for rank in range(world):
+            h = ptwm_b200.ContainerHandle(blob, device=0, shard=(rank, world))
+            mine = h.shard_indices()
+            for name, t in h.decode_model_streamed(indices=mine, pieces=2):
+                assert name not in got
+                got[name] = bytes_of(t)
+        assert got == want

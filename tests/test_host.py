@@ -273,3 +273,43 @@ def test_malformed_per_plane_op_chains_are_rejected(L, monkeypatch):
         if rc == 0:
             assert not _infos(L, h)[0].supported, what
             L.ptwm_b200_close(h)
+
+
+def test_sharded_open_partitions_the_records(L):
+    """ptwm_b200_open_shard reads the records of one rank's contiguous run only; the runs of all ranks partition
+    the container and agree with the cut by record bytes."""
+    import oracle
+    from _data import mixed_model
+    specs = mixed_model()
+    blob = oracle.write_container(specs, chunk_size=4096, emit_crc=True)
+    buf = (C.c_char * len(blob)).from_buffer_copy(blob)
+    rc, h = _open(L, blob)
+    assert rc == 0
+    full = _infos(L, h)
+    names = [t.name for t in full]
+    sizes = {t.name: (t.orig_size, t.first_byte, t.end_byte) for t in full}
+    L.ptwm_b200_close(h)
+    for world in (1, 2, 3, 5, len(specs) + 3):
+        seen = []
+        for rank in range(world):
+            hs = C.c_void_p()
+            assert L.ptwm_b200_open_shard(C.addressof(buf), len(blob), rank, world, C.byref(hs)) == 0
+            infos = _infos(L, hs)
+            assert [t.name for t in infos] == names
+            mine = [i for i, t in enumerate(infos) if t.supported]
+            assert mine == list(range(mine[0], mine[-1] + 1)) if mine else True
+            for i in mine:
+                assert (infos[i].orig_size, infos[i].first_byte, infos[i].end_byte) == sizes[infos[i].name]
+            for i, t in enumerate(infos):
+                if i not in mine:
+                    assert b"another rank" in t.unsupported_reason and t.compressed > 0
+            if mine:
+                idx = (C.c_uint32 * len(mine))(*mine)
+                p = C.c_void_p()
+                assert L.ptwm_b200_plan_create(hs, idx, len(mine), C.byref(p)) == 0
+                L.ptwm_b200_plan_destroy(p)
+            seen += mine
+            L.ptwm_b200_close(hs)
+        assert seen == list(range(len(names))), world
+    hs = C.c_void_p()
+    assert L.ptwm_b200_open_shard(C.addressof(buf), len(blob), 2, 2, C.byref(hs)) < 0
