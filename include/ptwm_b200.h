@@ -92,6 +92,10 @@ const char* ptwm_b200_last_error(void);
  * header holds of its Extension Table (extension/table.rs:136-141) and the
  * derivation of built-in ids (extension/id.rs:21-31).  Host code. */
 void ptwm_b200_blake3(const uint8_t* data, size_t len, uint8_t out[32]);
+/* XXH64, seed 0, of a host buffer: the hash behind meta_xxh64 (ptwc.rs:144-149), shared-state
+ * entries (container.rs:2089) and the `ptwm_bytes_xxhash64` key of a ptwm-shell file
+ * (python/ptwm/integrations/_safetensors.py:141-146).  Host code. */
+uint64_t ptwm_b200_xxh64(const uint8_t* data, size_t len);
 
 /* Parse a \x89PTWC container or a \x89PTWS frame held in host memory
  * (ContainerReader::open, container.rs:1395-1626; compact.rs:321-405).  The
@@ -226,7 +230,10 @@ void ptwm_b200_encoded_free(ptwm_b200_encoded* e);
  *   PTWM_RC_BUFFER_TOO_SMALL and a message naming the limit.
  * - The first call on a device looks the array's address up
  *   (cudaGetSymbolAddress) and raises the kernels' shared-memory limit; make that
- *   first call before any stream capture begins.
+ *   first call before any stream capture begins.  Every call waits on `stream`
+ *   twice: once to read the payload's tag and length prefix back, once for the
+ *   kernel, so it returns with the plane decoded, like the regular entry point.
+ * - A payload that fails to decode answers PTWM_RC_CORRUPT.
  * - All calls share the one array.  Its status word is cleared at the start of
  *   each call; two calls that overlap on the same GPU (different streams or
  *   threads) race on it and must be serialised by the caller. */

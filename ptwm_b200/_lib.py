@@ -63,6 +63,7 @@ _SIGNATURES = {
     "ptwm_b200_encoded_free": (None, [C.c_void_p]),
     "ptwm_b200_last_error": (C.c_char_p, []),
     "ptwm_b200_blake3": (None, [C.c_char_p, C.c_size_t, C.c_char_p]),
+    "ptwm_b200_xxh64": (C.c_uint64, [C.c_char_p, C.c_size_t]),
     "ptwm_b200_open": (C.c_int64, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
     "ptwm_b200_open_shard": (C.c_int64, [C.c_void_p, C.c_size_t, C.c_uint32, C.c_uint32, C.POINTER(C.c_void_p)]),
     "ptwm_b200_close": (None, [C.c_void_p]),
@@ -119,3 +120,8 @@ def lib():
 
 def last_error() -> str:
     return lib().ptwm_b200_last_error().decode("utf-8", "replace")
+
+
+def xxh64(data: bytes) -> int:
+    """XXH64 (seed 0) of host bytes, computed by the library's host code."""
+    return int(lib().ptwm_b200_xxh64(data, len(data)))

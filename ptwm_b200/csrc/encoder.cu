@@ -440,7 +440,8 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
 // plane and keep the reference's rules for falling back to the raw-tagged form (codecs/huffman.rs:37-88,
 // codecs/rans.rs:38-95).  `needed` receives the payload size, also when `out_cap` is too small (-2).
 int64_t ptwm::encode_plane_cuda(int codec, uint64_t in_dev, size_t n, uint64_t out_dev, size_t out_cap, uint64_t* needed, cudaStream_t st) {
-    auto need = [&](uint64_t v) { if (needed) *needed = v; return v; };
+    // the required size goes to *needed only when the output buffer cannot hold it
+    auto need = [&](uint64_t v) { if (needed && v > out_cap) *needed = v; return v; };
     uint8_t* out = reinterpret_cast<uint8_t*>(uintptr_t(out_dev));
     const uint8_t* in = reinterpret_cast<const uint8_t*>(uintptr_t(in_dev));
     if (codec == C_IDENTITY) {

@@ -622,6 +622,9 @@ class FileReader {
                 if (!e.unsupported) { failed[i] = e.what(); has_failed[i] = 1; return; }
                 t = TensorDesc{}; t.unsupported = e.what();
             }
+            // anything else (an allocation a hostile length asked for) must not leave a worker thread: record it like a parse failure
+            catch (const std::exception& e) { failed[i] = std::string("record could not be read: ") + e.what(); has_failed[i] = 1; return; }
+            catch (...) { failed[i] = "record could not be read"; has_failed[i] = 1; return; }
             t.name = recs[i].name; t.record_len = recs[i].len;
             out_.tensors[i] = std::move(t);
         };

@@ -21,7 +21,6 @@ namespace {
 
 std::mutex g_noalloc_mu;
 std::map<int, uint8_t*> g_noalloc_ptr;  // device ordinal -> device address of g_noalloc_scratch on that device
-std::map<int, bool> g_noalloc_attrs;
 
 // Once per device, with that device current.
 int64_t noalloc_scratch_for(int device, uint8_t** out) {
@@ -61,7 +60,10 @@ extern "C" int64_t ptwm_b200_decode_plane_noalloc(uint8_t state_format_version, 
     cudaStream_t st = reinterpret_cast<cudaStream_t>(uintptr_t(stream));
 
     uint8_t head[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (in_len) CUDA_TRY(cudaMemcpy(head, reinterpret_cast<const void*>(uintptr_t(in_dev_ptr)), std::min<size_t>(in_len, 8), cudaMemcpyDeviceToHost));
+    if (in_len) {  // tag and length prefix, read in the order of the caller's stream: whatever produced the payload there has finished
+        CUDA_TRY(cudaMemcpyAsync(head, reinterpret_cast<const void*>(uintptr_t(in_dev_ptr)), std::min<size_t>(in_len, 8), cudaMemcpyDeviceToHost, st));
+        CUDA_TRY(cudaStreamSynchronize(st));
+    }
     ChunkDesc ch{};
     ch.body_off = 0; ch.body_len = in_len;
     uint64_t decoded;
@@ -117,6 +119,6 @@ extern "C" int64_t ptwm_b200_decode_plane_noalloc(uint8_t state_format_version, 
     uint32_t status = 0;
     CUDA_TRY(cudaMemcpyAsync(&status, d_status, 4, cudaMemcpyDeviceToHost, st));
     CUDA_TRY(cudaStreamSynchronize(st));
-    if (status) return fail(PTWM_RC_INVALID_INPUT, status_text(status));
+    if (status) return fail(PTWM_RC_CORRUPT, status_text(status));
     return int64_t(decoded);
 }

@@ -315,9 +315,12 @@ int64_t device_plan(ptwm_b200_plan& pl, int dev, DevicePlan** out) {
     if ((rc = upload(&d.items, all)) < 0 || (rc = upload(&d.merges, allm)) < 0 || (rc = upload(&d.tiles, allt)) < 0 || (rc = upload(&d.posts, pl.posts)) < 0 || (rc = upload(&d.post_tiles, pl.post_tiles)) < 0 ||
         (rc = upload(&d.verify, pl.verify)) < 0 ||
         (rc = upload(&d.hashes, pl.hashes)) < 0) { d.release(); return rc; }
-    CUDA_TRY(cudaMalloc(&d.status, (pl.item_tensor.size() + 1) * sizeof(uint32_t)));
-    CUDA_TRY(cudaMalloc(&d.acc, (pl.n_acc + 1) * sizeof(uint32_t)));
-    CUDA_TRY(cudaMalloc(&d.hash_out, (pl.hashes.size() + 1) * sizeof(uint64_t)));
+    cudaError_t e;
+    if ((e = cudaMalloc(&d.status, (pl.item_tensor.size() + 1) * sizeof(uint32_t))) != cudaSuccess || (e = cudaMalloc(&d.acc, (pl.n_acc + 1) * sizeof(uint32_t))) != cudaSuccess ||
+        (e = cudaMalloc(&d.hash_out, (pl.hashes.size() + 1) * sizeof(uint64_t))) != cudaSuccess) {
+        d.release();  // the lists already uploaded
+        return fail(PTWM_RC_CUDA, std::string("cudaMalloc of the plan's status arrays: ") + cudaGetErrorString(e));
+    }
     pl.dev[dev] = d;
     *out = &pl.dev[dev];
     return 0;
@@ -474,9 +477,15 @@ int64_t decode_plane_cuda(uint8_t sfv, const uint8_t* state, size_t state_len, c
     int64_t rc = device_state(int(device), &ds);
     if (rc < 0) return rc;
     cudaStream_t st = ds->stream;
-    // the tag and length prefix decide what runs: read them back (5 bytes)
+    // The tag and length prefix decide what runs: read them back, in stream order.  The producer of the
+    // payload was ordered against this stream (the caller hands the stream handle to the tensor's DLPack
+    // export, native.rs:105-112 of the reference); a copy on the legacy default stream would not wait for it,
+    // because this stream is non-blocking.
     uint8_t head[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (in_len) CUDA_TRY(cudaMemcpy(head, reinterpret_cast<const void*>(in_dev), std::min<size_t>(in_len, 8), cudaMemcpyDeviceToHost));
+    if (in_len) {
+        CUDA_TRY(cudaMemcpyAsync(head, reinterpret_cast<const void*>(in_dev), std::min<size_t>(in_len, 8), cudaMemcpyDeviceToHost, st));
+        CUDA_TRY(cudaStreamSynchronize(st));
+    }
     ChunkDesc ch{};
     ch.body_off = 0; ch.body_len = in_len;
     uint64_t decoded;
@@ -530,7 +539,7 @@ int64_t decode_plane_cuda(uint8_t sfv, const uint8_t* state, size_t state_len, c
     uint32_t status = 0;
     CUDA_TRY(cudaMemcpyAsync(&status, d_status, 4, cudaMemcpyDeviceToHost, st));
     CUDA_TRY(cudaStreamSynchronize(st));
-    if (status) return fail(PTWM_RC_INVALID_INPUT, status_text(status));
+    if (status) return fail(PTWM_RC_CORRUPT, status_text(status));  // the payload itself is damaged: same code as plan_finish
     return int64_t(decoded);
 }
 
@@ -548,6 +557,7 @@ extern "C" {
 
 const char* ptwm_b200_last_error(void) { return last_error_ref().c_str(); }
 void ptwm_b200_blake3(const uint8_t* data, size_t len, uint8_t out[32]) { blake3_hash(data, len, out); }
+uint64_t ptwm_b200_xxh64(const uint8_t* data, size_t len) { return xxh64_host(data, len); }
 
 uint64_t ptwm_hardware_backend_v1_cuda_stream_handle(uint32_t device_ordinal) { return stream_handle(device_ordinal); }
 uint64_t ptwm_plane_codec_v1_cuda_stream_handle(uint32_t device_ordinal) { return stream_handle(device_ordinal); }
@@ -562,7 +572,7 @@ int64_t ptwm_plane_codec_v1_decode_cuda(uint8_t sfv, const uint8_t* state_ptr, s
 }
 int64_t ptwm_plane_codec_v1_encode_cuda(uint8_t, const uint8_t*, size_t, const uint8_t* codec_id, size_t codec_id_len, uint64_t in_dev, size_t in_len, uint64_t out_dev,
                                         size_t out_cap, uint64_t* needed_out, uint32_t device_ordinal) {
-    if (needed_out) *needed_out = 0;
+    // *needed_out is written only together with PTWM_RC_BUFFER_TOO_SMALL and left untouched otherwise (native.rs:176-184)
     if (!codec_id || codec_id_len != 32) return fail(PTWM_RC_INVALID_INPUT, "codec_id must be a 32-byte canonical id");
     int codec = -1;
     for (const BuiltinId& b : kBuiltins) if (!std::memcmp(b.id, codec_id, 32)) codec = b.codec;

@@ -24,6 +24,7 @@ from typing import Any, Iterable, Mapping, Optional, Sequence
 
 import torch
 
+from . import _lib
 from .container import NO_SYNC, ContainerHandle, DecodePlan, PtwmError
 from .sharding import contiguous_shards
 
@@ -32,38 +33,65 @@ __all__ = ["PtwmIndex", "plan_shards", "shard_filename", "load_file", "read_shar
 INDEX_NAME = "model.ptwm.index.json"
 SINGLE_NAME = "model.ptwm"
 _PTWM_SHELL_SIGNAL = "ptwm-shell"
+_PTWM_SHELL_TENSOR = "__ptwm_payload__"
 
 
 # ---- shard bookkeeping ---------------------------------------------------------
+_INDEX_FORMAT = "ptwm"
+_INDEX_FORMAT_VERSION = 1
+
+
 @dataclass(frozen=True)
 class PtwmIndex:
-    """``model.ptwm.index.json``: which shard file holds which tensor."""
+    """``model.ptwm.index.json``: which shard file holds which tensor.
+
+    The file has the two top-level keys of a safetensors index, so tools that
+    collect shard names from ``weight_map`` work on it unchanged; ``metadata``
+    adds ``format = "ptwm"``, ``format_version`` and the compressed total beside
+    ``total_size`` (behaviour pinned by tests/ptwm/sharding/test_index.py of the
+    reference)."""
     total_size: int
     compressed_total_size: int
     weight_map: dict = field(default_factory=dict)
 
+    def to_json(self) -> dict:
+        return {
+            "metadata": {
+                "format": _INDEX_FORMAT,
+                "format_version": _INDEX_FORMAT_VERSION,
+                "total_size": int(self.total_size),
+                "compressed_total_size": int(self.compressed_total_size),
+            },
+            "weight_map": {str(k): str(v) for k, v in self.weight_map.items()},
+        }
+
+    @classmethod
+    def from_json(cls, doc: Mapping[str, Any], origin="<index>") -> "PtwmIndex":
+        header = doc.get("metadata") or {}
+        if header.get("format") != _INDEX_FORMAT:
+            raise ValueError(f"{origin}: metadata.format={header.get('format')!r}, expected 'ptwm'. This is not a .ptwm index file.")
+        return cls(int(header["total_size"]), int(header.get("compressed_total_size", 0)), dict(doc.get("weight_map") or {}))
+
     def write(self, path) -> None:
-        payload = {"metadata": {"total_size": self.total_size, "format": "ptwm", "format_version": 1,
-                                "compressed_total_size": self.compressed_total_size},
-                   "weight_map": dict(self.weight_map)}
-        Path(path).write_text(json.dumps(payload, indent=2))
+        with open(os.fspath(path), "w", encoding="utf-8") as f:
+            json.dump(self.to_json(), f, indent=2)
 
     @classmethod
     def read(cls, path) -> "PtwmIndex":
-        payload = json.loads(Path(path).read_text())
-        meta = payload.get("metadata", {})
-        fmt = meta.get("format")
-        if fmt != "ptwm":
-            raise ValueError(f"{path}: metadata.format={fmt!r}, expected 'ptwm'. This is not a .ptwm index file.")
-        return cls(total_size=int(meta["total_size"]), compressed_total_size=int(meta.get("compressed_total_size", 0)),
-                   weight_map=dict(payload.get("weight_map", {})))
+        with open(os.fspath(path), "r", encoding="utf-8") as f:
+            return cls.from_json(json.load(f), origin=path)
+
+    def shard_files(self) -> list[str]:
+        """Distinct shard file names, sorted."""
+        return sorted(set(self.weight_map.values()))
 
 
 def shard_filename(idx_one_based: int, total: int, *, suffix: str) -> str:
-    """``model-NNNNN-of-MMMMM.<suffix>``."""
-    if not 1 <= idx_one_based <= total:
+    """``model-NNNNN-of-MMMMM.<suffix>`` (five digits each, numbering from 1),
+    the Hugging Face shard naming."""
+    if idx_one_based < 1 or idx_one_based > total:
         raise ValueError(f"shard index {idx_one_based} out of [1, {total}]")
-    return f"model-{idx_one_based:05d}-of-{total:05d}.{suffix}"
+    return "model-%05d-of-%05d.%s" % (idx_one_based, total, suffix)
 
 
 def plan_shards(sized_tensors: Sequence[tuple[str, int]], *, max_shard_size: int) -> list[list[tuple[str, int]]]:
@@ -89,7 +117,8 @@ class _Staging:
     the GPU.  Pinning memory is slow (of the order of a second per few GB), so
     the buffers are small, reused round-robin within a load and kept between
     loads."""
-    _cache: dict = {}
+    _idle: list = []          # sets that no load is using, most recently returned last
+    _lock = threading.Lock()
 
     def __init__(self, slot_bytes: int, slots: int):
         self.slot_bytes = slot_bytes
@@ -98,12 +127,24 @@ class _Staging:
         self.busy: list = [None] * slots  # event of the last copy that read the slot
 
     @classmethod
-    def get(cls, slot_bytes: int, slots: int) -> "_Staging":
-        key = (slot_bytes, slots)
-        if key not in cls._cache:
-            cls._cache.clear()  # one configuration at a time: pinned memory is not returned to the system quickly
-            cls._cache[key] = cls(slot_bytes, slots)
-        return cls._cache[key]
+    def checkout(cls, slot_bytes: int, slots: int) -> "_Staging":
+        """A set that belongs to the caller alone until ``release``: two loads that
+        overlap (two threads, one loader per GPU) never share buffers or slot events."""
+        with cls._lock:
+            for i, st in enumerate(cls._idle):
+                if st.slot_bytes == slot_bytes and len(st.bufs) == slots:
+                    return cls._idle.pop(i)
+            cls._idle.clear()  # another configuration: let its pinned memory go (nothing is using it)
+        return cls(slot_bytes, slots)
+
+    def release(self) -> None:
+        for ev in self.busy:
+            if ev is not None:
+                ev.synchronize()  # no copy still reads these buffers
+        self.busy = [None] * len(self.bufs)
+        with _Staging._lock:
+            _Staging._idle.append(self)
+            del _Staging._idle[:-2]  # keep at most two idle sets pinned
 
 
 def _read_into(fd: int, view: memoryview, offset: int, pool: ThreadPoolExecutor, threads: int) -> None:
@@ -140,7 +181,7 @@ class _FileStream:
         self.blob = torch.empty(max(last - first, 1), dtype=torch.uint8, device=dev)
         self.copier = torch.cuda.Stream(dev)
         self.copier.wait_stream(torch.cuda.current_stream(dev))  # the buffer may be recycled memory that earlier work still reads
-        self.stage = _Staging.get(slot_bytes, slots)
+        self.stage = _Staging.checkout(slot_bytes, slots)
         self.progress = threading.Condition()
         self.marks: list = []     # (file offset reached, event recorded after the copy that reached it)
         self.failure: list = []
@@ -196,6 +237,9 @@ class _FileStream:
     def close(self) -> None:
         self.thread.join()
         self.blob.record_stream(self.copier)
+        if self.stage is not None:
+            self.stage.release()  # waits for the last copies out of the buffers, then hands the set back
+            self.stage = None
         if self.failure:
             raise self.failure[0]
 
@@ -283,7 +327,7 @@ def load_file(path, device: Optional[int] = None, *, names: Optional[Iterable[st
 def _shard_names(root: Path) -> list[str]:
     index_path = root / INDEX_NAME
     if index_path.exists():
-        return sorted(set(PtwmIndex.read(index_path).weight_map.values()))
+        return PtwmIndex.read(index_path).shard_files()
     if not (root / SINGLE_NAME).exists():
         raise FileNotFoundError(f"{root}: no {SINGLE_NAME} or {INDEX_NAME}")
     return [SINGLE_NAME]
@@ -341,76 +385,87 @@ def _device_ordinal(device) -> Optional[int]:
 
 
 class SafeOpen:
-    """``safetensors.safe_open`` look-alike that also understands ``.ptwm``
-    files (mode A) and ``ptwm-shell`` safetensors files, whose single
-    ``__ptwm_payload__`` tensor is a whole container (mode B).  Decoding is
-    lazy: the container is parsed on open, a tensor is decoded on the GPU when
-    ``get_tensor`` asks for it.  Any other safetensors file is passed through
-    to the safetensors library."""
+    """``safetensors.safe_open`` look-alike for three kinds of file:
+
+    * a ``.ptwm`` container (by suffix): keys are the container's tensors,
+      ``metadata()`` is ``None``;
+    * a "ptwm-shell" safetensors file, i.e. one whose metadata says
+      ``weights_format = "ptwm-shell"`` and whose only tensor
+      ``__ptwm_payload__`` is a whole container: keys are the embedded
+      container's tensors, ``metadata()`` is the shell's;
+    * any other safetensors file: everything is forwarded to safetensors.
+
+    A container is parsed when the file is opened and nothing is decoded until
+    ``get_tensor`` names a tensor; that one tensor is then decoded on the GPU.
+    Behaviour pinned by tests/ptwm/integrations/test_mode_a_safe_open.py and
+    test_mode_b_shell.py of the reference."""
 
     def __init__(self, filename, framework: str = "pt", device="cuda") -> None:
-        self._filename = os.fspath(filename)
-        self._framework = framework
-        self._device = device
-        self._mode_a = Path(self._filename).suffix == ".ptwm"
-        self._mode_b = False
-        self._ptwm: Optional[ContainerHandle] = None
-        self._underlying = None
-        if self._mode_a:
-            self._ptwm = ContainerHandle.from_file(self._filename, device=_device_ordinal(device))
+        path = os.fspath(filename)
+        self._container: Optional[ContainerHandle] = None   # set for .ptwm files and shells
+        self._st = None                                      # the safetensors handle, when the file is one
+        self._shell_metadata = None
+        if path.endswith(".ptwm"):
+            self._container = ContainerHandle.from_file(path, device=_device_ordinal(device))
             return
         from safetensors import safe_open
-        self._underlying = safe_open(self._filename, framework, "cpu" if self._is_ptwm_shell_probe() else str(device))
-        meta = self._underlying.metadata() or {}
-        if meta.get("weights_format") == _PTWM_SHELL_SIGNAL:
-            self._mode_b = True
-            payload = self._underlying.get_tensor("__ptwm_payload__")
-            self._ptwm = ContainerHandle(payload, device=_device_ordinal(device))
-
-    def _is_ptwm_shell_probe(self) -> bool:
-        # the shell's payload must land in host memory (the parser reads it there), so peek at the metadata first
-        from safetensors import safe_open
-        with safe_open(self._filename, self._framework, "cpu") as f:
-            return (f.metadata() or {}).get("weights_format") == _PTWM_SHELL_SIGNAL
+        # opened on the host first: a shell's payload has to be parsed from host memory
+        probe = safe_open(path, framework, "cpu")
+        info = probe.metadata() or {}
+        if info.get("weights_format") == _PTWM_SHELL_SIGNAL:
+            self._shell_metadata = info
+            self._container = ContainerHandle(probe.get_tensor(_PTWM_SHELL_TENSOR), device=_device_ordinal(device))
+            self._st = probe
+        else:
+            probe.__exit__(None, None, None)
+            self._st = safe_open(path, framework, str(device))
 
     def keys(self) -> list[str]:
-        return self._ptwm.names() if self._ptwm is not None else list(self._underlying.keys())
+        if self._container is not None:
+            return self._container.names()
+        return list(self._st.keys())
 
     def metadata(self):
-        return None if self._mode_a else self._underlying.metadata()
+        if self._container is not None:
+            return self._shell_metadata  # None for a bare .ptwm file
+        return self._st.metadata()
 
     def get_tensor(self, name: str) -> torch.Tensor:
-        if self._ptwm is None:
-            return self._underlying.get_tensor(name)
-        if name not in self._ptwm:
+        if self._container is None:
+            return self._st.get_tensor(name)
+        if name not in self._container:
             raise KeyError(name)
-        return self._ptwm.decode(name)
+        return self._container.decode(name)
 
     def get_slice(self, name: str) -> Any:
-        if self._ptwm is not None:
+        if self._container is not None:
             raise NotImplementedError("get_slice is not supported on .ptwm/ptwm-shell containers")
-        return self._underlying.get_slice(name)
+        return self._st.get_slice(name)
 
     def __enter__(self) -> "SafeOpen":
         return self
 
-    def __exit__(self, exc_type, exc_value, traceback) -> None:
-        if self._underlying is not None:
-            return self._underlying.__exit__(exc_type, exc_value, traceback)
-        return None
+    def __exit__(self, *exc) -> None:
+        if self._st is not None:
+            self._st.__exit__(*exc)
 
     def __getattr__(self, name: str) -> Any:
-        underlying = self.__dict__.get("_underlying")
-        if underlying is None:
+        # only reached for names this class does not define: hand them to safetensors when there is a file of its kind
+        st = self.__dict__.get("_st")
+        if st is None or self.__dict__.get("_container") is not None:
             raise AttributeError(f"'SafeOpen' has no attribute {name!r} (no underlying safetensors file in .ptwm mode)")
-        return getattr(underlying, name)
+        return getattr(st, name)
 
 
 def write_mode_b_shell(out_path, ptwm_bytes: bytes) -> None:
-    """Wrap a container as a valid single-tensor ``.safetensors`` file: one U8
-    tensor ``__ptwm_payload__`` and ``weights_format = "ptwm-shell"`` in the
-    metadata."""
+    """Wrap a container as a single-tensor ``.safetensors`` file that plain
+    safetensors can open: the U8 tensor ``__ptwm_payload__`` holds the container
+    bytes, the metadata carries ``weights_format = "ptwm-shell"``,
+    ``weights_format_version = "1"`` and ``ptwm_bytes_xxhash64``, the XXH64
+    (seed 0) of the container as 16 hex digits."""
     from safetensors.torch import save_file
-    payload = torch.frombuffer(bytearray(ptwm_bytes), dtype=torch.uint8).clone()
-    save_file({"__ptwm_payload__": payload}, os.fspath(out_path),
-              metadata={"weights_format": _PTWM_SHELL_SIGNAL, "weights_format_version": "1"})
+    data = bytes(ptwm_bytes)
+    digest = _lib.xxh64(data)
+    body = torch.frombuffer(bytearray(data), dtype=torch.uint8) if data else torch.zeros(0, dtype=torch.uint8)
+    save_file({_PTWM_SHELL_TENSOR: body}, os.fspath(out_path),
+              metadata={"weights_format": _PTWM_SHELL_SIGNAL, "weights_format_version": "1", "ptwm_bytes_xxhash64": f"{digest:016x}"})

@@ -94,6 +94,34 @@ def test_host_buffer_pair_decodes_rans():
     assert _lib.lib().ptwm_plane_codec_v1_decode(payload, len(payload), small, 10) == -2  # BufferTooSmall (native.rs:634-657)
 
 
+def test_payload_produced_on_a_side_stream_is_ordered_by_the_stream_handle():
+    """The reference hands the library's stream handle to the tensor's DLPack export, which makes that stream wait
+    for the producer (flavor/native.rs:105-112, crates/ptwm-py/src/hardware.rs:119-126).  Nothing else orders the two:
+    no device-wide synchronisation happens between producing the payload and the call."""
+    L = _lib.lib()
+    plane = ((np.random.default_rng(12).normal(0, 3, 200000).astype(np.int64) + 120) % 256).astype(np.uint8).tobytes()
+    for codec, symbol in ((oracle.RANS, "ptwm_hardware_backend_v1_dispatch_decode_cuda"), (oracle.HUFFMAN, "ptwm_plane_codec_v1_decode_cuda"),
+                          (oracle.TANS, "ptwm_b200_decode_plane_noalloc")):
+        _, _, payload = oracle.plane_encode(codec, plane)
+        assert payload[:1] == b"\x01"
+        staged = torch.frombuffer(bytearray(payload), dtype=torch.uint8).pin_memory()
+        src = torch.zeros(len(payload), dtype=torch.uint8, device="cuda")  # reads as a raw-tagged payload until the producer has run
+        out = torch.zeros(len(plane), dtype=torch.uint8, device="cuda")
+        torch.cuda.synchronize()
+        handle = L.ptwm_hardware_backend_v1_cuda_stream_handle(0)
+        side = torch.cuda.Stream()  # a non-blocking stream, like every torch side stream
+        with torch.cuda.stream(side):
+            torch.cuda._sleep(400_000_000)  # the producer is still busy when the call below starts
+            src.copy_(staged, non_blocking=True)
+        torch.cuda.ExternalStream(handle).wait_stream(side)  # what __dlpack__(stream=handle) does
+        args = [1, None, 0, bytes.fromhex(IDS[codec]), 32, src.data_ptr(), len(payload), out.data_ptr(), len(plane), 0]
+        if symbol.endswith("noalloc"):
+            args.append(handle)
+        rc = getattr(L, symbol)(*args)
+        assert rc == len(plane), (symbol, rc, _lib.last_error())
+        assert bytes_of(out) == plane, symbol
+
+
 def test_stream_handle_is_persistent():
     L = _lib.lib()
     a = L.ptwm_hardware_backend_v1_cuda_stream_handle(0)

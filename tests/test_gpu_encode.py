@@ -75,12 +75,15 @@ from test_gpu_decode import IDS, plane_cases  # noqa: E402  (canonical ids and t
 from ptwm_b200 import _lib  # noqa: E402
 
 
+NEEDED_UNTOUCHED = 0xDEADBEEF  # "On success *needed_out is left untouched" (flavor/native.rs:176-184 of the reference)
+
+
 def encode_cuda(codec, plane: bytes, cap=None):
     L = _lib.lib()
     src = torch.frombuffer(bytearray(plane or b"\0"), dtype=torch.uint8).cuda()
     cap = len(plane) + 16 if cap is None else cap
     out = torch.zeros(max(cap, 1), dtype=torch.uint8, device="cuda")
-    needed = _lib.C.c_uint64(0)
+    needed = _lib.C.c_uint64(NEEDED_UNTOUCHED)
     rc = L.ptwm_plane_codec_v1_encode_cuda(1, None, 0, bytes.fromhex(IDS[codec]), 32, src.data_ptr() if plane else 0, len(plane), out.data_ptr(), cap,
                                            _lib.C.byref(needed), 0)
     return rc, needed.value, bytes(out[:max(rc, 0)].cpu().numpy().tobytes())
@@ -94,7 +97,7 @@ def test_plane_encode_cuda_matches_oracle(codec):
             continue
         expect = oracle.plane_encode(codec, plane)[2]
         rc, needed, got = encode_cuda(codec, plane)
-        assert rc == len(expect) == needed, (name, rc, len(expect), needed)
+        assert rc == len(expect) and needed == NEEDED_UNTOUCHED, (name, rc, len(expect), needed)
         assert got == expect, name
         coded += codec != oracle.IDENTITY and got[:1] == b"\x01"
     if codec != oracle.IDENTITY:

@@ -56,6 +56,21 @@ def test_index_round_trip(tmp_path):
         PtwmIndex.read(bad)
 
 
+def test_shell_file_is_plain_safetensors_with_the_container_hash(tmp_path):
+    """tests/ptwm/integrations/test_mode_b_shell.py of the reference: the shell opens with stock safetensors, names its
+    format and carries the XXH64 of the wrapped bytes as 16 hex digits."""
+    xxhash = pytest.importorskip("xxhash")
+    from safetensors import safe_open
+    blob = oracle.write_container(mixed_model()[:3], chunk_size=4096)
+    ptwm_b200.write_mode_b_shell(tmp_path / "shell.safetensors", blob)
+    with safe_open(str(tmp_path / "shell.safetensors"), framework="pt") as f:
+        assert list(f.keys()) == ["__ptwm_payload__"]
+        meta = f.metadata()
+        assert meta["weights_format"] == "ptwm-shell" and meta["weights_format_version"] == "1"
+        assert meta["ptwm_bytes_xxhash64"] == xxhash.xxh64(blob).hexdigest() and len(meta["ptwm_bytes_xxhash64"]) == 16
+        assert f.get_tensor("__ptwm_payload__").numpy().tobytes() == blob
+
+
 def test_directory_without_a_model_raises(tmp_path):
     with pytest.raises(FileNotFoundError):
         read_sharded_ptwm(tmp_path)
@@ -87,6 +102,32 @@ def test_load_file_matches_oracle(tmp_path, stream):
     # a second load reuses the pinned buffers
     again = ptwm_b200.load_file(tmp_path / "m.ptwm", 0, **stream)
     assert all(_bytes_of(again[n]) == raw for n, raw in expected.items())
+
+
+@pytest.mark.gpu
+def test_two_loads_at_once_do_not_share_staging_buffers(tmp_path):
+    """Two threads load two different files through small staging sets at the same time; without plane CRCs or hashes a
+    slot shared between them would hand one file's bytes to the other unnoticed."""
+    import threading
+    specs = mixed_model()
+    want = [_write(tmp_path / "a.ptwm", specs, chunk_size=4096), _write(tmp_path / "b.ptwm", list(reversed(specs)), chunk_size=2048, menu=(oracle.IDENTITY, oracle.HUFFMAN))]
+    got, errors = [None, None], []
+
+    def work(k, path):
+        try:
+            for _ in range(3):
+                got[k] = ptwm_b200.load_file(path, device=0, verify=False, slot_bytes=8192, slots=2, threads=2, pieces=3)
+        except BaseException as e:  # noqa: BLE001
+            errors.append(e)
+
+    threads = [threading.Thread(target=work, args=(0, tmp_path / "a.ptwm")), threading.Thread(target=work, args=(1, tmp_path / "b.ptwm"))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for k in range(2):
+        assert {n: _bytes_of(t) for n, t in got[k].items()} == want[k]
 
 
 @pytest.mark.gpu
