@@ -60,8 +60,10 @@ int64_t ptwm_hardware_backend_v1_dispatch_decode_cuda(uint8_t state_format_versi
  * PlaneCodecCudaEncodeFn (native.rs:150,163-174,185-197).  encode_cuda turns one plane in
  * device memory into its payload (identity: the bytes; huffman / rans: TAG|len|blob with the
  * reference's raw fallback, byte for byte what codecs/huffman.rs:37-88 and codecs/rans.rs:38-95
- * produce); tans and order1_scale_ac answer PTWM_RC_UNSUPPORTED.  *needed_out receives the
- * payload size, also when out_cap is too small (PTWM_RC_BUFFER_TOO_SMALL). */
+ * produce; tans: codecs/tans.rs:39-90).  order1_scale_ac encodes with the state the caller passes
+ * (the flat ABI has no way to hand a fitted state back) and answers PTWM_RC_UNSUPPORTED without
+ * one.  *needed_out receives the payload size when out_cap is too small
+ * (PTWM_RC_BUFFER_TOO_SMALL) and is left untouched otherwise (native.rs:176-184). */
 uint64_t ptwm_plane_codec_v1_cuda_stream_handle(uint32_t device_ordinal);
 int64_t ptwm_plane_codec_v1_decode_cuda(uint8_t state_format_version, const uint8_t* state_ptr, size_t state_len, const uint8_t* codec_id_ptr,
                                         size_t codec_id_len, uint64_t in_dev_ptr, size_t in_len, uint64_t out_dev_ptr, size_t out_cap,
@@ -184,10 +186,13 @@ typedef struct ptwm_b200_encode_tensor {
 #define PTWM_B200_MENU_IDENTITY 1u
 #define PTWM_B200_MENU_HUFFMAN  2u
 #define PTWM_B200_MENU_RANS     4u
+#define PTWM_B200_MENU_TANS     8u
+#define PTWM_B200_MENU_O1SAC    16u   /* offered only to scale planes with a row layout (order1_scale_ac.rs:493-514) */
+#define PTWM_B200_CHUNK_NONE    0xFFFFFFFFu   /* chunk_size: write unchunked planes, the reference's default (compressor.rs:112-113) */
 
 typedef struct ptwm_b200_encode_options {
-    uint32_t chunk_size;     /* plane bytes per chunk (CompressorOptions.chunk_size, compressor.rs:112-113); 0 = 65536 */
-    uint32_t menu;           /* PTWM_B200_MENU_* bits the per-plane selection may use; 0 = all three */
+    uint32_t chunk_size;     /* plane bytes per chunk (CompressorOptions.chunk_size, compressor.rs:112-113); 0 = 65536; PTWM_B200_CHUNK_NONE = unchunked */
+    uint32_t menu;           /* PTWM_B200_MENU_* bits the per-plane selection may use; 0 = all five */
     int32_t forced_codec;    /* codec wire id to force on every plane (CompressorOptions.forced_codec), -1 = select */
     uint8_t emit_plane_crc;  /* CompressorOptions.emit_plane_crc */
     uint8_t emit_payload_hash; /* CompressorOptions.emit_payload_hash */
@@ -197,9 +202,14 @@ typedef struct ptwm_b200_encode_options {
 typedef struct ptwm_b200_encoded ptwm_b200_encoded;
 
 /* compress_model (compressor.rs:972-1200) for the production split / passthrough
- * chains with chunked planes, compact \x89PTWC layout: split + reorder, per-chunk
- * histograms, table build and stream encoding run on the device; the host lays
- * out records, index and footer.  The container is left in device memory. */
+ * chains, compact \x89PTWC layout: split + reorder, histograms, table build and
+ * stream encoding (identity, huffman, rans, tans, order1_scale_ac) run on the
+ * device; the host lays out records, index and footer.  A plane's codec is the
+ * one with the smallest state + payload over the menu, first in dispatch order
+ * on ties (select.rs:27-64, dispatch.rs:13-49), judged on the whole plane from
+ * its histograms; the plane is then written in chunks of chunk_size bytes, or
+ * whole (one record payload with an inline state) for PTWM_B200_CHUNK_NONE.
+ * The container is left in device memory. */
 int64_t ptwm_b200_encode_model(const ptwm_b200_encode_tensor* tensors, size_t n, const ptwm_b200_encode_options* options, uint32_t device_ordinal,
                                uint64_t stream, ptwm_b200_encoded** out);
 uint64_t ptwm_b200_encoded_size(const ptwm_b200_encoded* e);

@@ -385,9 +385,10 @@ def select_codec(plane: bytes, menu: Sequence[int], row_len: int, role: int):
 
 
 def write_container(specs: Sequence[TensorSpec], *, chunk_size: Optional[int] = None, menu: Sequence[int] = (IDENTITY, HUFFMAN, RANS, TANS, O1SAC),
-                    forced_codec: Optional[int] = None, emit_hash: bool = False, emit_crc: bool = False) -> bytes:
+                    forced_codec: Optional[int] = None, emit_hash: bool = False, emit_crc: bool = False, choices: Optional[list] = None) -> bytes:
     """compress_model (compressor.rs:972-1200) with one candidate chain per
-    tensor and no shared-state pass, compact layout."""
+    tensor and no shared-state pass, compact layout.  `choices`, when given, receives
+    the codec picked for every plane in container order."""
     plans = []
     registry: list = []  # [(nodes, roles)] after binding
     for s in specs:
@@ -412,6 +413,8 @@ def write_container(specs: Sequence[TensorSpec], *, chunk_size: Optional[int] = 
             else:
                 c, st, sv, pl = select_codec(plane, menu, row_len, role)
                 chosen.append((c, st, sv, pl, row_len))
+        if choices is not None:
+            choices.extend(c[0] for c in chosen)
         plans.append((s, kind, registry.index(key), roles, planes, chosen))
 
     # Extension Table: chain ops in registry order, then the used codecs in built-in order (container.rs:167-223).

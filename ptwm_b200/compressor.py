@@ -17,8 +17,9 @@ import torch
 from . import _lib
 from .container import PtwmError, _check, stream_handle
 
-IDENTITY, HUFFMAN, RANS = 0, 1, 3
-_MENU_BIT = {IDENTITY: 1, HUFFMAN: 2, RANS: 4}
+IDENTITY, HUFFMAN, RANS, TANS, ORDER1_SCALE_AC = 0, 1, 3, 7, 0x11
+_MENU_BIT = {IDENTITY: 1, HUFFMAN: 2, RANS: 4, TANS: 8, ORDER1_SCALE_AC: 16}
+_CHUNK_NONE = 0xFFFFFFFF
 _USAGE = {"standard": 0, "scale": 1, "global_scale": 2, "fp4": 3}
 
 _DTYPE_CODES = {torch.float32: 1, torch.float16: 4, torch.bfloat16: 6, torch.uint8: 13, torch.int8: 17, torch.float8_e4m3fn: 29, torch.float8_e5m2: 30}
@@ -28,12 +29,15 @@ if hasattr(torch, "float4_e2m1fn_x2"):
 
 @dataclass(frozen=True, kw_only=True)
 class CompressionConfig:
-    """``streaming_chunk`` = plane bytes per chunk (CompressorOptions.chunk_size);
-    ``codec_menu`` = codec wire ids selection may use; ``forced_codec`` = one
-    codec for every plane (the reference's method_hint fast path);
+    """``streaming_chunk`` = plane bytes per chunk (CompressorOptions.chunk_size),
+    ``None`` = unchunked planes, the reference's default (a plane is then four
+    serial streams, or one: slow to write and to read on a GPU);
+    ``codec_menu`` = codec wire ids selection may use (Order1ScaleAC is only ever
+    offered to scale planes with a row layout); ``forced_codec`` = one codec for
+    every plane (the reference's method_hint fast path);
     ``emit_plane_crc`` / ``emit_payload_hash`` as in python/ptwm/_config.py:177-184."""
-    streaming_chunk: int = 65536
-    codec_menu: Sequence[int] = (IDENTITY, HUFFMAN, RANS)
+    streaming_chunk: Optional[int] = 65536
+    codec_menu: Sequence[int] = (IDENTITY, HUFFMAN, RANS, TANS, ORDER1_SCALE_AC)
     forced_codec: Optional[int] = None
     emit_plane_crc: bool = False
     emit_payload_hash: bool = False
@@ -113,9 +117,9 @@ def compress_model(tensors: Mapping[str, torch.Tensor], config: Optional[Compres
     menu = 0
     for c in cfg.codec_menu:
         if c not in _MENU_BIT:
-            raise ValueError(f"codec {c} is not offered by the device encoder (identity, huffman, rans)")
+            raise ValueError(f"codec {c} is not offered by the device encoder (identity, huffman, rans, tans, order1_scale_ac)")
         menu |= _MENU_BIT[c]
-    opt = _lib.EncodeOptions(int(cfg.streaming_chunk), menu, -1 if cfg.forced_codec is None else int(cfg.forced_codec), int(cfg.emit_plane_crc),
+    opt = _lib.EncodeOptions(_CHUNK_NONE if cfg.streaming_chunk is None else int(cfg.streaming_chunk), menu, -1 if cfg.forced_codec is None else int(cfg.forced_codec), int(cfg.emit_plane_crc),
                              int(cfg.emit_payload_hash))
     torch.cuda.current_stream(dev).synchronize()
     h = C.c_void_p()

@@ -6,7 +6,9 @@
 //   split      transforms/fusion.rs:35-122,207-262,329-371,431-473
 //   rANS       entropy/rans/compress.rs:35-259
 //   Huffman    entropy/huffman/{compress.rs:9-103, bitstream.rs:3-51, weights.rs:8-32}
-//   framing    compressor.rs:316-381, codecs/{huffman,rans}.rs encode
+//   tANS       entropy/tans/mod.rs:199-339
+//   O1SAC      codecs/order1_scale_ac.rs:620-663,963-1025, quantize.rs:13-45, range_coder.rs:16-113
+//   framing    compressor.rs:316-381, codecs/{huffman,rans,tans}.rs encode
 #pragma once
 #include "encode_tables.cuh"
 #include "kernels.cuh"
@@ -24,28 +26,39 @@ constexpr uint32_t SPLIT_TILE = 8192;
 
 struct EncChunk {
     uint64_t plane_off;  // this chunk's bytes in the planes buffer
-    uint64_t slot_off;   // four stream slots of slot_cap bytes each in the slot buffer
+    uint64_t slot_off;   // four stream slots of slot_cap bytes each in the slot buffer (tANS / O1SAC: one stream over all four)
+    uint64_t table_off;  // this chunk's area in the table buffer (size by codec, see below)
     uint32_t n;
     uint32_t slot_cap;
     uint32_t plane;      // global plane index
-    uint32_t pad;
+    uint32_t row_len;    // O1SAC: symbols per row (context resets at row starts); 0 = one row spanning the chunk
 };
 struct EncResult {       // per chunk, read back by the host
-    uint32_t stream_len[4];
-    uint32_t hdr_n;      // rANS: max_sym; Huffman: number of weights
+    uint32_t stream_len[4];  // tANS: [0] bytes of bits, [1..2] total bits (lo, hi); O1SAC: [0] payload bytes, [1] state bytes
+    uint32_t hdr_n;      // rANS: max_sym; Huffman: number of weights; tANS: present symbols; O1SAC: context rows
     uint32_t coded;      // 0: no table could be built, store raw
 };
 struct GatherItem {
     uint64_t dst;        // absolute offset of the chunk frame in the container
     uint32_t chunk;
-    uint32_t mode;       // 0 identity (bare bytes), 1 raw-tagged, 2 rANS, 3 Huffman; + GATHER_BARE: the payload alone, no chunk frame header
+    uint32_t mode;       // 0 identity (bare bytes), 1 raw-tagged, 2 rANS, 3 Huffman, 4 tANS, 5 Order1ScaleAC (state inside the frame);
+                         // + GATHER_BARE: the payload alone, no chunk frame header (and no state)
 };
 constexpr uint32_t GATHER_BARE = 0x100;
+constexpr uint32_t GATHER_NOFRAME = 0x200;  // an unchunked plane: inline state (if the codec has one) and payload, no frame header
 
-// layout of the 1 KiB table area per chunk
-//   rANS:    freqs u16[256] | cum u16[256]
-//   Huffman: lengths u8[256] | unused[256] | rev codes u16[256]
+// layout of the table area of a chunk
+//   rANS:    freqs u16[256] | cum u16[256]                                                  (1 KiB)
+//   Huffman: lengths u8[256] | unused[256] | rev codes u16[256]                            (1 KiB)
+//   tANS:    norm u16[256] | delta_nb u32[256] | delta_find_state i32[256] | next-state u16[2048] | spread symbols u8[2048]
+//   O1SAC:   joint counts u32[256][256] | row-start counts u32[256] | present u8[256] | rank u16[256] |
+//            pmf u16[257][256] (row 0 marginal, row 1 + c for context c) | cum u16[257][256]
 constexpr uint32_t ENC_TABLE_BYTES = 1024;
+constexpr uint32_t ENC_TANS_TABLE_BYTES = 512 + 1024 + 1024 + 4096 + 2048;
+constexpr uint32_t O1E_JOINT = 0, O1E_MARG = 262144, O1E_PRESENT = O1E_MARG + 1024, O1E_RANK = O1E_PRESENT + 256, O1E_PMF = O1E_RANK + 512,
+                   O1E_CUM = O1E_PMF + 257 * 512, ENC_O1SAC_TABLE_BYTES = O1E_CUM + 257 * 512;
+constexpr uint32_t O1SAC_TOTAL = 4096;
+__host__ __device__ inline uint32_t enc_table_bytes(int codec) { return codec == C_TANS ? ENC_TANS_TABLE_BYTES : codec == C_O1SAC ? ENC_O1SAC_TABLE_BYTES : ENC_TABLE_BYTES; }
 
 __global__ void __launch_bounds__(256) split_kernel(const SplitItem* __restrict__ items, uint32_t n_items, uint8_t* __restrict__ planes) {
     uint32_t tile = blockIdx.x;
@@ -108,9 +121,10 @@ __global__ void __launch_bounds__(64) table_kernel(const EncChunk* __restrict__ 
     if (ci >= n_chunks) return;
     const EncChunk c = chunks[ci];
     const uint32_t* raw = hist + uint64_t(ci) * 256;
-    uint8_t* tab = tables + uint64_t(ci) * ENC_TABLE_BYTES;
+    uint8_t* tab = tables + c.table_off;
     EncResult r{{0, 0, 0, 0}, 0, 0};
     int codec = plane_codec[c.plane];
+    if (codec == C_O1SAC) return;  // fitted by its own kernels
     if (codec == C_RANS && c.n) {
         uint16_t* freqs = reinterpret_cast<uint16_t*>(tab);
         uint16_t* cum = freqs + 256;
@@ -128,6 +142,34 @@ __global__ void __launch_bounds__(64) table_kernel(const EncChunk* __restrict__ 
             huffman_codes(lengths, reinterpret_cast<uint16_t*>(tab + 512));
             r.hdr_n = uint32_t(nw); r.coded = 1;
         }
+    } else if (codec == C_TANS && c.n) {  // entropy/tans/mod.rs:199-266
+        uint16_t* norm = reinterpret_cast<uint16_t*>(tab);
+        uint32_t* dnb = reinterpret_cast<uint32_t*>(tab + 512);
+        int32_t* dfs = reinterpret_cast<int32_t*>(tab + 1536);
+        uint16_t* next_state = reinterpret_cast<uint16_t*>(tab + 2560);
+        uint8_t* spread = tab + 6656;
+        const int nsym = tans_normalize(raw, c.n, norm);
+        if (nsym >= 2) {
+            uint32_t pos = 0;
+            for (int s = 0; s < 256; ++s)
+                for (uint32_t k = 0; k < norm[s]; ++k) { spread[pos] = uint8_t(s); pos = (pos + 1283u) & 2047u; }
+            uint16_t fill[256];
+            uint32_t running = 0;
+            int32_t tot = 0;
+            for (int s = 0; s < 256; ++s) {
+                fill[s] = uint16_t(running); running += norm[s];
+                const uint32_t cnt = norm[s];
+                dnb[s] = 0; dfs[s] = 0;
+                if (cnt == 1) { dnb[s] = (11u << 16) - 2048u; dfs[s] = tot - 1; tot += 1; }
+                else if (cnt > 1) {
+                    const uint32_t max_bits = 11u - (31u - uint32_t(__clz(cnt - 1)));
+                    dnb[s] = (max_bits << 16) - (cnt << max_bits);
+                    dfs[s] = tot - int32_t(cnt); tot += int32_t(cnt);
+                }
+            }
+            for (uint32_t u = 0; u < 2048; ++u) { const int s = spread[u]; next_state[fill[s]++] = uint16_t(2048u + u); }
+            r.hdr_n = uint32_t(nsym); r.coded = 1;
+        }
     }
     results[ci] = r;
 }
@@ -142,8 +184,38 @@ __global__ void __launch_bounds__(128) encode_kernel(const EncChunk* __restrict_
     uint32_t ci = gi >> 2, s = gi & 3;
     if (ci >= n_chunks) return;
     const EncChunk c = chunks[ci];
-    if (!results[ci].coded) return;
     int codec = plane_codec[c.plane];
+    if (codec == C_O1SAC || !results[ci].coded) return;
+    if (codec == C_TANS) {  // one stream per chunk, bits appended upward from the start of the slot area (mod.rs:268-318)
+        if (s) return;
+        const uint8_t* tab = tables + c.table_off;
+        const uint32_t* dnb = reinterpret_cast<const uint32_t*>(tab + 512);
+        const int32_t* dfs = reinterpret_cast<const int32_t*>(tab + 1536);
+        const uint16_t* next_state = reinterpret_cast<const uint16_t*>(tab + 2560);
+        const uint8_t* src = planes + c.plane_off;
+        uint32_t* w32 = reinterpret_cast<uint32_t*>(slots + c.slot_off);  // slot areas start on 16-byte boundaries
+        uint64_t acc = 0, total_bits = 0;
+        uint32_t nb_acc = 0, words = 0, value = 2048;
+        auto add_bits = [&](uint32_t v, uint32_t nb) {
+            acc |= uint64_t(v & ((1u << nb) - 1u)) << nb_acc;
+            nb_acc += nb; total_bits += nb;
+            if (nb_acc >= 32) { w32[words++] = uint32_t(acc); acc >>= 32; nb_acc -= 32; }
+        };
+        for (uint32_t k = c.n; k-- > 0;) {
+            const uint32_t b = src[k];
+            const uint32_t nb = (value + dnb[b]) >> 16;
+            add_bits(value, nb);
+            value = next_state[int32_t(value >> nb) + dfs[b]];
+        }
+        add_bits(value, 11);
+        uint8_t* tail = reinterpret_cast<uint8_t*>(w32 + words);
+        uint32_t bytes = words * 4;
+        while (nb_acc > 0) { *tail++ = uint8_t(acc); acc >>= 8; nb_acc = nb_acc > 8 ? nb_acc - 8 : 0; ++bytes; }
+        results[ci].stream_len[0] = bytes;
+        results[ci].stream_len[1] = uint32_t(total_bits);
+        results[ci].stream_len[2] = uint32_t(total_bits >> 32);
+        return;
+    }
     uint32_t start, len;
     split_four_dev(c.n, s, start, len);
     const uint8_t* src = planes + c.plane_off + start;
@@ -160,7 +232,7 @@ __global__ void __launch_bounds__(128) encode_kernel(const EncChunk* __restrict_
         if (++have == 8) { w -= 8; *reinterpret_cast<uint64_t*>(w) = acc; have = 0; acc = 0; }
     };
     auto flush = [&]() { while (have) { --have; *--w = uint8_t(acc >> (8 * have)); } };
-    const uint8_t* tab = tables + uint64_t(ci) * ENC_TABLE_BYTES;
+    const uint8_t* tab = tables + c.table_off;
     if (codec == C_RANS) {
         const uint16_t* freqs = reinterpret_cast<const uint16_t*>(tab);
         const uint16_t* cum = freqs + 256;
@@ -200,8 +272,9 @@ __global__ void __launch_bounds__(128) gather_kernel(const GatherItem* __restric
     uint8_t* d = out + g.dst;
     const uint32_t t = threadIdx.x;
     const uint32_t mode = g.mode & 0xFFu;
-    if (!(g.mode & GATHER_BARE)) {
-        if (t < 5) d[t] = 0;
+    const bool framed = !(g.mode & (GATHER_BARE | GATHER_NOFRAME));
+    if (framed) {
+        if (t < 5 && mode != 5) d[t] = 0;
         d += 5;
     }
     if (mode <= 1) {
@@ -210,9 +283,46 @@ __global__ void __launch_bounds__(128) gather_kernel(const GatherItem* __restric
         for (uint32_t i = t; i < c.n; i += blockDim.x) d[i] = p[i];
         return;
     }
+    const uint8_t* tab = tables + c.table_off;
+    if (mode == 5) {  // Order1ScaleAC: inline state [bitmap 32][marginal 512][rows 512 each, contexts in increasing order], then the coder's bytes
+        const uint8_t* present = tab + O1E_PRESENT;
+        const uint16_t* rank = reinterpret_cast<const uint16_t*>(tab + O1E_RANK);
+        const uint16_t* pmf = reinterpret_cast<const uint16_t*>(tab + O1E_PMF);
+        if (!(g.mode & GATHER_BARE)) {
+            const uint32_t state_len = r.stream_len[1];
+            if (framed && t == 0) {  // frame header: state_version 1, state length
+                uint8_t* fh = d - 5;
+                fh[0] = 1; fh[1] = uint8_t(state_len); fh[2] = uint8_t(state_len >> 8); fh[3] = uint8_t(state_len >> 16); fh[4] = uint8_t(state_len >> 24);
+            }
+            if (t < 32) { uint32_t bits = 0; for (int k = 0; k < 8; ++k) bits |= uint32_t(present[8 * t + k] != 0) << k; d[t] = uint8_t(bits); }
+            for (uint32_t i = t; i < 256; i += blockDim.x) { d[32 + 2 * i] = uint8_t(pmf[i]); d[33 + 2 * i] = uint8_t(pmf[i] >> 8); }
+            for (uint32_t ctx = 0; ctx < 256; ++ctx) {
+                if (!present[ctx]) continue;
+                uint8_t* row = d + 32 + 512 + 512 * uint32_t(rank[ctx]);
+                const uint16_t* pr = pmf + 256 * (1 + ctx);
+                for (uint32_t i = t; i < 256; i += blockDim.x) { row[2 * i] = uint8_t(pr[i]); row[2 * i + 1] = uint8_t(pr[i] >> 8); }
+            }
+            d += state_len;
+        }
+        const uint8_t* sp = slots + c.slot_off;
+        for (uint32_t i = t; i < r.stream_len[0]; i += blockDim.x) d[i] = sp[i];
+        return;
+    }
     if (t == 0) { d[0] = 1; d[1] = uint8_t(c.n); d[2] = uint8_t(c.n >> 8); d[3] = uint8_t(c.n >> 16); d[4] = uint8_t(c.n >> 24); }
     d += 5;
-    const uint8_t* tab = tables + uint64_t(g.chunk) * ENC_TABLE_BYTES;
+    if (mode == 4) {  // tANS blob: [11][nsym u16][(symbol, freq u16) per present symbol][total bits u64][bits]
+        const uint16_t* norm = reinterpret_cast<const uint16_t*>(tab);
+        if (t == 0) {
+            d[0] = 11; d[1] = uint8_t(r.hdr_n); d[2] = uint8_t(r.hdr_n >> 8);
+            uint8_t* q = d + 3;
+            for (int sy = 0; sy < 256; ++sy) if (norm[sy]) { q[0] = uint8_t(sy); q[1] = uint8_t(norm[sy]); q[2] = uint8_t(norm[sy] >> 8); q += 3; }
+            for (int k = 0; k < 4; ++k) { q[k] = uint8_t(r.stream_len[1] >> (8 * k)); q[4 + k] = uint8_t(r.stream_len[2] >> (8 * k)); }
+        }
+        d += 3 + 3 * r.hdr_n + 8;
+        const uint8_t* sp = slots + c.slot_off;
+        for (uint32_t i = t; i < r.stream_len[0]; i += blockDim.x) d[i] = sp[i];
+        return;
+    }
     uint32_t hdr;
     if (mode == 2) {
         const uint16_t* freqs = reinterpret_cast<const uint16_t*>(tab);
@@ -237,6 +347,112 @@ __global__ void __launch_bounds__(128) gather_kernel(const GatherItem* __restric
         for (uint32_t i = t; i < r.stream_len[s]; i += blockDim.x) d[i] = sp[i];
         d += r.stream_len[s];
     }
+}
+
+// ---- Order1ScaleAC encode (codecs/order1_scale_ac.rs:620-663, 963-1025) -------------------------------------
+// Lag-1 counts of one chunk: the first symbol of a row counts toward the marginal, every other symbol toward the row
+// of the symbol before it.  One CTA per listed chunk; the count areas were cleared beforehand.
+__global__ void __launch_bounds__(256) o1sac_count_kernel(const EncChunk* __restrict__ chunks, const uint32_t* __restrict__ list, const uint8_t* __restrict__ planes,
+                                                          uint8_t* __restrict__ tables) {
+    const EncChunk c = chunks[list[blockIdx.x]];
+    uint32_t* joint = reinterpret_cast<uint32_t*>(tables + c.table_off + O1E_JOINT);
+    uint32_t* marg = reinterpret_cast<uint32_t*>(tables + c.table_off + O1E_MARG);
+    const uint8_t* p = planes + c.plane_off;
+    const uint32_t row_len = c.row_len ? c.row_len : (c.n ? c.n : 1);
+    for (uint32_t i = threadIdx.x; i < c.n; i += blockDim.x) {
+        if (i % row_len == 0) atomicAdd(&marg[p[i]], 1u);
+        else atomicAdd(&joint[uint32_t(p[i - 1]) * 256 + p[i]], 1u);
+    }
+}
+// Probability rows from the counts (a context gets a row when it was seen at all), their cumulative sums for the coder,
+// and the rank of every present context (its place among the rows of the serialized state).  One CTA of 288 threads per chunk:
+// thread c < 256 owns context c, thread 256 the marginal.
+__global__ void __launch_bounds__(288) o1sac_fit_kernel(const EncChunk* __restrict__ chunks, const uint32_t* __restrict__ list, uint8_t* __restrict__ tables,
+                                                        EncResult* __restrict__ results) {
+    const uint32_t ci = list[blockIdx.x];
+    uint8_t* tab = tables + chunks[ci].table_off;
+    const uint32_t* joint = reinterpret_cast<const uint32_t*>(tab + O1E_JOINT);
+    const uint32_t* marg = reinterpret_cast<const uint32_t*>(tab + O1E_MARG);
+    uint8_t* present = tab + O1E_PRESENT;
+    uint16_t* rank = reinterpret_cast<uint16_t*>(tab + O1E_RANK);
+    uint16_t* pmf = reinterpret_cast<uint16_t*>(tab + O1E_PMF);
+    uint16_t* cum = reinterpret_cast<uint16_t*>(tab + O1E_CUM);
+    const uint32_t t = threadIdx.x;
+    __shared__ uint32_t seen[256];
+    if (t <= 256) {
+        const uint32_t* raw = t < 256 ? joint + 256 * t : marg;
+        const uint32_t row = t < 256 ? 1 + t : 0;
+        bool use = true;
+        if (t < 256) {
+            uint64_t total = 0;
+            for (int i = 0; i < 256; ++i) total += raw[i];
+            use = total != 0;
+            present[t] = use;
+            seen[t] = use;
+        }
+        if (use) {
+            uint16_t* out = pmf + 256 * row;
+            quantize_pmf256(raw, O1SAC_TOTAL, out);
+            uint32_t acc = 0;
+            for (int i = 0; i < 256; ++i) { cum[256 * row + i] = uint16_t(acc); acc += out[i]; }
+        }
+    }
+    __syncthreads();
+    if (t == 0) {
+        uint32_t k = 0;
+        for (int ctx = 0; ctx < 256; ++ctx) { rank[ctx] = uint16_t(k); k += seen[ctx]; }
+        results[ci].hdr_n = k;
+        results[ci].stream_len[1] = 32 + 512 + 512 * k;
+        results[ci].coded = 1;
+    }
+}
+// The range coder over one chunk (range_coder.rs:16-113): 64-bit low, 32-bit range, carry held back in a cache byte and
+// a run of 0xFF bytes; total 4096 makes range / total a shift.  One thread per listed chunk, bytes upward from the
+// start of the chunk's slot area.
+__global__ void __launch_bounds__(64) o1sac_encode_kernel(const EncChunk* __restrict__ chunks, const uint32_t* __restrict__ list, uint32_t n_list,
+                                                          const uint8_t* __restrict__ planes, const uint8_t* __restrict__ tables, uint8_t* __restrict__ slots,
+                                                          EncResult* __restrict__ results) {
+    const uint32_t li = blockIdx.x * blockDim.x + threadIdx.x;
+    if (li >= n_list) return;
+    const uint32_t ci = list[li];
+    const EncChunk c = chunks[ci];
+    const uint8_t* tab = tables + c.table_off;
+    const uint8_t* present = tab + O1E_PRESENT;
+    const uint16_t* pmf = reinterpret_cast<const uint16_t*>(tab + O1E_PMF);
+    const uint16_t* cum = reinterpret_cast<const uint16_t*>(tab + O1E_CUM);
+    const uint8_t* p = planes + c.plane_off;
+    uint8_t* out = slots + c.slot_off;
+    uint32_t written = 0;
+    uint64_t low = 0, range = 0xFFFFFFFFull;
+    uint32_t cache = 0, cache_size = 0;
+    auto shift_low = [&]() {
+        const uint32_t carry = uint32_t(low >> 32) & 0xFFu, top = uint32_t(low >> 24) & 0xFFu;
+        if (top == 0xFF && carry == 0) ++cache_size;
+        else {
+            out[written++] = uint8_t(cache + carry);
+            const uint8_t fill = carry ? 0x00 : 0xFF;
+            for (uint32_t i = 0; i < cache_size; ++i) out[written++] = fill;
+            cache_size = 0;
+            cache = top;
+        }
+        low = (low & 0x00FFFFFFull) << 8;
+    };
+    const uint32_t row_len = c.row_len ? c.row_len : (c.n ? c.n : 1);
+    uint32_t in_row = 0, row = 0;
+    for (uint32_t i = 0; i < c.n; ++i) {
+        const uint32_t sym = p[i];
+        const uint32_t cu = cum[256 * row + sym], pr = pmf[256 * row + sym];
+        const uint64_t rpt = range >> 12;
+        low += uint64_t(cu) * rpt;
+        range = uint64_t(pr) * rpt;
+        while (range < (1ull << 24)) { shift_low(); range <<= 8; }
+        if (++in_row == row_len) { in_row = 0; row = 0; }
+        else row = present[sym] ? 1 + sym : 0;
+    }
+    for (int i = 0; i < 5; ++i) shift_low();
+    out[written++] = uint8_t(cache);
+    for (uint32_t i = 0; i < cache_size; ++i) out[written++] = 0xFF;
+    results[ci].stream_len[0] = written;
 }
 
 // Scatter host-built byte pieces (record headers, index, footer) into the container.

@@ -4,7 +4,10 @@
 //   rANS     entropy/rans/compress.rs:72-122 (normalize_freqs)
 //   Huffman  entropy/huffman/tree.rs:19-85 (from_frequencies), :212-242
 //            (enforce_max_code_length), :119-141 (canonical codes)
+//   tANS     entropy/tans/mod.rs:153-194 (normalize)
+//   O1SAC    quantize.rs:13-45 (quantize_pmf)
 #pragma once
+#include <math.h>
 #include <stdint.h>
 
 namespace ptwm {
@@ -35,6 +38,58 @@ __host__ __device__ inline int rans_normalize(const uint32_t* raw, uint64_t tota
         freqs[max_freq_sym] = uint16_t(freqs[max_freq_sym] + (2048 - assigned));
     }
     return max_sym;
+}
+
+// Normalised tANS frequencies (sum 2048): floor(c * 2048 / total) with a floor
+// of one; an excess is taken one at a time from the first largest entry above
+// one, a deficit goes to the first most frequent symbol.  Returns the number
+// of present symbols.
+__host__ __device__ inline int tans_normalize(const uint32_t* counts, uint64_t total, uint16_t* norm) {
+    uint32_t sum = 0, max_count = 0;
+    int max_sym = 0, nsym = 0;
+    for (int s = 0; s < 256; ++s) {
+        norm[s] = 0;
+        const uint32_t c = counts[s];
+        if (c == 0) continue;
+        uint32_t v = uint32_t(uint64_t(c) * 2048u / total);
+        if (v == 0) v = 1;
+        norm[s] = uint16_t(v); sum += v; ++nsym;
+        if (c > max_count) { max_count = c; max_sym = s; }
+    }
+    while (sum > 2048) {
+        int bi = -1; uint32_t bv = 1;
+        for (int s = 0; s < 256; ++s) if (norm[s] > bv) { bv = norm[s]; bi = s; }
+        if (bi < 0) break;
+        norm[bi]--; sum--;
+    }
+    if (sum < 2048) norm[max_sym] = uint16_t(norm[max_sym] + (2048 - sum));
+    return nsym;
+}
+
+// Probability row of the Order1ScaleAC state from raw counts: Laplace +1,
+// scaled to `total` and rounded half away from zero in double precision, at
+// least one each; then the last largest entry is shaved, or the first smallest
+// grown, until the row sums to `total`.
+__host__ __device__ inline void quantize_pmf256(const uint32_t* raw, uint32_t total, uint16_t* out) {
+    double sum = 0;
+    for (int i = 0; i < 256; ++i) sum += double(raw[i] + 1);
+    uint32_t current = 0;
+    for (int i = 0; i < 256; ++i) {
+        double v = round((double(raw[i] + 1) / sum) * double(total));
+        if (v < 1.0) v = 1.0;
+        out[i] = uint16_t(v);
+        current += out[i];
+    }
+    while (current > total) {
+        int am = 0;
+        for (int i = 0; i < 256; ++i) if (out[i] >= out[am]) am = i;
+        if (out[am] > 1) { out[am]--; current--; } else break;
+    }
+    while (current < total) {
+        int am = 0;
+        for (int i = 0; i < 256; ++i) if (out[i] < out[am]) am = i;
+        out[am]++; current++;
+    }
 }
 
 // Huffman code lengths for a histogram: repeated merge of the two smallest

@@ -77,9 +77,11 @@ struct PlanePlan {
     uint32_t first_chunk = 0, n_chunks = 0;
     int codec = C_IDENTITY;
     uint32_t crc = 0;
+    uint8_t role = 0;        // compact terminal role byte of the chain
+    uint32_t row_len = 0;    // rows layout of the plane (last dimension of a passthrough tensor), 0 = flat
     // layout
     std::vector<uint64_t> frame_size;  // per chunk (or one entry for an empty plane)
-    uint64_t payload_len = 0;
+    uint64_t payload_len = 0, state_len = 0;  // state_len: inline state of an unchunked Order1ScaleAC plane
 };
 struct TensorPlan {
     ChainDef chain;
@@ -88,15 +90,21 @@ struct TensorPlan {
     uint64_t hash = 0;
 };
 
-// Estimated size of the whole plane under each codec, the way the reference's
-// trial encode compares them (select.rs:27-64 over dispatch.rs:13-49: Huffman,
-// rANS, then Identity; the first smallest wins).  Huffman is exact up to the
-// per-stream byte rounding, rANS uses the table's information content.
-int select_codec(const unsigned long long* hist, uint64_t n, uint32_t menu) {
+// Size of the whole plane under each codec of the menu, the way the reference's
+// trial encode compares them (select.rs:27-64: smallest state + payload, the
+// first on ties, over dispatch.rs:13-49's order: Order1ScaleAC where it accepts
+// the plane, Huffman, rANS, tANS, Identity).  The sizes come from the plane's
+// histograms instead of three or four full serial encodes of the plane:
+// Huffman is exact up to the per-stream byte rounding, rANS and tANS use the
+// information content under their normalised tables, Order1ScaleAC the
+// information content under the rows it would fit (`o1sac_bytes` < 0: the
+// codec does not accept this plane).
+int select_codec(const unsigned long long* hist, uint64_t n, uint32_t menu, double o1sac_bytes) {
     double best = 0; int best_codec = -1;
     auto offer = [&](int codec, double size) { if (best_codec < 0 || size < best) { best = size; best_codec = codec; } };
     uint32_t raw32[256];
     for (int i = 0; i < 256; ++i) raw32[i] = uint32_t(hist[i]);
+    if ((menu & PTWM_B200_MENU_O1SAC) && o1sac_bytes >= 0) offer(C_O1SAC, o1sac_bytes);
     if ((menu & PTWM_B200_MENU_HUFFMAN)) {
         double size = 1;
         if (n) {
@@ -125,8 +133,46 @@ int select_codec(const unsigned long long* hist, uint64_t n, uint32_t menu) {
         }
         offer(C_RANS, size);
     }
+    if ((menu & PTWM_B200_MENU_TANS)) {
+        double size = 1;
+        if (n) {
+            uint16_t norm[256];
+            int nsym = n <= 0xFFFFFFFFull ? tans_normalize(raw32, n, norm) : 0;
+            if (nsym < 2) size = 1.0 + double(n);
+            else {
+                double bits = 11;
+                for (int i = 0; i < 256; ++i) if (hist[i]) bits += double(hist[i]) * std::log2(2048.0 / norm[i]);
+                double blob = 3 + 3 * nsym + 8 + std::ceil(bits / 8);
+                size = blob >= double(n) ? 1.0 + double(n) : 5.0 + blob;
+            }
+        }
+        offer(C_TANS, size);
+    }
     if ((menu & PTWM_B200_MENU_IDENTITY)) offer(C_IDENTITY, double(n));
     return best_codec;
+}
+
+// Order1ScaleAC accepts byte planes with a row layout whose role is a block or global scale in E4M3, E5M2 or E8M0
+// (order1_scale_ac.rs:493-514); role bytes as in chain/wire_compact.rs:434-459.
+bool o1sac_accepts(uint8_t role, uint32_t row_len) { return row_len && (role <= 0x02 || (role >= 0x08 && role <= 0x0A)); }
+
+// state + payload bytes Order1ScaleAC would need for a plane with these lag-1 counts (the tables of one chunk area, on the host)
+double o1sac_estimate(const uint32_t* joint, const uint32_t* marg) {
+    double bits = 0;
+    uint32_t rows = 0;
+    uint16_t pmf[256];
+    quantize_pmf256(marg, O1SAC_TOTAL, pmf);
+    for (int i = 0; i < 256; ++i) if (marg[i]) bits += double(marg[i]) * std::log2(double(O1SAC_TOTAL) / pmf[i]);
+    for (int ctx = 0; ctx < 256; ++ctx) {
+        const uint32_t* raw = joint + 256 * ctx;
+        uint64_t total = 0;
+        for (int i = 0; i < 256; ++i) total += raw[i];
+        if (!total) continue;
+        ++rows;
+        quantize_pmf256(raw, O1SAC_TOTAL, pmf);
+        for (int i = 0; i < 256; ++i) if (raw[i]) bits += double(raw[i]) * std::log2(double(O1SAC_TOTAL) / pmf[i]);
+    }
+    return 32.0 + 512.0 + 512.0 * rows + std::ceil(bits / 8) + 6;
 }
 
 struct Piece { uint64_t dst; std::vector<uint8_t> bytes; };
@@ -159,10 +205,12 @@ cudaError_t upload_vec(DeviceBuf& b, const std::vector<T>& v, cudaStream_t st) {
 
 int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, const ptwm_b200_encode_options& opt, int device, cudaStream_t st,
                     CrcTables* d_tabs, ptwm_b200_encoded& enc) {
-    const uint32_t chunk_size = opt.chunk_size ? opt.chunk_size : 65536u;
-    const uint32_t menu = opt.menu ? opt.menu : 7u;
-    if (opt.forced_codec >= 0 && opt.forced_codec != C_IDENTITY && opt.forced_codec != C_HUFFMAN && opt.forced_codec != C_RANS)
-        return fail(PTWM_RC_UNSUPPORTED, "device encode offers identity, huffman and rans");
+    const bool chunked = opt.chunk_size != PTWM_B200_CHUNK_NONE;
+    const uint64_t chunk_size = !chunked ? (1ull << 32) : opt.chunk_size ? opt.chunk_size : 65536u;
+    const uint32_t menu = opt.menu ? opt.menu : 31u;
+    if (opt.forced_codec >= 0 && opt.forced_codec != C_IDENTITY && opt.forced_codec != C_HUFFMAN && opt.forced_codec != C_RANS && opt.forced_codec != C_TANS &&
+        opt.forced_codec != C_O1SAC)
+        return fail(PTWM_RC_UNSUPPORTED, "device encode offers identity, huffman, rans, tans and order1_scale_ac");
 
     // ---- chains, registry, planes, chunks -----------------------------------
     std::vector<TensorPlan> plan(n_tensors);
@@ -198,12 +246,16 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
         for (int p = 0; p < np; ++p) {
             PlanePlan& pp = plan[i].planes[size_t(p)];
             pp.len = plane_len; pp.buf_off = planes_bytes; pp.first_chunk = uint32_t(chunks.size());
+            pp.role = plan[i].chain.roles[size_t(p)];
+            // a passthrough plane keeps the tensor's rows (its last dimension); split planes are flat (transforms/byte_split.rs:76)
+            pp.row_len = kind == K_PASS && t.ndim >= 1 && t.shape[t.ndim - 1] && plane_len ? uint32_t(t.shape[t.ndim - 1]) : 0u;
             sp.plane_off[p] = planes_bytes;
             planes_bytes += align_up(plane_len, 16);
             for (uint64_t off = 0; off < plane_len; off += chunk_size) {
                 uint32_t n = uint32_t(std::min<uint64_t>(chunk_size, plane_len - off));
                 uint32_t cap = uint32_t(align_up(uint64_t((n + 3) / 4) * 3 / 2 + 16, 16));  // <= 12 bits per symbol plus the rANS state
-                chunks.push_back(EncChunk{pp.buf_off + off, 0, n, cap, n_planes, 0});
+                // chunks are coded flat (compressor.rs:352-355); a whole plane keeps its rows
+                chunks.push_back(EncChunk{pp.buf_off + off, 0, 0, n, cap, n_planes, chunked ? 0u : pp.row_len});
             }
             pp.n_chunks = uint32_t(chunks.size()) - pp.first_chunk;
             ++n_planes;
@@ -256,23 +308,63 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
     }
     std::vector<uint32_t> accs(n_planes);
     if (opt.emit_plane_crc && n_planes) CUDA_TRY(cudaMemcpyAsync(accs.data(), d_acc.p, accs.size() * 4, cudaMemcpyDeviceToHost, st));
+
+    // Lag-1 counts of every plane Order1ScaleAC accepts, with the plane's rows, for the size comparison below.
+    std::vector<double> o1sac_size(n_planes, -1.0);
+    if (opt.forced_codec < 0 && (menu & PTWM_B200_MENU_O1SAC)) {
+        std::vector<EncChunk> whole;
+        std::vector<uint32_t> which, list;
+        uint32_t pi = 0;
+        for (auto& tp : plan) for (auto& pp : tp.planes) {
+            if (pp.len && o1sac_accepts(pp.role, pp.row_len) && pp.len % pp.row_len == 0) {
+                list.push_back(uint32_t(whole.size()));
+                whole.push_back(EncChunk{pp.buf_off, 0, uint64_t(whole.size()) * (O1E_PRESENT), uint32_t(pp.len), 0, pi, pp.row_len});
+                which.push_back(pi);
+            }
+            ++pi;
+        }
+        if (!whole.empty()) {
+            DeviceBuf d_whole, d_list, d_counts;
+            CUDA_TRY(upload_vec(d_whole, whole, st));
+            CUDA_TRY(upload_vec(d_list, list, st));
+            CUDA_TRY(d_counts.alloc(whole.size() * size_t(O1E_PRESENT)));
+            CUDA_TRY(cudaMemsetAsync(d_counts.p, 0, whole.size() * size_t(O1E_PRESENT), st));
+            o1sac_count_kernel<<<uint32_t(whole.size()), 256, 0, st>>>(d_whole.as<EncChunk>(), d_list.as<uint32_t>(), d_planes.as<uint8_t>(), d_counts.as<uint8_t>());
+            CUDA_TRY(cudaGetLastError());
+            std::vector<uint32_t> counts(whole.size() * size_t(O1E_PRESENT / 4));
+            CUDA_TRY(cudaMemcpyAsync(counts.data(), d_counts.p, counts.size() * 4, cudaMemcpyDeviceToHost, st));
+            CUDA_TRY(cudaStreamSynchronize(st));
+            for (size_t k = 0; k < whole.size(); ++k) {
+                const uint32_t* base = counts.data() + k * size_t(O1E_PRESENT / 4);
+                o1sac_size[which[k]] = o1sac_estimate(base + O1E_JOINT / 4, base + O1E_MARG / 4);
+            }
+        }
+    }
     CUDA_TRY(cudaStreamSynchronize(st));
 
     // ---- codec per plane ------------------------------------------------------
     std::vector<uint8_t> plane_codec(n_planes);
+    std::vector<uint32_t> o1sac_chunks;
+    uint64_t tables_bytes = 0;
     {
         uint32_t pi = 0;
         const CrcTables& T = crc_tables();
         for (size_t i = 0; i < n_tensors; ++i) {
             enc.plane_codecs.emplace_back();
             for (auto& pp : plan[i].planes) {
-                pp.codec = opt.forced_codec >= 0 ? opt.forced_codec : select_codec(&plane_hist[size_t(pi) * 256], pp.len, menu);
+                pp.codec = opt.forced_codec >= 0 ? opt.forced_codec : select_codec(&plane_hist[size_t(pi) * 256], pp.len, menu, o1sac_size[pi]);
                 if (pp.codec < 0) return fail(PTWM_RC_INVALID_INPUT, "empty codec menu");
+                if (pp.codec == C_O1SAC && !chunked && pp.row_len && pp.len % pp.row_len) return fail(PTWM_RC_INVALID_INPUT, "order1_scale_ac: the row length does not divide the plane");
                 plane_codec[pi] = uint8_t(pp.codec);
                 enc.plane_codecs.back().push_back(pp.codec);
                 if (opt.emit_plane_crc) pp.crc = pp.len ? ~(accs[pi] ^ gf2_mulmod(x_pow_8n(T.x2n, pp.len), 0xFFFFFFFFu)) : 0u;
-                if (pp.codec != C_IDENTITY)  // stream slots only for planes that get coded
-                    for (uint32_t k = 0; k < pp.n_chunks; ++k) { EncChunk& ch = chunks[pp.first_chunk + k]; ch.slot_off = slots_bytes; slots_bytes += uint64_t(ch.slot_cap) * 4; }
+                if (pp.codec != C_IDENTITY)  // stream slots and table areas only for planes that get coded
+                    for (uint32_t k = 0; k < pp.n_chunks; ++k) {
+                        EncChunk& ch = chunks[pp.first_chunk + k];
+                        ch.slot_off = slots_bytes; slots_bytes += uint64_t(ch.slot_cap) * 4;
+                        ch.table_off = tables_bytes; tables_bytes += enc_table_bytes(pp.codec);
+                        if (pp.codec == C_O1SAC) o1sac_chunks.push_back(pp.first_chunk + k);
+                    }
                 ++pi;
             }
             if (opt.emit_payload_hash) plan[i].hash = hashes[i];
@@ -282,10 +374,24 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
     // ---- tables and streams ---------------------------------------------------
     CUDA_TRY(upload_vec(d_codec, plane_codec, st));
     if (n_chunks) CUDA_TRY(cudaMemcpyAsync(d_chunks.p, chunks.data(), chunks.size() * sizeof(EncChunk), cudaMemcpyHostToDevice, st));
-    CUDA_TRY(d_tables.alloc(uint64_t(n_chunks) * ENC_TABLE_BYTES));
+    CUDA_TRY(d_tables.alloc(tables_bytes));
     CUDA_TRY(d_results.alloc(uint64_t(n_chunks) * sizeof(EncResult)));
+    CUDA_TRY(cudaMemsetAsync(d_results.p, 0, uint64_t(n_chunks) * sizeof(EncResult) + (n_chunks ? 0 : 1), st));
     CUDA_TRY(d_slots.alloc(slots_bytes));
     std::vector<EncResult> results(n_chunks);
+    DeviceBuf d_o1list;
+    if (!o1sac_chunks.empty()) {  // Order1ScaleAC: counts, rows, then the range coder, one chunk per block / thread
+        CUDA_TRY(upload_vec(d_o1list, o1sac_chunks, st));
+        for (uint32_t ci : o1sac_chunks) CUDA_TRY(cudaMemsetAsync(d_tables.as<uint8_t>() + chunks[ci].table_off, 0, O1E_PRESENT, st));
+        const uint32_t n_o1 = uint32_t(o1sac_chunks.size());
+        o1sac_count_kernel<<<n_o1, 256, 0, st>>>(d_chunks.as<EncChunk>(), d_o1list.as<uint32_t>(), d_planes.as<uint8_t>(), d_tables.as<uint8_t>());
+        CUDA_TRY(cudaGetLastError());
+        o1sac_fit_kernel<<<n_o1, 288, 0, st>>>(d_chunks.as<EncChunk>(), d_o1list.as<uint32_t>(), d_tables.as<uint8_t>(), d_results.as<EncResult>());
+        CUDA_TRY(cudaGetLastError());
+        o1sac_encode_kernel<<<(n_o1 + 63) / 64, 64, 0, st>>>(d_chunks.as<EncChunk>(), d_o1list.as<uint32_t>(), n_o1, d_planes.as<uint8_t>(), d_tables.as<uint8_t>(),
+                                                             d_slots.as<uint8_t>(), d_results.as<EncResult>());
+        CUDA_TRY(cudaGetLastError());
+    }
     if (n_chunks) {
         table_kernel<<<(n_chunks + 63) / 64, 64, 0, st>>>(d_chunks.as<EncChunk>(), n_chunks, d_codec.as<uint8_t>(), d_hist.as<uint32_t>(), d_tables.as<uint8_t>(), d_results.as<EncResult>());
         CUDA_TRY(cudaGetLastError());
@@ -297,9 +403,13 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
 
     // ---- layout: chunk frames, plane payloads, records ------------------------
     std::vector<uint32_t> chunk_mode(n_chunks);
+    const uint64_t frame_hdr = chunked ? 5 : 0;  // [state_version][state_len u32] in front of every chunk; an unchunked plane has none
     for (auto& tp : plan) for (auto& pp : tp.planes) {
-        if (pp.len == 0) {  // an empty plane is one empty chunk (compressor.rs:333-345)
-            pp.frame_size.push_back(pp.codec == C_IDENTITY ? 5 : 6);
+        if (pp.len == 0) {  // an empty plane is one empty chunk (compressor.rs:333-345), or an empty payload / the raw tag alone when unchunked
+            // Order1ScaleAC fitted to no symbols: no rows, the smoothed marginal (16 everywhere), and the coder's six flush bytes
+            const uint64_t body = pp.codec == C_IDENTITY ? 0 : pp.codec == C_O1SAC ? 6 : 1;
+            if (pp.codec == C_O1SAC) pp.state_len = 32 + 512;
+            pp.frame_size.push_back(frame_hdr + pp.state_len + body);
             pp.payload_len = pp.frame_size[0];
             continue;
         }
@@ -307,25 +417,34 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
             uint32_t ci = pp.first_chunk + k;
             const EncResult& r = results[ci];
             uint64_t n = chunks[ci].n, size;
-            if (pp.codec == C_IDENTITY) { chunk_mode[ci] = 0; size = 5 + n; }
-            else {
-                uint64_t hdr = pp.codec == C_RANS ? 1 + 2 * (uint64_t(r.hdr_n) + 1) : (r.hdr_n <= 127 ? 1 : 2) + (uint64_t(r.hdr_n) + 1) / 2;
-                uint64_t blob = hdr + 16 + uint64_t(r.stream_len[0]) + r.stream_len[1] + r.stream_len[2] + r.stream_len[3];
+            if (pp.codec == C_IDENTITY) { chunk_mode[ci] = 0; size = frame_hdr + n; }
+            else if (pp.codec == C_O1SAC) {
+                chunk_mode[ci] = 5;
+                size = frame_hdr + r.stream_len[1] + r.stream_len[0];  // the state sits in front of the coder's bytes either way
+                if (!chunked) pp.state_len = r.stream_len[1];
+            } else {
+                uint64_t blob;
+                if (pp.codec == C_TANS) blob = 3 + 3 * uint64_t(r.hdr_n) + 8 + r.stream_len[0];
+                else {
+                    uint64_t hdr = pp.codec == C_RANS ? 1 + 2 * (uint64_t(r.hdr_n) + 1) : (r.hdr_n <= 127 ? 1 : 2) + (uint64_t(r.hdr_n) + 1) / 2;
+                    blob = hdr + 16 + uint64_t(r.stream_len[0]) + r.stream_len[1] + r.stream_len[2] + r.stream_len[3];
+                }
                 // stored raw when coding does not shrink the chunk (compress.rs NotBeneficial) or the length rule refuses it (length_prefix.rs:29-33)
-                bool coded = r.coded && blob < n && (pp.codec != C_RANS || n <= (1ull << 30) || n <= blob * 64);
-                chunk_mode[ci] = coded ? (pp.codec == C_RANS ? 2 : 3) : 1;
-                size = coded ? 5 + 1 + 4 + blob : 5 + 1 + n;
+                bool coded = r.coded && blob < n && (pp.codec == C_HUFFMAN || n <= (1ull << 30) || n <= blob * 64);
+                chunk_mode[ci] = coded ? (pp.codec == C_RANS ? 2 : pp.codec == C_HUFFMAN ? 3 : 4) : 1;
+                size = coded ? frame_hdr + 1 + 4 + blob : frame_hdr + 1 + n;
             }
+            if (!chunked) chunk_mode[ci] |= GATHER_NOFRAME;
             pp.frame_size.push_back(size);
             pp.payload_len += size;
         }
-        if (pp.payload_len > 0xFFFFFFFFull) return fail(PTWM_RC_UNSUPPORTED, "chunked plane payload exceeds the u32 offset range (compressor.rs:370-372)");
+        if (pp.payload_len > 0xFFFFFFFFull) return fail(PTWM_RC_UNSUPPORTED, "plane payload exceeds the u32 offset range (compressor.rs:370-372)");
     }
 
     // Extension Table: chain ops in registry order, then the used codecs in built-in order (container.rs:167-223)
     std::vector<std::pair<uint8_t, uint16_t>> table;
     for (auto& c : registry) for (auto& nd : c.nodes) if (std::find(table.begin(), table.end(), std::make_pair(uint8_t(1), nd.first)) == table.end()) table.push_back({1, nd.first});
-    for (int codec : {int(C_IDENTITY), int(C_HUFFMAN), int(C_RANS)}) {
+    for (int codec : {int(C_IDENTITY), int(C_HUFFMAN), int(C_RANS), int(C_TANS), int(C_O1SAC)}) {
         bool used = false;
         for (auto& tp : plan) for (auto& pp : tp.planes) used |= pp.codec == codec;
         if (used) table.push_back({2, uint16_t(codec)});
@@ -377,6 +496,32 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
         put_varint(b, plan[i].planes.size());
         for (size_t p = 0; p < plan[i].planes.size(); ++p) {
             PlanePlan& pp = plan[i].planes[p];
+            if (!chunked) {
+                // one payload per plane with the state in front of it (tensor_record_compact.rs:203-493): every codec but Identity
+                // is written with an inline state (empty unless Order1ScaleAC), the plane's row layout is recorded
+                const bool inline_state = pp.codec != C_IDENTITY, extra = pp.codec == C_O1SAC;
+                b.push_back(uint8_t((inline_state ? 0x04 : 0) | (opt.emit_plane_crc ? 0x01 : 0) | (pp.row_len ? 0x10 : 0) | (extra ? 0x20 : 0)));
+                b.push_back(plane_role_byte(plan[i].chain.roles[p]));
+                put_varint(b, table_index(2, uint16_t(pp.codec)));
+                if (extra) { b.push_back(1); put_varint(b, 0); }
+                if (inline_state) put_varint(b, pp.state_len);
+                put_varint(b, pp.payload_len - pp.state_len);
+                if (pp.row_len) put_varint(b, pp.row_len);
+                if (opt.emit_plane_crc) put_u32(b, pp.crc);
+                if (pp.len == 0) {
+                    if (pp.codec == C_O1SAC) {  // state of an empty plane: no rows, the marginal of no counts (16 everywhere); payload: the coder's flush
+                        for (int z = 0; z < 32; ++z) b.push_back(0);
+                        for (int z = 0; z < 256; ++z) { b.push_back(16); b.push_back(0); }
+                        for (int z = 0; z < 6; ++z) b.push_back(0);
+                    } else if (pp.codec != C_IDENTITY) b.push_back(0);
+                    flush(b);
+                    continue;
+                }
+                flush(b);
+                gathers.push_back(GatherItem{pos, pp.first_chunk, chunk_mode[pp.first_chunk]});
+                pos += pp.frame_size[0];
+                continue;
+            }
             b.push_back(uint8_t(0x02 | (opt.emit_plane_crc ? 0x01 : 0)));
             b.push_back(plane_role_byte(plan[i].chain.roles[p]));
             put_varint(b, table_index(2, uint16_t(pp.codec)));
@@ -390,8 +535,15 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
                 off += pp.frame_size[k];
             }
             if (pp.len == 0) {  // the one empty frame is host data
-                for (int z = 0; z < 5; ++z) b.push_back(0);
-                if (pp.codec != C_IDENTITY) b.push_back(0);
+                if (pp.codec == C_O1SAC) {
+                    b.push_back(1); put_u32(b, 32 + 512);
+                    for (int z = 0; z < 32; ++z) b.push_back(0);
+                    for (int z = 0; z < 256; ++z) { b.push_back(16); b.push_back(0); }
+                    for (int z = 0; z < 6; ++z) b.push_back(0);
+                } else {
+                    for (int z = 0; z < 5; ++z) b.push_back(0);
+                    if (pp.codec != C_IDENTITY) b.push_back(0);
+                }
                 flush(b);
                 continue;
             }
@@ -439,7 +591,8 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
 // Identity copies; Huffman and rANS run the container encoder's kernels on a single chunk that spans the
 // plane and keep the reference's rules for falling back to the raw-tagged form (codecs/huffman.rs:37-88,
 // codecs/rans.rs:38-95).  `needed` receives the payload size, also when `out_cap` is too small (-2).
-int64_t ptwm::encode_plane_cuda(int codec, uint64_t in_dev, size_t n, uint64_t out_dev, size_t out_cap, uint64_t* needed, cudaStream_t st) {
+int64_t ptwm::encode_plane_cuda(int codec, const uint8_t* state, size_t state_len, uint8_t state_version, uint64_t in_dev, size_t n, uint64_t out_dev, size_t out_cap,
+                                uint64_t* needed, cudaStream_t st) {
     // the required size goes to *needed only when the output buffer cannot hold it
     auto need = [&](uint64_t v) { if (needed && v > out_cap) *needed = v; return v; };
     uint8_t* out = reinterpret_cast<uint8_t*>(uintptr_t(out_dev));
@@ -450,7 +603,49 @@ int64_t ptwm::encode_plane_cuda(int codec, uint64_t in_dev, size_t n, uint64_t o
         CUDA_TRY(cudaStreamSynchronize(st));
         return int64_t(n);
     }
-    if (codec != C_HUFFMAN && codec != C_RANS) return fail(PTWM_RC_UNSUPPORTED, "device encode covers identity, huffman and rans");
+    if (n > 0xFFFFFFFFull && codec == C_O1SAC) return fail(PTWM_RC_UNSUPPORTED, "plane too long for the device encoder");
+    DeviceBuf d_chunk, d_codec, d_hist, d_phist, d_tables, d_results, d_slots, d_gather, d_list;
+    const uint64_t slot_cap = ((n / 4 + 1) * 12 + 7) / 8 + 64;  // a symbol takes at most 12 bits in any of the codecs
+    EncChunk chunk{0, 0, 0, uint32_t(n), uint32_t(slot_cap), 0, 0};
+    const uint8_t codec_byte = uint8_t(codec);
+    if (codec == C_O1SAC) {
+        // The flat ABI has no way to return a fitted state, so the rows come from the caller (the shared-state form of
+        // order1_scale_ac.rs:620-633): [bitmap 32][marginal 512][rows 512 each], one row spanning the plane.
+        if (!state_len) return fail(PTWM_RC_UNSUPPORTED, "order1_scale_ac through the plane-codec ABI needs the state to encode with (state_ptr, state_len)");
+        try { check_o1sac(state, state_len, state_version, 5, 0, 0); } catch (const FormatError& e) { return fail(PTWM_RC_INVALID_INPUT, e.what()); }
+        if (slot_cap > 0x3FFFFFFFull) return fail(PTWM_RC_UNSUPPORTED, "plane too long for the device encoder");
+        std::vector<uint8_t> tab(ENC_O1SAC_TABLE_BYTES, 0);
+        uint16_t* pmf = reinterpret_cast<uint16_t*>(tab.data() + O1E_PMF);
+        uint16_t* cum = reinterpret_cast<uint16_t*>(tab.data() + O1E_CUM);
+        auto load_row = [&](uint32_t row, const uint8_t* src) {
+            uint32_t acc = 0;
+            for (int i = 0; i < 256; ++i) { pmf[256 * row + i] = uint16_t(src[2 * i] | (src[2 * i + 1] << 8)); cum[256 * row + i] = uint16_t(acc); acc += pmf[256 * row + i]; }
+        };
+        load_row(0, state + 32);
+        uint32_t k = 0;
+        for (uint32_t ctx = 0; ctx < 256; ++ctx)
+            if (state[ctx >> 3] & (1u << (ctx & 7))) { tab[O1E_PRESENT + ctx] = 1; load_row(1 + ctx, state + 32 + 512 + 512 * size_t(k)); ++k; }
+        const uint32_t zero = 0;
+        CUDA_TRY(d_chunk.alloc(sizeof(EncChunk)));
+        CUDA_TRY(d_tables.alloc(tab.size()));
+        CUDA_TRY(d_results.alloc(sizeof(EncResult)));
+        CUDA_TRY(d_slots.alloc(4 * slot_cap));
+        CUDA_TRY(d_list.alloc(4));
+        CUDA_TRY(cudaMemcpyAsync(d_chunk.p, &chunk, sizeof(chunk), cudaMemcpyHostToDevice, st));
+        CUDA_TRY(cudaMemcpyAsync(d_tables.p, tab.data(), tab.size(), cudaMemcpyHostToDevice, st));
+        CUDA_TRY(cudaMemcpyAsync(d_list.p, &zero, 4, cudaMemcpyHostToDevice, st));
+        CUDA_TRY(cudaMemsetAsync(d_results.p, 0, sizeof(EncResult), st));
+        o1sac_encode_kernel<<<1, 64, 0, st>>>(d_chunk.as<EncChunk>(), d_list.as<uint32_t>(), 1, in, d_tables.as<uint8_t>(), d_slots.as<uint8_t>(), d_results.as<EncResult>());
+        CUDA_TRY(cudaGetLastError());
+        EncResult r;
+        CUDA_TRY(cudaMemcpyAsync(&r, d_results.p, sizeof(r), cudaMemcpyDeviceToHost, st));
+        CUDA_TRY(cudaStreamSynchronize(st));
+        if (need(r.stream_len[0]) > out_cap) return fail(PTWM_RC_BUFFER_TOO_SMALL, "output buffer too small");
+        CUDA_TRY(cudaMemcpyAsync(out, d_slots.p, r.stream_len[0], cudaMemcpyDeviceToDevice, st));
+        CUDA_TRY(cudaStreamSynchronize(st));
+        return int64_t(r.stream_len[0]);
+    }
+    if (codec != C_HUFFMAN && codec != C_RANS && codec != C_TANS) return fail(PTWM_RC_UNSUPPORTED, "device encode covers identity, huffman, rans, tans and order1_scale_ac");
     if (n == 0) {  // an empty plane is the raw tag alone
         if (need(1) > out_cap) return fail(PTWM_RC_BUFFER_TOO_SMALL, "output buffer too small");
         CUDA_TRY(cudaMemsetAsync(out, 0, 1, st));
@@ -459,19 +654,14 @@ int64_t ptwm::encode_plane_cuda(int codec, uint64_t in_dev, size_t n, uint64_t o
     }
     uint32_t mode = 1;
     uint64_t size = 1 + uint64_t(n);
-    DeviceBuf d_chunk, d_codec, d_hist, d_phist, d_tables, d_results, d_slots, d_gather;
-    EncChunk chunk{0, 0, 0, 0, 0, 0};
+    CUDA_TRY(d_chunk.alloc(sizeof(EncChunk)));
+    CUDA_TRY(d_results.alloc(sizeof(EncResult)));
+    CUDA_TRY(d_tables.alloc(enc_table_bytes(codec)));
     if (n <= 0xFFFFFFFFull) {  // the length prefix is a u32; longer planes stay raw
-        const uint64_t slot_cap = ((n / 4 + 1) * 11 + 7) / 8 + 64;  // a symbol takes at most 11 bits in either codec
-        if (slot_cap > 0xFFFFFFFFull) return fail(PTWM_RC_UNSUPPORTED, "plane too long for the device encoder");
-        chunk.n = uint32_t(n); chunk.slot_cap = uint32_t(slot_cap);
-        const uint8_t codec_byte = uint8_t(codec);
-        CUDA_TRY(d_chunk.alloc(sizeof(EncChunk)));
+        if (slot_cap > 0x3FFFFFFFull) return fail(PTWM_RC_UNSUPPORTED, "plane too long for the device encoder");
         CUDA_TRY(d_codec.alloc(1));
         CUDA_TRY(d_hist.alloc(256 * sizeof(uint32_t)));
         CUDA_TRY(d_phist.alloc(256 * sizeof(unsigned long long)));
-        CUDA_TRY(d_tables.alloc(ENC_TABLE_BYTES));
-        CUDA_TRY(d_results.alloc(sizeof(EncResult)));
         CUDA_TRY(d_slots.alloc(4 * slot_cap));
         CUDA_TRY(cudaMemcpyAsync(d_chunk.p, &chunk, sizeof(chunk), cudaMemcpyHostToDevice, st));
         CUDA_TRY(cudaMemcpyAsync(d_codec.p, &codec_byte, 1, cudaMemcpyHostToDevice, st));
@@ -483,14 +673,15 @@ int64_t ptwm::encode_plane_cuda(int codec, uint64_t in_dev, size_t n, uint64_t o
         EncResult r;
         CUDA_TRY(cudaMemcpyAsync(&r, d_results.p, sizeof(r), cudaMemcpyDeviceToHost, st));
         CUDA_TRY(cudaStreamSynchronize(st));
-        const uint64_t hdr = codec == C_RANS ? 1 + 2 * (uint64_t(r.hdr_n) + 1) : (r.hdr_n <= 127 ? 1 : 2) + (uint64_t(r.hdr_n) + 1) / 2;
-        const uint64_t blob = hdr + 16 + uint64_t(r.stream_len[0]) + r.stream_len[1] + r.stream_len[2] + r.stream_len[3];
-        const bool coded = r.coded && blob < n && (codec != C_RANS || n <= (1ull << 30) || n <= blob * 64);
-        if (coded) { mode = codec == C_RANS ? 2 : 3; size = 1 + 4 + blob; }
+        uint64_t blob;
+        if (codec == C_TANS) blob = 3 + 3 * uint64_t(r.hdr_n) + 8 + r.stream_len[0];
+        else {
+            const uint64_t hdr = codec == C_RANS ? 1 + 2 * (uint64_t(r.hdr_n) + 1) : (r.hdr_n <= 127 ? 1 : 2) + (uint64_t(r.hdr_n) + 1) / 2;
+            blob = hdr + 16 + uint64_t(r.stream_len[0]) + r.stream_len[1] + r.stream_len[2] + r.stream_len[3];
+        }
+        const bool coded = r.coded && blob < n && (codec == C_HUFFMAN || n <= (1ull << 30) || n <= blob * 64);
+        if (coded) { mode = codec == C_RANS ? 2 : codec == C_HUFFMAN ? 3 : 4; size = 1 + 4 + blob; }
     } else {
-        CUDA_TRY(d_chunk.alloc(sizeof(EncChunk)));
-        CUDA_TRY(d_results.alloc(sizeof(EncResult)));
-        CUDA_TRY(d_tables.alloc(ENC_TABLE_BYTES));
         CUDA_TRY(d_slots.alloc(16));
     }
     if (need(size) > out_cap) return fail(PTWM_RC_BUFFER_TOO_SMALL, "output buffer too small");

@@ -42,6 +42,7 @@ const CrcTables& crc_tables();
 inline uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
 
 // One plane into one payload on the device (encoder.cu); body of ptwm_plane_codec_v1_encode_cuda.
-int64_t encode_plane_cuda(int codec, uint64_t in_dev, size_t n, uint64_t out_dev, size_t out_cap, uint64_t* needed, cudaStream_t st);
+int64_t encode_plane_cuda(int codec, const uint8_t* state, size_t state_len, uint8_t state_version, uint64_t in_dev, size_t n, uint64_t out_dev, size_t out_cap,
+                          uint64_t* needed, cudaStream_t st);
 
 }  // namespace ptwm

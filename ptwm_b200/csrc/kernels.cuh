@@ -597,9 +597,14 @@ __device__ __forceinline__ void rans_short_group(const uint32_t* tab, const uint
 // nearly incompressible bytes (many symbols, close to a byte each) that would
 // happen in every other group, so a lane whose chunk has many distinct symbols
 // (`dense`, only where DENSE_OK) reloads the window after four symbols.
+// The byte count is ((leading zeros - 1) & 24) / 8, which holds for every state
+// below 2^31.  An update never takes a state from below 2^31 to above it
+// (freq <= 2^11, x >> 11 < 2^20), so only a stream whose stored initial state
+// has the top bit set can get there: such a lane passes `slow` and takes the
+// byte-wise path for every group.
 template <int LS, bool DENSE_OK>
 __device__ __forceinline__ void rans_group8(const uint32_t* tab, const uint32_t* lst, const uint32_t* rw, uint32_t& x, uint32_t& rq, uint32_t& s_lo,
-                                            uint32_t& s_hi, bool dense) {
+                                            uint32_t& s_hi, bool dense, bool slow) {
     uint32_t wh, wl, used = 0, over = 0;
     const uint32_t x0 = x, rq0 = rq;
     ring_window_be(rw, rq, wh, wl);
@@ -615,13 +620,13 @@ __device__ __forceinline__ void rans_group8(const uint32_t* tab, const uint32_t*
         const uint32_t ins = (0x3210u & ~(0xFu << (4 * (j & 3)))) | (4u << (4 * (j & 3)));  // low byte of e into byte j & 3
         if (j < 4) s_lo = __byte_perm(s_lo, e, ins); else s_hi = __byte_perm(s_hi, e, ins);
         // bytes until x >= 2^23, at most three: 0 for clz <= 8, 1 for 9..16, 2 for 17..24, 3 above
-        uint32_t sh = uint32_t(max(int(__clz(x)) - 1, 0)) & 0x18u;
+        uint32_t sh = (uint32_t(__clz(x)) - 1u) & 0x18u;
         x = __funnelshift_l(wh, x, sh);
         wh = __funnelshift_l(wl, wh, sh);
         wl <<= sh;
         used += sh;
     }
-    if (used > 64 || over > 64) {
+    if (used > 64 || over > 64 || slow) {
         x = x0; rq = rq0;
         rans_short_group<LS>(tab, lst, rw, x, rq, 8, s_lo, s_hi);
     } else {
@@ -747,6 +752,7 @@ __global__ void __launch_bounds__(32, 20) rans_decode_kernel_t(const DecodeItem*
             Epilogue ep = make_epilogue(bases, it);
             const uint8_t* st = src + my_off;
             uint32_t x = ld_u32_unaligned(st);
+            const bool slow = x >> 31;  // see rans_group8
             // ring cursor as a 32-bit offset from the 16-byte aligned block that holds the first renorm byte
             const uintptr_t g0 = (reinterpret_cast<uintptr_t>(st) + 4) & ~uintptr_t(15);
             uint32_t rq = uint32_t(reinterpret_cast<uintptr_t>(st) + 4 - g0);
@@ -781,7 +787,7 @@ __global__ void __launch_bounds__(32, 20) rans_decode_kernel_t(const DecodeItem*
             }
             fast_groups(ep, it.n, pos, remaining, [&](uint32_t& s_lo, uint32_t& s_hi) {
                 top_up();
-                rans_group8<LS, !PER_LANE>(tab, lst, rw, x, rq, s_lo, s_hi, dense);
+                rans_group8<LS, !PER_LANE>(tab, lst, rw, x, rq, s_lo, s_hi, dense, slow);
             });
             // tail: whatever the fast loops left
             while (remaining) {

@@ -570,8 +570,8 @@ int64_t ptwm_plane_codec_v1_decode_cuda(uint8_t sfv, const uint8_t* state_ptr, s
                                         uint64_t in_dev_ptr, size_t in_len, uint64_t out_dev_ptr, size_t out_cap, uint32_t device_ordinal) {
     return decode_plane_cuda(sfv, state_ptr, state_len, codec_id_ptr, codec_id_len, in_dev_ptr, in_len, out_dev_ptr, out_cap, device_ordinal);
 }
-int64_t ptwm_plane_codec_v1_encode_cuda(uint8_t, const uint8_t*, size_t, const uint8_t* codec_id, size_t codec_id_len, uint64_t in_dev, size_t in_len, uint64_t out_dev,
-                                        size_t out_cap, uint64_t* needed_out, uint32_t device_ordinal) {
+int64_t ptwm_plane_codec_v1_encode_cuda(uint8_t sfv, const uint8_t* state_ptr, size_t state_len, const uint8_t* codec_id, size_t codec_id_len, uint64_t in_dev, size_t in_len,
+                                        uint64_t out_dev, size_t out_cap, uint64_t* needed_out, uint32_t device_ordinal) {
     // *needed_out is written only together with PTWM_RC_BUFFER_TOO_SMALL and left untouched otherwise (native.rs:176-184)
     if (!codec_id || codec_id_len != 32) return fail(PTWM_RC_INVALID_INPUT, "codec_id must be a 32-byte canonical id");
     int codec = -1;
@@ -583,7 +583,7 @@ int64_t ptwm_plane_codec_v1_encode_cuda(uint8_t, const uint8_t*, size_t, const u
     DeviceState* ds;
     int64_t rc = device_state(int(device_ordinal), &ds);
     if (rc < 0) return rc;
-    return encode_plane_cuda(codec, in_dev, in_len, out_dev, out_cap, needed_out, ds->stream);
+    return encode_plane_cuda(codec, state_len ? state_ptr : nullptr, state_len, sfv, in_dev, in_len, out_dev, out_cap, needed_out, ds->stream);
 }
 // Host buffers, rANS (the codec this bundle registers as its plane codec): the payload is built on GPU 0.
 int64_t ptwm_plane_codec_v1_encode(const uint8_t* in, size_t in_len, uint8_t* out, size_t out_len) {
@@ -601,7 +601,7 @@ int64_t ptwm_plane_codec_v1_encode(const uint8_t* in, size_t in_len, uint8_t* ou
     Free f2{d_out};
     CUDA_TRY(cudaMemcpy(d_in, in, in_len, cudaMemcpyHostToDevice));
     uint64_t needed = 0;
-    int64_t n = encode_plane_cuda(C_RANS, uint64_t(reinterpret_cast<uintptr_t>(d_in)), in_len, uint64_t(reinterpret_cast<uintptr_t>(d_out)), cap, &needed, ds->stream);
+    int64_t n = encode_plane_cuda(C_RANS, nullptr, 0, 0, uint64_t(reinterpret_cast<uintptr_t>(d_in)), in_len, uint64_t(reinterpret_cast<uintptr_t>(d_out)), cap, &needed, ds->stream);
     if (n < 0) return n;
     if (size_t(n) > out_len) return fail(PTWM_RC_BUFFER_TOO_SMALL, "output buffer too small");
     CUDA_TRY(cudaMemcpy(out, d_out, size_t(n), cudaMemcpyDeviceToHost));
