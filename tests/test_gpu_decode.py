@@ -248,6 +248,20 @@ def test_full_size_properties():
         check_container(blob, {s.name: s.raw for s in specs})
 
 
+def test_replica_mode_with_one_rank_equals_decode_model():
+    # the gather-of-one path: the rank's own span is the whole range, nothing crosses NVLink, then one local decode
+    from ptwm_b200.sharding import decode_replica
+    specs = mixed_model()
+    blob = oracle.write_container(specs, chunk_size=4096, emit_crc=True, emit_hash=True)
+    h = ptwm_b200.ContainerHandle(torch.frombuffer(bytearray(blob), dtype=torch.uint8).pin_memory(), device=0)
+    got, received = decode_replica(h)
+    assert received == 0 and [n for n, _ in got] == [s.name for s in specs]
+    for (name, t), s in zip(got, specs):
+        assert bytes_of(t) == s.raw, name
+    some, _ = decode_replica(h, names=[specs[3].name, specs[0].name])
+    assert [n for n, _ in some] == [specs[3].name, specs[0].name] and bytes_of(some[0][1]) == specs[3].raw
+
+
 def test_partial_blob_span_and_subset_plan():
     # a rank keeps only the byte range of its own tensors on the device
     specs = mixed_model()
