@@ -5,10 +5,17 @@ Workload: the synthetic Llama-3-8B-shape bf16 state dict (291 tensors,
 as ONE compact container by this package's device encoder the way the
 reference's own decode benchmark writes its input (forced rANS, no payload
 hash, no plane CRC: benchmarks/decode_throughput.py:41-42 and
-benchmarks/_common.py:190-198 of the reference), with 64 KiB chunks.  A step
+benchmarks/_common.py:190-198 of the reference), with 32 KiB chunks.  A step
 decodes the whole container; with N ranks the records are split into N
 contiguous runs and every rank decodes its own run from its own byte range of
 the file, with no collective (strong scaling).
+
+At one GPU the line also carries `extras`: smaller cases of what other writers
+produce (plane CRCs and payload hashes verified, 512 KiB chunks, tANS exponent
+planes, the full codec menu, the other benchmark configurations with their own
+roofline figures, and the encode path), each timed with the L2 flushed between
+iterations.  With N ranks it carries `replica_e2e`: every rank ends up with the
+whole model (its share of the compressed bytes over PCIe, the rest over NVLink).
 
   python bench.py --gpus 1 --steps 5 --warmup 3
   python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N
@@ -70,7 +77,11 @@ def build_container(shapes, indices, device, chunk: int, codec: str, crc: bool):
         raw += tensors[name].numel() * 2
     forced = {"rans": RANS, "huffman": HUFFMAN, "identity": IDENTITY, "auto": None}[codec]
     cfg = CompressionConfig(streaming_chunk=chunk, forced_codec=forced, codec_menu=(IDENTITY, HUFFMAN, RANS), emit_plane_crc=crc, emit_payload_hash=False)
+    torch.cuda.synchronize(device)
+    t0 = time.perf_counter()
     enc = compress_model(tensors, cfg, device=device.index)
+    torch.cuda.synchronize(device)
+    enc.encode_s = time.perf_counter() - t0  # the call returns with the container complete in device memory
     return enc, raw, tensors
 
 
@@ -150,6 +161,182 @@ def time_cpu_decode(blob, expect, threads: int, repeats: int):
     return statistics.median(times), dec
 
 
+_FLUSH = {}
+
+
+def flush_l2(device):
+    """Overwrite a buffer larger than the 126 MB L2 so that the next iteration starts with a cold cache."""
+    buf = _FLUSH.get(device)
+    if buf is None:
+        buf = _FLUSH[device] = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    buf.fill_(1)
+
+
+def sigma_row_weights(rows, cols, seed, device):
+    """Normal(0, sigma_row), sigma_row log-uniform in [0.005, 0.05] per row (the block-set configurations)."""
+    import math
+    g = torch.Generator(device=device).manual_seed(seed)
+    w = torch.randn(rows, cols, generator=g, device=device)
+    lo, hi = math.log(0.005), math.log(0.05)
+    return w * torch.exp(torch.rand(rows, 1, generator=g, device=device) * (hi - lo) + lo)
+
+
+def _e2m1_pack(x):
+    levels = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], device=x.device)
+    idx = (x.abs().unsqueeze(-1) - levels).abs().argmin(-1).to(torch.uint8) | ((x < 0).to(torch.uint8) << 3)
+    return (idx[..., 0::2] | (idx[..., 1::2] << 4)).contiguous()
+
+
+def config_tensors(which: str, device):
+    """Synthetic tensors of the reference's benchmark configurations 1-4 -> (tensors, usage)."""
+    d, ffn = 4096, 14336
+    if which == "config1":
+        return {"w": make_tensor(0, (d, d), False, device)}, {}
+    if which in ("config2_fp32", "config2_fp16"):
+        dt = torch.float32 if which.endswith("fp32") else torch.float16
+        shapes = [("q", d, d), ("k", d, d), ("v", d, d), ("o", d, d), ("gate", ffn, d), ("up", ffn, d), ("down", d, ffn)]
+        t = {f"blk.{n}_proj.weight": sigma_row_weights(r, c, 1000 + i, device).to(dt) for i, (n, r, c) in enumerate(shapes)}
+        for i, n in enumerate(("input_layernorm", "post_attention_layernorm")):
+            g = torch.Generator(device=device).manual_seed(1100 + i)
+            t[f"blk.{n}.weight"] = (1 + 0.01 * torch.randn(d, generator=g, device=device)).to(dt)
+        return t, {}
+    if which == "config3":
+        t = {}
+        for i, (rows, cols) in enumerate([(ffn, d), (d, ffn)]):
+            w = sigma_row_weights(rows, cols, 2000 + i, device)
+            scale = w.abs().amax(dim=1, keepdim=True) / 448.0
+            t[f"l{i}.weight"] = (w / scale).to(torch.float8_e4m3fn)
+            t[f"l{i}.weight_scale"] = scale.reshape(-1).float()
+        return t, {}
+    if which == "config4":
+        rows, cols = ffn, d
+        w = sigma_row_weights(rows, cols, 3000, device).double()
+        blk = w.reshape(rows, cols // 32, 32)
+        e = (127 + torch.ceil(torch.log2(blk.abs().amax(-1).clamp_min(1e-30) / 6.0))).clamp(0, 254).to(torch.uint8)
+        mx = _e2m1_pack((blk / torch.exp2(e.double() - 127).unsqueeze(-1)).reshape(rows, cols).float())
+        g = w.abs().max() / (448.0 * 6.0)
+        blk = w.reshape(rows, cols // 16, 16)
+        s8 = (blk.abs().amax(-1) / 6.0 / g).float().to(torch.float8_e4m3fn)
+        sc = s8.float().double() * g
+        sc = torch.where(sc == 0, torch.ones_like(sc), sc).unsqueeze(-1)
+        nv = _e2m1_pack((blk / sc).reshape(rows, cols).float())
+        t = {"mx.blocks": mx, "mx.scales": e.contiguous(), "nv.weight": nv, "nv.weight_scale": s8.contiguous(), "nv.weight_scale_2": g.float().reshape(1)}
+        return t, {"mx.blocks": "fp4", "mx.scales": "scale", "nv.weight": "fp4", "nv.weight_scale": "scale", "nv.weight_scale_2": "global_scale"}
+    raise ValueError(which)
+
+
+_SLOT_NAMES_DECODE = ("rans", "huffman", "tans", "o1sac", "rans_fused", "huffman_fused", "tans_final", "o1sac_final")
+
+
+def measure_case(tensors, usage, cfg, device, peak, verify=False, reps=5, check=True):
+    """Encode `tensors` on the device, then decode the container from device memory `reps` times with the L2 flushed
+    before each, CUDA events around each pass; per-kernel times from separate passes.  Returns one extras entry."""
+    import ptwm_b200
+    from ptwm_b200.compressor import compress_model
+    local = device.index
+    raw = sum(t.numel() * t.element_size() for t in tensors.values())
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    enc = compress_model(tensors, cfg, usage=usage, device=local)
+    torch.cuda.synchronize()
+    encode_s = time.perf_counter() - t0
+    blob_dev = enc.to_tensor()
+    host = blob_dev.cpu()
+    codecs = enc.plane_codecs
+    size = enc.size
+    del enc
+    h = ptwm_b200.ContainerHandle(host, device=local, verify=verify)
+    plan = h.plan()
+    lo, hi = plan.blob_span
+    out = torch.empty(plan.out_bytes, dtype=torch.uint8, device=device)
+    scratch = torch.empty(max(plan.scratch_bytes, 1), dtype=torch.uint8, device=device)
+    flags = (ptwm_b200.VERIFY_CRC | ptwm_b200.VERIFY_HASH) if verify else 0
+    span = blob_dev[lo:hi]
+    plan.run(span, out, scratch, blob_first=lo, flags=flags)
+    if check:
+        for (name, t), v in zip(tensors.items(), plan.views(out)):
+            if not torch.equal(v.contiguous().view(torch.uint8).reshape(-1), t.contiguous().view(torch.uint8).reshape(-1)):
+                raise SystemExit(f"extras: decoded tensor {name} differs from the source")
+    times = []
+    for _ in range(2 + reps):
+        flush_l2(device)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        plan.run(span, out, scratch, blob_first=lo, flags=flags | ptwm_b200.NO_SYNC)
+        b.record()
+        plan.finish(local, flags)
+        times.append(a.elapsed_time(b))
+    ms = statistics.median(times[2:])
+    slot = {}
+    for _ in range(3):
+        flush_l2(device)
+        plan.run(span, out, scratch, blob_first=lo, flags=flags | ptwm_b200.TIME_KERNELS)
+        for name, (t, nbytes, items) in plan.timings(local).items():
+            slot.setdefault(name, ([], nbytes, items))[0].append(t)
+    kernels = {n: {"ms": round(statistics.median(v[0]), 4), "bytes": v[1], "items": v[2]} for n, v in slot.items()}
+    entry = {"raw_bytes": int(raw), "compressed_bytes": int(size), "ratio": round(size / max(raw, 1), 4), "ms": round(ms, 4), "value": raw / (ms * 1e-3) / 1e9,
+             "unit": "GB/s", "hbm_roofline_frac_whole_pass": (plan.bytes_read + raw) / (ms * 1e-3) / 1e9 / peak, "kernels": kernels,
+             "codecs": sorted({str(v) for v in codecs.values()}), "launches": plan.launches}
+    dec = {n: k for n, k in kernels.items() if n in _SLOT_NAMES_DECODE or n in ("merge", "crc32", "xxh64")}
+    if dec:
+        top = max(dec, key=lambda n: dec[n]["ms"])
+        ach = dec[top]["bytes"] / (dec[top]["ms"] * 1e-3) / 1e9 if dec[top]["ms"] > 0 else 0.0
+        entry["roofline"] = {"bound": "hbm", "kernel": top, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                             "algorithmic_bytes": dec[top]["bytes"], "ms": dec[top]["ms"]}
+    entry["encode"] = {"ms": round(encode_s * 1e3, 3), "value": raw / encode_s / 1e9, "unit": "GB/s",
+                       "roofline": {"bound": "hbm", "achieved": (raw + size) / encode_s / 1e9, "peak": peak, "unit": "GB/s", "frac": (raw + size) / encode_s / 1e9 / peak,
+                                    "what": "raw bytes read + container bytes written over the wall time of compress_model (split, histograms, tables, streams, CRC/hash when asked, gather)"}}
+    return entry
+
+
+def run_extras(shapes, device, args, peak):
+    """Bounded samples of what other writers produce and of the other configurations (one GPU only)."""
+    from ptwm_b200.compressor import HUFFMAN, IDENTITY, ORDER1_SCALE_AC, RANS, TANS, CompressionConfig
+    full = (IDENTITY, HUFFMAN, RANS, TANS, ORDER1_SCALE_AC)
+    layers = min(args.cpu_layers, LLAMA8B["layers"])
+    sample = {shapes[i][0]: make_tensor(i, shapes[i][1], shapes[i][2], device) for i in range(1, 1 + 9 * layers)}
+    what = f"first {layers} transformer layers of the headline state dict"
+    out = {}
+    cases = {
+        "verify": (dict(streaming_chunk=args.chunk, forced_codec=RANS, emit_plane_crc=True, emit_payload_hash=True), True, what + ", written with plane CRC-32s and XXH64 payload hashes, both checked on decode"),
+        "chunk_512k": (dict(streaming_chunk=512 << 10, forced_codec=RANS), False, what + ", 512 KiB chunks (the reference benchmark's own chunk size, benchmarks/decode_throughput.py:41-42)"),
+        "huffman": (dict(streaming_chunk=args.chunk, forced_codec=HUFFMAN), False, what + ", Huffman exponent planes"),
+        "tans_menu": (dict(streaming_chunk=args.chunk, forced_codec=TANS), False, what + ", tANS exponent planes (what the reference's trial encode picks for them)"),
+        "full_menu_64k": (dict(streaming_chunk=65536, codec_menu=full, emit_plane_crc=True), True, what + ", codec per plane from the full menu, 64 KiB chunks, plane CRCs checked"),
+    }
+    for name, (kw, verify, desc) in cases.items():
+        e = measure_case(sample, {}, CompressionConfig(**kw), device, peak, verify=verify)
+        e["sample"] = desc
+        out[name] = e
+    del sample
+    torch.cuda.empty_cache()
+    for which in ("config1", "config2_fp32", "config2_fp16", "config3", "config4"):
+        tensors, usage = config_tensors(which, device)
+        e = measure_case(tensors, usage, CompressionConfig(streaming_chunk=args.chunk, codec_menu=full), device, peak)
+        e["sample"] = f"{which}: shapes and value distributions of the reference's benchmark configuration, full codec menu, {args.chunk // 1024} KiB chunks"
+        out[which] = e
+        del tensors
+        torch.cuda.empty_cache()
+    out["l2"] = "a 256 MB buffer is overwritten before every timed pass (config1 and the scale planes are smaller than the 126 MB L2)"
+    return out
+
+
+def reference_wheel():
+    """The reference's own package, when one was installed under baseline/_ref (it cannot be built in this image: no Rust toolchain)."""
+    path = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(path):
+        return None
+    sys.path.insert(0, path)
+    try:
+        import ptwm  # noqa: F401
+        from ptwm import _rust
+        return _rust
+    except Exception:
+        return None
+    finally:
+        sys.path.remove(path)
+
+
 def run_reference(args):
     """The reference arm: the CPU restatement of ptwm-core's decode_model on the host cores (the Rust crate itself cannot be built in this image)."""
     rank = int(os.environ.get("RANK", "0"))
@@ -169,19 +356,32 @@ def run_reference(args):
         expect = b"".join(s.raw for s in specs)
         raw = len(expect)
         sample = "4 bf16 [1024,4096] tensors written by the oracle (no CUDA device for the product encoder)"
-    c = oracle.Container(blob)
-    n = len(c.tensors)
+    rust = reference_wheel()
+    kind = "port"
+    if rust is not None:  # the reference's own decoder, on the same bytes; its output also pins the port (and the device writer) against it
+        os.environ.setdefault("RAYON_NUM_THREADS", str(threads))
+        decoded = rust.decode_model(blob)
+        got = b"".join(bytes(v) for _, v in (decoded.items() if hasattr(decoded, "items") else decoded))
+        if got != expect:
+            raise SystemExit("the reference decoder and the source tensors disagree on the device-written container")
+        run = lambda: rust.decode_model(blob)  # noqa: E731
+        kind = "reference"
+        sample += f"; ptwm._rust.decode_model, RAYON_NUM_THREADS={os.environ['RAYON_NUM_THREADS']}"
+    else:
+        c = oracle.Container(blob)
+        n = len(c.tensors)
+        run = lambda: c.decode_range(0, n, threads=threads, verify=True)  # noqa: E731
     for _ in range(args.warmup):
-        c.decode_range(0, n, threads=threads, verify=True)
+        run()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        c.decode_range(0, n, threads=threads, verify=True)
+        run()
     dt = (time.perf_counter() - t0) / args.steps
     value = raw / dt / 1e9
     line = {"impl": "reference", "metric": "decoded_GB_per_s", "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
             "config": workload_config(args, raw_bytes=raw, compressed=len(blob)),
-            "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+            "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": kind, "sample": sample},
             "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     emit_json(line)
 
@@ -221,6 +421,7 @@ def run_ours(args):
     enc, raw_total, tensors = build_container(shapes, range(len(shapes)), device, args.chunk, args.codec, args.crc)
     compressed = enc.size
     codecs = enc.plane_codecs
+    encode_s = enc.encode_s
     host_blob = torch.empty(compressed, dtype=torch.uint8, pin_memory=True)
     blob_dev = enc.to_tensor()
     host_blob.copy_(blob_dev)
@@ -308,6 +509,29 @@ def run_ours(args):
         del decoded, h2
     e2e_s = statistics.mean(e2e_times)
 
+    # ---- replica mode (N > 1): every rank ends up with the whole model ------------------------------------------
+    replica = None
+    if world > 1:
+        from ptwm_b200.sharding import decode_replica
+        hr = ptwm_b200.ContainerHandle(host_blob, device=local, verify=bool(args.crc))
+        rep_times, nvlink = [], 0
+        for it in range(2 + min(args.steps, 5)):
+            barrier()
+            t0 = time.perf_counter()
+            decoded, nvlink = decode_replica(hr, None)
+            torch.cuda.synchronize()
+            dt = torch.tensor([time.perf_counter() - t0], device=device, dtype=torch.float64)
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+            if it >= 2:
+                rep_times.append(float(dt.item()))
+            n_rep = len(decoded)
+            del decoded
+        sec = statistics.mean(rep_times)
+        replica = {"value": raw_total / sec / 1e9, "unit": "GB/s per replica", "ms_per_step": sec * 1e3, "tensors_per_rank": n_rep,
+                   "nvlink_bytes_received_per_rank": int(nvlink), "h2d_bytes_per_rank": int(compressed - nvlink),
+                   "includes": "per rank: H2D of its span of the compressed container (1 / N of it), one NCCL broadcast per owner into place, one full local decode; container already parsed"}
+        del hr
+
     # ---- optional: the same container as a file (page cache warm) -> load_file --------------------------------
     file_load = None
     if args.file_dir and world == 1:
@@ -364,12 +588,23 @@ def run_ours(args):
                 "e2e": {"value": total_raw / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(total_h2d), "d2h_bytes_per_step": int(status_bytes * world),
                         "ms_per_step": e2e_s * 1e3,
                         "parts_ms": {"parse": 1e3 * statistics.mean(p[0] for p in e2e_parts), "plan_copy_decode": 1e3 * statistics.mean(p[1] for p in e2e_parts)},
-                        "pieces": args.pieces,
+                        "pieces": args.pieces, "h2d_GBps_per_rank": total_h2d / world / max(statistics.mean(p[1] for p in e2e_parts), 1e-9) / 1e9,
                         "includes": "ContainerHandle(pinned host bytes).decode_model_streamed: parse, per piece plan + H2D copy + decode + status read-back, the copies overlapping the rest (at one GPU the copy starts before the parse; at more a rank opens the container with shard=(rank, world) and reads only its own records)"},
                 "gpu_launches": int(total_launches) * args.steps, "setup_s": round(setup_s, 1),
                 "plane_codecs": sorted({str(v) for v in codecs.values()})}
+        if world == 1:
+            line["encode"] = {"value": raw_total / encode_s / 1e9, "unit": "GB/s", "ms": encode_s * 1e3,
+                              "roofline": {"bound": "hbm", "achieved": (raw_total + compressed) / encode_s / 1e9, "peak": peak, "unit": "GB/s",
+                                           "frac": (raw_total + compressed) / encode_s / 1e9 / peak},
+                              "what": "compress_model of the whole state dict in device memory (set-up of this run, one pass, wall time): raw bytes read + container bytes written"}
         if file_load:
             line["file_load"] = file_load
+        if replica:
+            line["replica_e2e"] = replica
+        if world == 1 and not args.no_extras and args.workload == "llama8b" and not args.layers:
+            del span_dev, out, scratch, plan, handle
+            torch.cuda.empty_cache()
+            line["extras"] = run_extras(shapes, device, args, peak)
         if args.workload != "llama8b":
             line["config"]["workload"] = "16 x bf16 [4096,4096] (profiling case)"
         if world == 1 and not args.no_cpu and args.workload == "llama8b":
@@ -409,6 +644,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer transformer layers than 32 (for quick checks; not the benchmark workload)")
     ap.add_argument("--cpu-layers", type=int, default=4, help="layers in the CPU baseline sample")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the extra cases (other writers' containers, configurations 1-4, encode)")
     ap.add_argument("--file-dir", default="", help="also write the container to a file in this directory and time ptwm_b200.load_file on it (extra key file_load; N=1 only)")
     ap.add_argument("--file-threads", type=int, default=16, help="reader threads of load_file")
     ap.add_argument("--no-check", action="store_true", help="skip the parity check (only for timing experimental kernel builds; never for a reported number)")

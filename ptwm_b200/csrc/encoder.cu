@@ -302,7 +302,7 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
         CUDA_TRY(upload_vec(d_hitems, hash_items, st));
         CUDA_TRY(d_hout.alloc(hash_items.size() * 8));
         Bases b{nullptr, 0, 0, nullptr, nullptr};
-        xxh64_kernel<<<uint32_t((hash_items.size() + 7) / 8), 32, 0, st>>>(d_hitems.as<HashItem>(), uint32_t(hash_items.size()), b, d_hout.as<uint64_t>());
+        xxh64_kernel<<<uint32_t(hash_items.size()), 32, 0, st>>>(d_hitems.as<HashItem>(), uint32_t(hash_items.size()), b, d_hout.as<uint64_t>());
         CUDA_TRY(cudaGetLastError());
         CUDA_TRY(cudaMemcpyAsync(hashes.data(), d_hout.p, hashes.size() * 8, cudaMemcpyDeviceToHost, st));
     }

@@ -1638,32 +1638,62 @@ __global__ void __launch_bounds__(128) crc_planes_kernel(const VerifyTensor* __r
     for (int p = 0; p < np; ++p) atomicXor(&acc[t.acc_base + p], gf2_mulmod(shift, c[p]));
 }
 
-// XXH64 (seed 0) of each tensor: the four accumulators of the stripe loop are
-// independent, so four lanes share a tensor; the rest is sequential by design
-// of the hash.
+// XXH64 (seed 0) of each tensor, one warp per tensor.  The hash is sequential by design: four accumulators, each
+// fed one 8-byte word of every 32-byte stripe through add, rotate and a 64-bit multiply, so four lanes carry the
+// state and a tensor cannot go faster than that dependent chain allows (about 2 GB/s).  What the rest of the warp
+// does is keep the chain fed: all 32 lanes fetch the next 4 KiB of the tensor with 128-bit loads while lanes 0-3 work
+// through the 128 stripes of the current block out of shared memory, so DRAM latency never shows.  Tensors hash
+// concurrently, one per block, and the host lists the largest first: the longest tensor is the critical path.
 __device__ __forceinline__ uint64_t rotl64(uint64_t x, int r) { return (x << r) | (x >> (64 - r)); }
 __device__ __forceinline__ uint64_t ld_u64_unaligned(const uint8_t* p) { return uint64_t(ld_u32_unaligned(p)) | uint64_t(ld_u32_unaligned(p + 4)) << 32; }
+constexpr uint32_t XXH_BLOCK = 4096;
 
 __global__ void __launch_bounds__(32) xxh64_kernel(const HashItem* __restrict__ items, uint32_t n_items, Bases bases, uint64_t* __restrict__ out) {
     const uint64_t P1 = 11400714785074694791ull, P2 = 14029467366897019727ull, P3 = 1609587929392839161ull, P4 = 9650029242287828579ull,
                    P5 = 2870177450012600261ull;
-    uint32_t lane = threadIdx.x, sub = lane & 3;
-    uint32_t idx = blockIdx.x * 8 + (lane >> 2);
-    bool valid = idx < n_items;
-    HashItem it = valid ? items[idx] : HashItem{0, 0};
-    const uint8_t* p = valid ? rd(bases, it.data) : nullptr;
-    uint64_t len = it.len;
-    uint64_t v = sub == 0 ? P1 + P2 : sub == 1 ? P2 : sub == 2 ? 0 : 0 - P1;
-    uint64_t stripes = len / 32;
-    const bool aligned = (reinterpret_cast<uintptr_t>(p) & 7) == 0;
-    for (uint64_t s = 0; s < stripes; ++s) {
-        const uint8_t* q = p + s * 32 + sub * 8;
-        uint64_t in = aligned ? *reinterpret_cast<const uint64_t*>(q) : ld_u64_unaligned(q);
-        v += in * P2; v = rotl64(v, 31); v *= P1;
+    __shared__ __align__(16) uint8_t stage[XXH_BLOCK];
+    const uint32_t lane = threadIdx.x, idx = blockIdx.x;
+    if (idx >= n_items) return;
+    const HashItem it = items[idx];
+    const uint8_t* p = rd(bases, it.data);
+    const uint64_t len = it.len, stripes = len / 32;
+    uint64_t v = lane == 0 ? P1 + P2 : lane == 1 ? P2 : lane == 2 ? 0 : 0 - P1;
+    uint64_t done = 0;  // stripes consumed
+    if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+        const uint64_t blocks = len / XXH_BLOCK;
+        uint4 nxt[8];
+        if (blocks) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) nxt[k] = __ldg(reinterpret_cast<const uint4*>(p) + k * 32 + lane);
+        }
+        for (uint64_t b = 0; b < blocks; ++b) {
+            __syncwarp();  // the previous block has been read
+#pragma unroll
+            for (int k = 0; k < 8; ++k) reinterpret_cast<uint4*>(stage)[k * 32 + lane] = nxt[k];
+            if (b + 1 < blocks) {
+                const uint4* q = reinterpret_cast<const uint4*>(p + (b + 1) * XXH_BLOCK);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) nxt[k] = __ldg(q + k * 32 + lane);
+            }
+            __syncwarp();
+            if (lane < 4) {
+                const uint64_t* w = reinterpret_cast<const uint64_t*>(stage) + lane;
+#pragma unroll 16
+                for (int st = 0; st < int(XXH_BLOCK / 32); ++st) { v += w[4 * st] * P2; v = rotl64(v, 31); v *= P1; }
+            }
+        }
+        done = blocks * (XXH_BLOCK / 32);
     }
-    uint64_t v1 = __shfl_sync(0xFFFFFFFFu, v, (lane & ~3u) + 0), v2 = __shfl_sync(0xFFFFFFFFu, v, (lane & ~3u) + 1),
-             v3 = __shfl_sync(0xFFFFFFFFu, v, (lane & ~3u) + 2), v4 = __shfl_sync(0xFFFFFFFFu, v, (lane & ~3u) + 3);
-    if (!valid || sub != 0) return;
+    if (lane < 4) {  // what is left of the stripes (all of them for a source that is not 16-byte aligned)
+        const bool aligned = (reinterpret_cast<uintptr_t>(p) & 7) == 0;
+        for (uint64_t st = done; st < stripes; ++st) {
+            const uint8_t* q = p + st * 32 + lane * 8;
+            const uint64_t in = aligned ? *reinterpret_cast<const uint64_t*>(q) : ld_u64_unaligned(q);
+            v += in * P2; v = rotl64(v, 31); v *= P1;
+        }
+    }
+    const uint64_t v1 = __shfl_sync(0xFFFFFFFFu, v, 0), v2 = __shfl_sync(0xFFFFFFFFu, v, 1), v3 = __shfl_sync(0xFFFFFFFFu, v, 2), v4 = __shfl_sync(0xFFFFFFFFu, v, 3);
+    if (lane != 0) return;
     auto round = [&](uint64_t acc, uint64_t in) { acc += in * P2; acc = rotl64(acc, 31); return acc * P1; };
     auto merge = [&](uint64_t h, uint64_t x) { x = round(0, x); h ^= x; return h * P1 + P4; };
     uint64_t h;

@@ -408,7 +408,7 @@ int64_t enqueue(ptwm_b200_plan& pl, DevicePlan& d, const Bases& bases, uint32_t 
     if ((flags & PTWM_B200_VERIFY_HASH) && !pl.hashes.empty()) {
         uint32_t n = uint32_t(pl.hashes.size());
         CUDA_TRY(mark(11, 0));
-        xxh64_kernel<<<(n + 7) / 8, 32, 0, st>>>(d.hashes, n, bases, d.hash_out);
+        xxh64_kernel<<<n, 32, 0, st>>>(d.hashes, n, bases, d.hash_out);
         CUDA_TRY(cudaGetLastError());
         CUDA_TRY(mark(11, 1));
     }
@@ -704,6 +704,14 @@ int64_t ptwm_b200_plan_create(const ptwm_b200_container* c, const uint32_t* indi
         }
         if (pl->blob_lo == UINT64_MAX) pl->blob_lo = pl->blob_hi = 0;
         pl->scratch_bytes = align_up(pl->scratch_bytes, 256);
+        {   // the payload hash of a tensor is one serial chain: the longest tensors start first, the longest one is the critical path
+            std::vector<size_t> order(pl->hashes.size());
+            for (size_t k = 0; k < order.size(); ++k) order[k] = k;
+            std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) { return pl->hashes[a].len > pl->hashes[b].len; });
+            std::vector<HashItem> hs; std::vector<HashExpect> he;
+            for (size_t k : order) { hs.push_back(pl->hashes[k]); he.push_back(pl->hash_expect[k]); }
+            pl->hashes.swap(hs); pl->hash_expect.swap(he);
+        }
         finish_lists(*pl);
         *out = pl.release();
         return 0;
