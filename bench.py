@@ -65,18 +65,18 @@ def make_tensor(name_index: int, shape, is_norm: bool, device) -> torch.Tensor:
     return x.to(torch.bfloat16)
 
 
-def build_container(shapes, indices, device, chunk: int, codec: str, crc: bool):
+def build_container(shapes, indices, device, chunk: int, codec: str, crc: bool, hash_: bool = False):
     """Encode the tensors `indices` of `shapes` on the device; returns (EncodedContainer, raw bytes)."""
     import ptwm_b200
-    from ptwm_b200.compressor import HUFFMAN, IDENTITY, RANS, CompressionConfig, compress_model
+    from ptwm_b200.compressor import HUFFMAN, IDENTITY, RANS, TANS, CompressionConfig, compress_model
     tensors = {}
     raw = 0
     for i in indices:
         name, shape, is_norm = shapes[i]
         tensors[name] = make_tensor(i, shape, is_norm, device)
         raw += tensors[name].numel() * 2
-    forced = {"rans": RANS, "huffman": HUFFMAN, "identity": IDENTITY, "auto": None}[codec]
-    cfg = CompressionConfig(streaming_chunk=chunk, forced_codec=forced, codec_menu=(IDENTITY, HUFFMAN, RANS), emit_plane_crc=crc, emit_payload_hash=False)
+    forced = {"rans": RANS, "huffman": HUFFMAN, "tans": TANS, "identity": IDENTITY, "auto": None}[codec]
+    cfg = CompressionConfig(streaming_chunk=chunk, forced_codec=forced, codec_menu=(IDENTITY, HUFFMAN, RANS), emit_plane_crc=crc, emit_payload_hash=hash_)
     torch.cuda.synchronize(device)
     t0 = time.perf_counter()
     enc = compress_model(tensors, cfg, device=device.index)
@@ -139,7 +139,7 @@ def cpu_sample(shapes, device, args, layers: int):
     """Container of the first `layers` transformer layers of the same state dict, as host bytes, plus the expected raw bytes."""
     per_layer = 9
     indices = list(range(1, 1 + per_layer * layers))
-    enc, raw, tensors = build_container(shapes, indices, device, args.chunk, args.codec, args.crc)
+    enc, raw, tensors = build_container(shapes, indices, device, args.chunk, args.codec, args.crc, args.hash)
     blob = enc.to_bytes()
     expect = b"".join(t.view(torch.uint8).cpu().numpy().tobytes() for t in tensors.values())
     del enc, tensors
@@ -389,7 +389,7 @@ def run_reference(args):
 def workload_config(args, raw_bytes, compressed):
     return {"workload": "llama3-8b-shape bf16 state dict, one PTWC container" if not args.layers else f"llama3-8b-shape bf16, {args.layers} layers",
             "raw_bytes": raw_bytes, "compressed_bytes": compressed, "ratio": round(compressed / max(raw_bytes, 1), 4), "chunk_bytes": args.chunk, "codec": args.codec,
-            "plane_crc": bool(args.crc), "payload_hash": False, "l2": "inputs and outputs far larger than the 126 MB L2 (no flush needed)",
+            "plane_crc": bool(args.crc), "payload_hash": bool(args.hash), "l2": "inputs and outputs far larger than the 126 MB L2 (no flush needed)",
             "parallelism": f"records split over {args.gpus} rank(s), no collective"}
 
 
@@ -418,7 +418,7 @@ def run_ours(args):
 
     # ---- set-up (untimed): synthesize, encode on the device, keep this rank's byte range ----
     t_setup = time.perf_counter()
-    enc, raw_total, tensors = build_container(shapes, range(len(shapes)), device, args.chunk, args.codec, args.crc)
+    enc, raw_total, tensors = build_container(shapes, range(len(shapes)), device, args.chunk, args.codec, args.crc, args.hash)
     compressed = enc.size
     codecs = enc.plane_codecs
     encode_s = enc.encode_s
@@ -426,7 +426,7 @@ def run_ours(args):
     blob_dev = enc.to_tensor()
     host_blob.copy_(blob_dev)
     del enc
-    handle = ptwm_b200.ContainerHandle(host_blob, device=local, verify=bool(args.crc))
+    handle = ptwm_b200.ContainerHandle(host_blob, device=local, verify=bool(args.crc or args.hash))
     infos = handle.tensor_infos()
     mine = shard_for_rank(infos, rank, world)
     plan = handle.plan(mine)
@@ -435,7 +435,7 @@ def run_ours(args):
     del blob_dev
     out = torch.empty(plan.out_bytes, dtype=torch.uint8, device=device)
     scratch = torch.empty(max(plan.scratch_bytes, 1), dtype=torch.uint8, device=device)
-    flags = ptwm_b200.VERIFY_CRC if args.crc else 0
+    flags = (ptwm_b200.VERIFY_CRC if args.crc else 0) | (ptwm_b200.VERIFY_HASH if args.hash else 0)
 
     # parity of this rank's tensors with the source tensors, once, before anything is timed
     plan.run(span_dev, out, scratch, blob_first=lo, flags=flags)
@@ -490,10 +490,10 @@ def run_ours(args):
         barrier()
         t0 = time.perf_counter()
         if world == 1:  # one rank needs every byte: start the copy before the parse
-            h2 = ptwm_b200.ContainerHandle(host_blob, device=local, verify=bool(args.crc), prefetch=True)
+            h2 = ptwm_b200.ContainerHandle(host_blob, device=local, verify=bool(args.crc or args.hash), prefetch=True)
             share = mine
         else:  # a rank reads only the records of its shard (a contiguous run cut by record bytes; the shards partition the container)
-            h2 = ptwm_b200.ContainerHandle(host_blob, device=local, verify=bool(args.crc), shard=(rank, world))
+            h2 = ptwm_b200.ContainerHandle(host_blob, device=local, verify=bool(args.crc or args.hash), shard=(rank, world))
             share = h2.shard_indices()
         t1 = time.perf_counter()
         decoded = h2.decode_model_streamed(indices=share, pieces=args.pieces)
@@ -513,7 +513,7 @@ def run_ours(args):
     replica = None
     if world > 1:
         from ptwm_b200.sharding import decode_replica
-        hr = ptwm_b200.ContainerHandle(host_blob, device=local, verify=bool(args.crc))
+        hr = ptwm_b200.ContainerHandle(host_blob, device=local, verify=bool(args.crc or args.hash))
         rep_times, nvlink = [], 0
         for it in range(2 + min(args.steps, 5)):
             barrier()
@@ -543,7 +543,7 @@ def run_ours(args):
             for it in range(args.warmup + args.steps):
                 torch.cuda.synchronize()
                 t0 = time.perf_counter()
-                state = ptwm_b200.load_file(path, local, pieces=8, verify=bool(args.crc), threads=args.file_threads, timings=info)
+                state = ptwm_b200.load_file(path, local, pieces=8, verify=bool(args.crc or args.hash), threads=args.file_threads, timings=info)
                 torch.cuda.synchronize()
                 if it >= args.warmup:
                     times.append(time.perf_counter() - t0)
@@ -638,8 +638,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--chunk", type=int, default=32768, help="plane bytes per chunk")
-    ap.add_argument("--codec", choices=["rans", "huffman", "auto", "identity"], default="rans")
+    ap.add_argument("--codec", choices=["rans", "huffman", "tans", "auto", "identity"], default="rans")
     ap.add_argument("--crc", action="store_true", help="write and verify plane CRC-32s")
+    ap.add_argument("--hash", action="store_true", help="write and verify XXH64 payload hashes (serial per tensor: the largest tensor bounds the pass)")
     ap.add_argument("--pieces", type=int, default=0, help="runs of tensors the end-to-end path decodes one after the other as their bytes arrive; 0 = 1 at one GPU, where the whole copy is started before the parse and a decode beside it only stretched the copy (213 ms with 1 piece, 219 with 4, 227 with 8), else 8")
     ap.add_argument("--layers", type=int, default=0, help="fewer transformer layers than 32 (for quick checks; not the benchmark workload)")
     ap.add_argument("--cpu-layers", type=int, default=4, help="layers in the CPU baseline sample")

@@ -1576,15 +1576,20 @@ __device__ __forceinline__ uint32_t terminal_bytes(uint32_t cur, uint32_t prev, 
     return r;
 }
 
+// The byte table is kept 32 times over in shared memory, entry i of lane l at word 32 i + l: a lookup never leaves
+// the lane's own bank, whatever the 32 indices of a warp are (one shared copy took 2.15 passes per lookup).  Tensor
+// bytes are read 16 at a time; a thread walks its own run, so every wider load saves that many single-sector requests.
 __global__ void __launch_bounds__(128) crc_planes_kernel(const VerifyTensor* __restrict__ tensors, uint32_t n_tensors, uint64_t n_runs, Bases bases,
                                                          const CrcTables* __restrict__ tabs, uint32_t* __restrict__ acc) {
-    __shared__ uint32_t T[256];
+    __shared__ uint32_t T32[256 * 32];
     __shared__ uint32_t X[64];
-    for (uint32_t i = threadIdx.x; i < 256; i += blockDim.x) T[i] = tabs->byte_table[i];
+    for (uint32_t i = threadIdx.x; i < 256 * 32; i += blockDim.x) T32[i] = tabs->byte_table[i >> 5];
     if (threadIdx.x < 64) X[threadIdx.x] = tabs->x2n[threadIdx.x];
     __syncthreads();
     uint64_t run = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (run >= n_runs) return;
+    const uint32_t* T = T32 + (threadIdx.x & 31);
+    auto step = [&](uint32_t crc, uint32_t byte) { return T[((crc ^ byte) & 0xFFu) << 5] ^ (crc >> 8); };
     uint32_t lo = 0, hi = n_tensors;
     while (lo + 1 < hi) { uint32_t mid = (lo + hi) >> 1; if (tensors[mid].first_run <= run) lo = mid; else hi = mid; }
     const VerifyTensor t = tensors[lo];
@@ -1592,46 +1597,98 @@ __global__ void __launch_bounds__(128) crc_planes_kernel(const VerifyTensor* __r
     uint32_t n = t.n_elems - first < VERIFY_RUN ? uint32_t(t.n_elems - first) : VERIFY_RUN;
     const uint8_t* out = rd(bases, t.out);
     uint32_t c[4] = {0, 0, 0, 0};
+    const bool wide = !t.post && (reinterpret_cast<uintptr_t>(out + first * uint64_t(kind_elem_bytes(int(t.kind)))) & 15) == 0;
     switch (t.kind) {
-        case K_PASS:
-            for (uint32_t i = 0; i < n; ++i) c[0] = T[(c[0] ^ out[first + i]) & 0xFF] ^ (c[0] >> 8);
+        case K_PASS: {
+            uint32_t i = 0;
+            if (wide) {
+                const uint4* q = reinterpret_cast<const uint4*>(out + first);
+                for (; i + 16 <= n; i += 16) {
+                    const uint4 v = __ldg(q++);
+                    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) c[0] = step(c[0], w[k >> 2] >> (8 * (k & 3)));
+                }
+            }
+            for (; i < n; ++i) c[0] = step(c[0], out[first + i]);
             break;
+        }
         case K_M16: {
             auto planes_of = [&](uint64_t e) {
                 uint32_t v = uint32_t(out[2 * e]) | uint32_t(out[2 * e + 1]) << 8;
                 return ((v << 1) & 0xFF00u) | ((v >> 8) & 0x0080u) | (v & 0x007Fu);
             };
+            uint32_t i = 0;
+            if (wide) {
+                const uint4* q = reinterpret_cast<const uint4*>(out + first * 2);
+                for (; i + 8 <= n; i += 8) {
+                    const uint4 v = __ldg(q++);
+                    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {  // two elements per word: the forward reorder of split/dtype16.rs:11-18 on both halves
+                        const uint32_t r = ((w[k] << 1) & 0xFF00FF00u) | ((w[k] >> 8) & 0x00800080u) | (w[k] & 0x007F007Fu);
+                        c[0] = step(c[0], r); c[1] = step(c[1], r >> 8);
+                        c[0] = step(c[0], r >> 16); c[1] = step(c[1], r >> 24);
+                    }
+                }
+            }
             uint32_t prev = (t.post && first) ? planes_of(first - 1) : 0u;
-            for (uint32_t i = 0; i < n; ++i) {
+            for (; i < n; ++i) {
                 uint32_t r = planes_of(first + i);
                 if (t.post) { uint32_t cur = r; r = terminal_bytes(r, prev, t.post, t.post_k, 2); prev = cur; }
-                c[0] = T[(c[0] ^ r) & 0xFF] ^ (c[0] >> 8);
-                c[1] = T[(c[1] ^ (r >> 8)) & 0xFF] ^ (c[1] >> 8);
+                c[0] = step(c[0], r);
+                c[1] = step(c[1], r >> 8);
             }
             break;
         }
         case K_M32: {
-            auto planes_of = [&](uint64_t e) {
-                uint32_t v = ld_u32_unaligned(out + 4 * e);
-                return ((v << 1) & 0xFF000000u) | ((v >> 8) & 0x00800000u) | (v & 0x007FFFFFu);
-            };
+            auto reorder = [](uint32_t v) { return ((v << 1) & 0xFF000000u) | ((v >> 8) & 0x00800000u) | (v & 0x007FFFFFu); };
+            auto planes_of = [&](uint64_t e) { return reorder(ld_u32_unaligned(out + 4 * e)); };
+            uint32_t i = 0;
+            if (wide) {
+                const uint4* q = reinterpret_cast<const uint4*>(out + first * 4);
+                for (; i + 4 <= n; i += 4) {
+                    const uint4 v = __ldg(q++);
+                    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint32_t r = reorder(w[k]);
+#pragma unroll
+                        for (int p = 0; p < 4; ++p) c[p] = step(c[p], r >> (8 * p));
+                    }
+                }
+            }
             uint32_t prev = (t.post && first) ? planes_of(first - 1) : 0u;
-            for (uint32_t i = 0; i < n; ++i) {
+            for (; i < n; ++i) {
                 uint32_t r = planes_of(first + i);
                 if (t.post) { uint32_t cur = r; r = terminal_bytes(r, prev, t.post, t.post_k, 4); prev = cur; }
 #pragma unroll
-                for (int p = 0; p < 4; ++p) c[p] = T[(c[p] ^ (r >> (8 * p))) & 0xFF] ^ (c[p] >> 8);
+                for (int p = 0; p < 4; ++p) c[p] = step(c[p], r >> (8 * p));
             }
             break;
         }
-        default:
-            for (uint32_t i = 0; i < n; ++i) {
-                uint32_t v = out[first + i];
-                uint32_t r = t.kind == K_E4M3 ? (((v & 0x78) << 1) | ((v & 0x80) >> 4) | (v & 0x07)) : (((v & 0x7C) << 1) | ((v & 0x80) >> 5) | (v & 0x03));
-                c[0] = T[(c[0] ^ (r >> 4)) & 0xFF] ^ (c[0] >> 8);
-                c[1] = T[(c[1] ^ (r & 0x0F)) & 0xFF] ^ (c[1] >> 8);
+        default: {
+            auto nibbles = [&](uint32_t v) { return t.kind == K_E4M3 ? (((v & 0x78) << 1) | ((v & 0x80) >> 4) | (v & 0x07)) : (((v & 0x7C) << 1) | ((v & 0x80) >> 5) | (v & 0x03)); };
+            uint32_t i = 0;
+            if (wide) {
+                const uint4* q = reinterpret_cast<const uint4*>(out + first);
+                for (; i + 16 <= n; i += 16) {
+                    const uint4 v = __ldg(q++);
+                    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) {
+                        const uint32_t r = nibbles((w[k >> 2] >> (8 * (k & 3))) & 0xFFu);
+                        c[0] = step(c[0], r >> 4); c[1] = step(c[1], r & 0x0F);
+                    }
+                }
+            }
+            for (; i < n; ++i) {
+                const uint32_t r = nibbles(out[first + i]);
+                c[0] = step(c[0], r >> 4);
+                c[1] = step(c[1], r & 0x0F);
             }
             break;
+        }
     }
     uint32_t shift = x_pow_8n(X, t.n_elems - first - n);
     int np = kind_planes(int(t.kind));
@@ -1640,9 +1697,10 @@ __global__ void __launch_bounds__(128) crc_planes_kernel(const VerifyTensor* __r
 
 // XXH64 (seed 0) of each tensor, one warp per tensor.  The hash is sequential by design: four accumulators, each
 // fed one 8-byte word of every 32-byte stripe through add, rotate and a 64-bit multiply, so four lanes carry the
-// state and a tensor cannot go faster than that dependent chain allows (about 2 GB/s).  What the rest of the warp
-// does is keep the chain fed: all 32 lanes fetch the next 4 KiB of the tensor with 128-bit loads while lanes 0-3 work
-// through the 128 stripes of the current block out of shared memory, so DRAM latency never shows.  Tensors hash
+// state and a tensor cannot go faster than that dependent chain allows (add, rotate, one 64-bit multiply per 32
+// bytes).  What the rest of the warp does is keep the chain short and fed: all 32 lanes fetch the next 4 KiB of the
+// tensor with 128-bit loads and multiply the current block's words by the second prime, while lanes 0-3 work through
+// the 128 stripes of the current block out of shared memory, so neither DRAM latency nor that multiply shows.  Tensors hash
 // concurrently, one per block, and the host lists the largest first: the longest tensor is the critical path.
 __device__ __forceinline__ uint64_t rotl64(uint64_t x, int r) { return (x << r) | (x >> (64 - r)); }
 __device__ __forceinline__ uint64_t ld_u64_unaligned(const uint8_t* p) { return uint64_t(ld_u32_unaligned(p)) | uint64_t(ld_u32_unaligned(p + 4)) << 32; }
@@ -1676,10 +1734,16 @@ __global__ void __launch_bounds__(32) xxh64_kernel(const HashItem* __restrict__ 
                 for (int k = 0; k < 8; ++k) nxt[k] = __ldg(q + k * 32 + lane);
             }
             __syncwarp();
+            {   // the products word * P2 do not depend on the accumulators: all lanes take them off the serial chain
+                uint64_t* w = reinterpret_cast<uint64_t*>(stage);
+#pragma unroll
+                for (int k = 0; k < int(XXH_BLOCK / 8 / 32); ++k) w[k * 32 + lane] *= P2;
+            }
+            __syncwarp();
             if (lane < 4) {
                 const uint64_t* w = reinterpret_cast<const uint64_t*>(stage) + lane;
 #pragma unroll 16
-                for (int st = 0; st < int(XXH_BLOCK / 32); ++st) { v += w[4 * st] * P2; v = rotl64(v, 31); v *= P1; }
+                for (int st = 0; st < int(XXH_BLOCK / 32); ++st) { v += w[4 * st]; v = rotl64(v, 31); v *= P1; }
             }
         }
         done = blocks * (XXH_BLOCK / 32);
