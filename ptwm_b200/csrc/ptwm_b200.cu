@@ -694,13 +694,17 @@ int64_t ptwm_b200_plan_create(const ptwm_b200_container* c, const uint32_t* indi
                 VerifyTensor v{make_ref(SP_OUT, off), t.planes[0].decoded_len, pl->n_runs, t.kind, pl->n_acc, 0, 0};
                 for (size_t p = 0; p < t.planes.size() && p < 4; ++p) { v.post |= uint32_t(t.planes[p].post) << (8 * p); v.post_k |= uint32_t(t.planes[p].post_k) << (8 * p); }
                 pl->n_runs += (v.n_elems + VERIFY_RUN - 1) / VERIFY_RUN;
+                pl->slot_bytes[10] += t.orig_size; pl->slot_items[10]++;  // the check reads the decoded tensor once
                 for (size_t p = 0; p < t.planes.size(); ++p) if (t.planes[p].has_crc) pl->crc_expect.push_back({pl->n_acc + uint32_t(p), t.planes[p].crc, t.planes[p].decoded_len, ti});
                 pl->n_acc += uint32_t(t.planes.size());
                 pl->verify.push_back(v);
             } else if (any_crc) {
                 for (const PlaneDesc& p : t.planes) if (p.has_crc && p.crc != 0) return fail(PTWM_RC_CORRUPT, "tensor '" + t.name + "': plane CRC mismatch");
             }
-            if (t.has_hash) { pl->hashes.push_back(HashItem{make_ref(SP_OUT, off), t.orig_size}); pl->hash_expect.push_back({t.hash, ti}); }
+            if (t.has_hash) {
+                pl->hashes.push_back(HashItem{make_ref(SP_OUT, off), t.orig_size}); pl->hash_expect.push_back({t.hash, ti});
+                pl->slot_bytes[11] += t.orig_size; pl->slot_items[11]++;
+            }
         }
         if (pl->blob_lo == UINT64_MAX) pl->blob_lo = pl->blob_hi = 0;
         pl->scratch_bytes = align_up(pl->scratch_bytes, 256);
