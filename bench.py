@@ -411,7 +411,7 @@ def run_ours(args):
         cfg["layers"] = args.layers
     shapes = model_shapes(**cfg)
     if not args.pieces:
-        args.pieces = 1 if world == 1 else 8
+        args.pieces = 8
     if args.workload == "c1x16":  # profiling-sized stand-in: sixteen bf16 [4096,4096] tensors (0.54 GB), same recipe
         shapes = [(f"w{i}.weight", (4096, 4096), False) for i in range(16)]
         cfg["layers"] = 0
@@ -641,7 +641,7 @@ def main():
     ap.add_argument("--codec", choices=["rans", "huffman", "tans", "auto", "identity"], default="rans")
     ap.add_argument("--crc", action="store_true", help="write and verify plane CRC-32s")
     ap.add_argument("--hash", action="store_true", help="write and verify XXH64 payload hashes (serial per tensor: the largest tensor bounds the pass)")
-    ap.add_argument("--pieces", type=int, default=0, help="runs of tensors the end-to-end path decodes one after the other as their bytes arrive; 0 = 1 at one GPU, where the whole copy is started before the parse and a decode beside it only stretched the copy (213 ms with 1 piece, 219 with 4, 227 with 8), else 8")
+    ap.add_argument("--pieces", type=int, default=0, help="runs of tensors the end-to-end path decodes one after the other as their bytes arrive (0 = 8): all but the last run decode while later bytes are still crossing PCIe")
     ap.add_argument("--layers", type=int, default=0, help="fewer transformer layers than 32 (for quick checks; not the benchmark workload)")
     ap.add_argument("--cpu-layers", type=int, default=4, help="layers in the CPU baseline sample")
     ap.add_argument("--no-cpu", action="store_true")

@@ -166,6 +166,14 @@ int64_t ptwm_b200_plan_run(ptwm_b200_plan* p, uint64_t blob_dev_ptr, uint64_t bl
  * ptwm_b200_plan_run.  The copies are synchronous: a pipeline that enqueues large
  * transfers prepares its plans first, so that no run waits behind them. */
 int64_t ptwm_b200_plan_prepare(ptwm_b200_plan* p, uint32_t device_ordinal);
+/* The same with the plan's device memory (work lists, status words) supplied by the caller:
+ * ptwm_b200_plan_device_bytes bytes at a 256-byte aligned address, which must outlive the plan's
+ * runs on that device.  Neither call allocates device memory then (cudaMalloc may wait for queued
+ * transfers; a loader that prepares plans beside a streaming copy takes the memory from its own pool).
+ * The lists reach the device through a kernel reading pinned host memory, not through the copy
+ * engine, so preparing a plan does not wait behind transfers that are already queued. */
+uint64_t ptwm_b200_plan_device_bytes(const ptwm_b200_plan* p);
+int64_t ptwm_b200_plan_prepare_in(ptwm_b200_plan* p, uint32_t device_ordinal, uint64_t dev_ptr, uint64_t cap);
 int64_t ptwm_b200_plan_finish(ptwm_b200_plan* p, uint32_t flags, uint32_t device_ordinal, uint64_t stream);
 
 

@@ -80,6 +80,8 @@ _SIGNATURES = {
                                        C.c_uint32, C.c_uint64]),
     "ptwm_b200_plan_finish": (C.c_int64, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint64]),
     "ptwm_b200_plan_prepare": (C.c_int64, [C.c_void_p, C.c_uint32]),
+    "ptwm_b200_plan_device_bytes": (C.c_uint64, [C.c_void_p]),
+    "ptwm_b200_plan_prepare_in": (C.c_int64, [C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint64]),
     "ptwm_b200_plan_timings": (C.c_int64, [C.c_void_p, C.c_uint32, C.POINTER(C.c_float), C.POINTER(C.c_uint64), C.POINTER(C.c_uint32)]),
     "ptwm_b200_decode_plane_noalloc": (C.c_int64, [C.c_uint8, C.c_void_p, C.c_size_t, C.c_char_p, C.c_size_t, C.c_uint64, C.c_size_t, C.c_uint64,
                                                    C.c_size_t, C.c_uint32, C.c_uint64]),

@@ -95,6 +95,7 @@ class DecodePlan:
         if getattr(self, "_p", None):
             _lib.lib().ptwm_b200_plan_destroy(self._p)
             self._p = None
+        self._dev_mem = None  # after the plan: its runs are over
 
     def run(self, blob_dev: torch.Tensor, out: torch.Tensor, scratch: Optional[torch.Tensor], *, blob_first: int = 0, flags: int = 0,
             stream: Optional[int] = None) -> None:
@@ -109,8 +110,14 @@ class DecodePlan:
                                              out.data_ptr() if out.numel() else 0, out.numel(), sp, sc, flags, dev, stream))
 
     def prepare(self, device: int) -> None:
-        """Send the work lists to the device now rather than in the first run."""
-        _check(_lib.lib().ptwm_b200_plan_prepare(self._p, device))
+        """Send the work lists to the device now rather than in the first run.  Their device memory comes from
+        torch's allocator (no cudaMalloc, which may wait for transfers that are already queued) and lives as long as the plan."""
+        L = _lib.lib()
+        if getattr(self, "_dev_mem", None) is None:
+            self._dev_mem = torch.empty(int(L.ptwm_b200_plan_device_bytes(self._p)), dtype=torch.uint8, device=torch.device("cuda", device))
+            _check(L.ptwm_b200_plan_prepare_in(self._p, device, self._dev_mem.data_ptr(), self._dev_mem.numel()))
+        else:
+            _check(L.ptwm_b200_plan_prepare(self._p, device))
 
     def finish(self, device: int, flags: int = 0, stream: Optional[int] = None) -> None:
         if stream is None:

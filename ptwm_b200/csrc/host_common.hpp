@@ -33,6 +33,8 @@ struct DeviceState {
     cudaStream_t stream = nullptr;   // the library's process-persistent stream for the device
     CrcTables* d_tabs = nullptr;     // CRC byte table and x^(2^k) powers
     bool attrs = false;
+    void* stage = nullptr;           // pinned host buffer the plan work lists pass through on their way to the device
+    size_t stage_cap = 0;
 };
 
 // Caller holds a DeviceGuard for `dev`.

@@ -1775,4 +1775,10 @@ __global__ void __launch_bounds__(32) xxh64_kernel(const HashItem* __restrict__ 
     out[idx] = h;
 }
 
+// Copies 16-byte words; the host side uses it to bring a plan's work lists from pinned host memory to the device
+// without queueing behind the copy engine's transfers.
+__global__ void __launch_bounds__(256) stage_in_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t n16) {
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n16; i += size_t(gridDim.x) * blockDim.x) dst[i] = src[i];
+}
+
 }  // namespace ptwm

@@ -2,6 +2,7 @@
 // into kernel work lists, the runner that launches them, and the C ABI
 // declared in include/ptwm_b200.h.
 #include <algorithm>
+#include <cstring>
 #include <map>
 #include <memory>
 #include <mutex>
@@ -87,9 +88,11 @@ struct DevicePlan {
     uint64_t* hash_out = nullptr;
     cudaEvent_t ev[24] = {nullptr};   // begin/end per launch slot, created on first timed run
     bool timed[12] = {false};
+    uint8_t* arena = nullptr;          // everything above lives in this one block
+    bool external = false;             // the block belongs to the caller (ptwm_b200_plan_prepare_in)
     void release() {
         for (auto& e : ev) if (e) cudaEventDestroy(e);
-        cudaFree(items); cudaFree(merges); cudaFree(tiles); cudaFree(posts); cudaFree(post_tiles); cudaFree(verify); cudaFree(hashes); cudaFree(status); cudaFree(acc); cudaFree(hash_out);
+        if (!external) cudaFree(arena);
         *this = DevicePlan{};
     }
 };
@@ -293,34 +296,72 @@ void finish_lists(ptwm_b200_plan& pl) {
     if (!pl.posts.empty()) pl.launches += delta ? 3 : 1;
 }
 
+// A plan's work lists reach the device through a kernel that reads them out of pinned host memory, not through a
+// host-to-device copy: a caller that streams a container to the GPU has tens of large copies queued on the copy
+// engine, and a small copy issued now would only run after all of them (the plan of the first piece would be ready
+// when the last byte of the container has arrived).  The kernel runs on the library's stream beside those copies.
+std::mutex g_stage_mu;  // one staging buffer per device, used under this lock
 template <class T>
-int64_t upload(T** dst, const std::vector<T>& v) {
+int64_t upload(T* dst, const std::vector<T>& v, DeviceState& ds) {
     if (v.empty()) return 0;
-    CUDA_TRY(cudaMalloc(dst, v.size() * sizeof(T)));
-    CUDA_TRY(cudaMemcpy(*dst, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice));
+    const size_t bytes = v.size() * sizeof(T), padded = (bytes + 15) & ~size_t(15);
+    std::lock_guard<std::mutex> g(g_stage_mu);
+    if (ds.stage_cap < padded) {  // grows only on the first large plan of a process: pinning synchronises with the device
+        if (ds.stage) CUDA_TRY(cudaFreeHost(ds.stage));
+        ds.stage = nullptr; ds.stage_cap = 0;
+        const size_t cap = std::max<size_t>(padded + padded / 2, size_t(32) << 20);
+        CUDA_TRY(cudaMallocHost(&ds.stage, cap));
+        ds.stage_cap = cap;
+    }
+    std::memcpy(ds.stage, v.data(), bytes);
+    const size_t n16 = padded / 16;
+    stage_in_kernel<<<unsigned(std::min<size_t>((n16 + 255) / 256, 1184)), 256, 0, ds.stream>>>(static_cast<const uint4*>(ds.stage), reinterpret_cast<uint4*>(dst), n16);
+    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(cudaStreamSynchronize(ds.stream));  // the staging buffer is free again, and the list is in place before any launch that uses it
     return 0;
 }
 
-// Caller holds the plan mutex and a DeviceGuard.
-int64_t device_plan(ptwm_b200_plan& pl, int dev, DevicePlan** out) {
+// Device bytes a plan needs for its work lists and status arrays, each part on a 256-byte boundary.
+struct PlanLayout { uint64_t off[10]; uint64_t total; };
+PlanLayout plan_layout(const ptwm_b200_plan& pl) {
+    size_t n_items = 0, n_merges = 0, n_tiles = 0;
+    for (int ph = 0; ph < 2; ++ph) { for (int cc = 0; cc < 4; ++cc) n_items += pl.dec[ph][cc].size(); n_merges += pl.merges[ph].size(); n_tiles += pl.tiles[ph].size(); }
+    const uint64_t sizes[10] = {n_items * sizeof(DecodeItem), n_merges * sizeof(MergeItem), n_tiles * 4, pl.posts.size() * sizeof(PostItem), pl.post_tiles.size() * 4,
+                                pl.verify.size() * sizeof(VerifyTensor), pl.hashes.size() * sizeof(HashItem), (pl.item_tensor.size() + 1) * 4, (uint64_t(pl.n_acc) + 1) * 4,
+                                (pl.hashes.size() + 1) * 8};
+    PlanLayout L{};
+    uint64_t at = 0;
+    for (int k = 0; k < 10; ++k) { L.off[k] = at; at += align_up(sizes[k], 256); }
+    L.total = at ? at : 256;
+    return L;
+}
+
+// Caller holds the plan mutex and a DeviceGuard.  `mem` / `cap`: device memory of the caller to build the plan in, or null.
+int64_t device_plan(ptwm_b200_plan& pl, int dev, DeviceState& ds, DevicePlan** out, uint8_t* mem = nullptr, uint64_t cap = 0) {
     auto found = pl.dev.find(dev);
     if (found != pl.dev.end()) { *out = &found->second; return 0; }
     DevicePlan d;
+    const PlanLayout L = plan_layout(pl);
+    if (mem) {
+        if (cap < L.total || (reinterpret_cast<uintptr_t>(mem) & 255)) return fail(PTWM_RC_BUFFER_TOO_SMALL, "plan memory smaller than ptwm_b200_plan_device_bytes or not 256-byte aligned");
+        d.arena = mem; d.external = true;
+    } else {
+        CUDA_TRY(cudaMalloc(&d.arena, L.total));
+    }
+    d.items = reinterpret_cast<DecodeItem*>(d.arena + L.off[0]); d.merges = reinterpret_cast<MergeItem*>(d.arena + L.off[1]);
+    d.tiles = reinterpret_cast<uint32_t*>(d.arena + L.off[2]); d.posts = reinterpret_cast<PostItem*>(d.arena + L.off[3]);
+    d.post_tiles = reinterpret_cast<uint32_t*>(d.arena + L.off[4]); d.verify = reinterpret_cast<VerifyTensor*>(d.arena + L.off[5]);
+    d.hashes = reinterpret_cast<HashItem*>(d.arena + L.off[6]); d.status = reinterpret_cast<uint32_t*>(d.arena + L.off[7]);
+    d.acc = reinterpret_cast<uint32_t*>(d.arena + L.off[8]); d.hash_out = reinterpret_cast<uint64_t*>(d.arena + L.off[9]);
     std::vector<DecodeItem> all;
     for (int ph = 0; ph < 2; ++ph) for (int cc = 0; cc < 4; ++cc) all.insert(all.end(), pl.dec[ph][cc].begin(), pl.dec[ph][cc].end());
     std::vector<MergeItem> allm;
     std::vector<uint32_t> allt;
     for (int ph = 0; ph < 2; ++ph) { allm.insert(allm.end(), pl.merges[ph].begin(), pl.merges[ph].end()); allt.insert(allt.end(), pl.tiles[ph].begin(), pl.tiles[ph].end()); }
     int64_t rc;
-    if ((rc = upload(&d.items, all)) < 0 || (rc = upload(&d.merges, allm)) < 0 || (rc = upload(&d.tiles, allt)) < 0 || (rc = upload(&d.posts, pl.posts)) < 0 || (rc = upload(&d.post_tiles, pl.post_tiles)) < 0 ||
-        (rc = upload(&d.verify, pl.verify)) < 0 ||
-        (rc = upload(&d.hashes, pl.hashes)) < 0) { d.release(); return rc; }
-    cudaError_t e;
-    if ((e = cudaMalloc(&d.status, (pl.item_tensor.size() + 1) * sizeof(uint32_t))) != cudaSuccess || (e = cudaMalloc(&d.acc, (pl.n_acc + 1) * sizeof(uint32_t))) != cudaSuccess ||
-        (e = cudaMalloc(&d.hash_out, (pl.hashes.size() + 1) * sizeof(uint64_t))) != cudaSuccess) {
-        d.release();  // the lists already uploaded
-        return fail(PTWM_RC_CUDA, std::string("cudaMalloc of the plan's status arrays: ") + cudaGetErrorString(e));
-    }
+    if ((rc = upload(d.items, all, ds)) < 0 || (rc = upload(d.merges, allm, ds)) < 0 || (rc = upload(d.tiles, allt, ds)) < 0 || (rc = upload(d.posts, pl.posts, ds)) < 0 ||
+        (rc = upload(d.post_tiles, pl.post_tiles, ds)) < 0 || (rc = upload(d.verify, pl.verify, ds)) < 0 ||
+        (rc = upload(d.hashes, pl.hashes, ds)) < 0) { d.release(); return rc; }
     pl.dev[dev] = d;
     *out = &pl.dev[dev];
     return 0;
@@ -743,7 +784,7 @@ int64_t ptwm_b200_plan_run(ptwm_b200_plan* p, uint64_t blob_dev_ptr, uint64_t bl
     cudaStream_t st = stream ? reinterpret_cast<cudaStream_t>(uintptr_t(stream)) : ds->stream;
     std::lock_guard<std::mutex> lock(p->mu);
     DevicePlan* d;
-    if ((rc = device_plan(*p, int(device_ordinal), &d)) < 0) return rc;
+    if ((rc = device_plan(*p, int(device_ordinal), *ds, &d)) < 0) return rc;
     // Refs hold file offsets; the kernels clamp their 16-byte fetches to the resident span
     Bases launch{reinterpret_cast<const uint8_t*>(uintptr_t(blob_dev_ptr)), blob_first, blob_first + blob_len, reinterpret_cast<uint8_t*>(uintptr_t(scratch_dev_ptr)),
                  reinterpret_cast<uint8_t*>(uintptr_t(out_dev_ptr))};
@@ -761,7 +802,21 @@ int64_t ptwm_b200_plan_prepare(ptwm_b200_plan* p, uint32_t device_ordinal) {
     if (rc < 0) return rc;
     std::lock_guard<std::mutex> lock(p->mu);
     DevicePlan* d;
-    return device_plan(*p, int(device_ordinal), &d);
+    return device_plan(*p, int(device_ordinal), *ds, &d);
+}
+
+uint64_t ptwm_b200_plan_device_bytes(const ptwm_b200_plan* p) { return p ? plan_layout(*p).total : 0; }
+int64_t ptwm_b200_plan_prepare_in(ptwm_b200_plan* p, uint32_t device_ordinal, uint64_t dev_ptr, uint64_t cap) {
+    if (!p || !dev_ptr) return fail(PTWM_RC_INVALID_INPUT, "null plan or memory");
+    DeviceGuard guard{int(device_ordinal)};
+    if (guard.err != cudaSuccess) return fail(PTWM_RC_CUDA, std::string("cudaSetDevice: ") + cudaGetErrorString(guard.err));
+    DeviceState* ds;
+    int64_t rc = device_state(int(device_ordinal), &ds);
+    if (rc < 0) return rc;
+    std::lock_guard<std::mutex> lock(p->mu);
+    if (p->dev.count(int(device_ordinal))) return fail(PTWM_RC_INVALID_INPUT, "the plan is already prepared on this device");
+    DevicePlan* d;
+    return device_plan(*p, int(device_ordinal), *ds, &d, reinterpret_cast<uint8_t*>(uintptr_t(dev_ptr)), cap);
 }
 
 int64_t ptwm_b200_plan_finish(ptwm_b200_plan* p, uint32_t flags, uint32_t device_ordinal, uint64_t stream) {
