@@ -189,6 +189,12 @@ typedef struct ptwm_b200_encode_tensor {
     uint8_t ndim;
     uint8_t usage;           /* 0 standard, 1 block scale (E4M3 / E8M0), 2 fp32 global scale, 3 packed fp4 values:
                                 which production chain the tensor gets (python/ptwm/preprocessing/_chains.py:320-357,610-727) */
+    uint8_t post_op;         /* one more op between the byte split and one of its terminals (16- and 32-bit float tensors):
+                                0 none (or chosen per PTWM_B200_TRY_*), 1 IntDelta, 2 MantissaZeroStrip(post_k)
+                                (_chains.py:360-389,486-560) */
+    uint8_t post_plane;      /* the plane the op goes on: the exponent plane for IntDelta, mantissa plane 0 for MantissaZeroStrip */
+    uint8_t post_k;          /* MantissaZeroStrip: bits stripped, 1..7 */
+    uint8_t reserved_;
 } ptwm_b200_encode_tensor;
 
 #define PTWM_B200_MENU_IDENTITY 1u
@@ -204,8 +210,13 @@ typedef struct ptwm_b200_encode_options {
     int32_t forced_codec;    /* codec wire id to force on every plane (CompressorOptions.forced_codec), -1 = select */
     uint8_t emit_plane_crc;  /* CompressorOptions.emit_plane_crc */
     uint8_t emit_payload_hash; /* CompressorOptions.emit_payload_hash */
-    uint8_t reserved[2];
+    uint8_t candidates;      /* PTWM_B200_TRY_* bits: candidate chains tried beside the plain split for every 16- / 32-bit float tensor
+                                without an explicit post_op; the chain with the smallest total wins, the first in the reference's
+                                order on ties (pass1_select_chain, compressor.rs:504-665; candidates of _chains.py:1151-1185) */
+    uint8_t reserved[1];
 } ptwm_b200_encode_options;
+#define PTWM_B200_TRY_INTDELTA 1u   /* split + IntDelta on the exponent plane */
+#define PTWM_B200_TRY_MZS      2u   /* split + MantissaZeroStrip(k), k = 1..4, on mantissa plane 0 */
 
 typedef struct ptwm_b200_encoded ptwm_b200_encoded;
 

@@ -45,12 +45,12 @@ class TensorInfo(C.Structure):
 
 class EncodeTensor(C.Structure):
     _fields_ = [("name", C.c_char_p), ("dev_ptr", C.c_uint64), ("nbytes", C.c_uint64), ("shape", C.c_uint64 * 8), ("dtype_code", C.c_uint16),
-                ("ndim", C.c_uint8), ("usage", C.c_uint8)]
+                ("ndim", C.c_uint8), ("usage", C.c_uint8), ("post_op", C.c_uint8), ("post_plane", C.c_uint8), ("post_k", C.c_uint8), ("reserved_", C.c_uint8)]
 
 
 class EncodeOptions(C.Structure):
     _fields_ = [("chunk_size", C.c_uint32), ("menu", C.c_uint32), ("forced_codec", C.c_int32), ("emit_plane_crc", C.c_uint8),
-                ("emit_payload_hash", C.c_uint8), ("reserved", C.c_uint8 * 2)]
+                ("emit_payload_hash", C.c_uint8), ("candidates", C.c_uint8), ("reserved", C.c_uint8 * 1)]
 
 
 _SIGNATURES = {

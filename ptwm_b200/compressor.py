@@ -38,6 +38,10 @@ class CompressionConfig:
     ``emit_plane_crc`` / ``emit_payload_hash`` as in python/ptwm/_config.py:177-184."""
     streaming_chunk: Optional[int] = 65536
     codec_menu: Sequence[int] = (IDENTITY, HUFFMAN, RANS, TANS, ORDER1_SCALE_AC)
+    # Candidate chains tried beside the plain split for every 16- / 32-bit float tensor ("intdelta": IntDelta on the
+    # exponent plane; "mzs": MantissaZeroStrip(1..4) on mantissa plane 0); the smallest total wins, the plain split on ties
+    # (the reference's STANDARD candidate lists, python/ptwm/preprocessing/_chains.py:1151-1185, as far as the decoder goes).
+    candidate_chains: Sequence[str] = ()
     forced_codec: Optional[int] = None
     emit_plane_crc: bool = False
     emit_payload_hash: bool = False
@@ -79,12 +83,15 @@ def _planes_of(code: int, usage: int) -> int:
 
 
 def compress_model(tensors: Mapping[str, torch.Tensor], config: Optional[CompressionConfig] = None, *, usage: Optional[Mapping[str, str]] = None,
-                   device: Optional[int] = None) -> EncodedContainer:
+                   device: Optional[int] = None, post: Optional[Mapping[str, tuple]] = None) -> EncodedContainer:
     """Encode CUDA tensors into one container.  ``usage`` maps a tensor name to
     'scale', 'global_scale' or 'fp4' for the microscaling chains; everything
-    else gets the standard chain of its dtype."""
+    else gets the standard chain of its dtype.  ``post`` fixes the chain of a
+    16- / 32-bit float tensor instead of leaving it to ``candidate_chains``:
+    ``("intdelta",)`` or ``("mzs", k)``."""
     cfg = config or CompressionConfig()
     usage = usage or {}
+    post = post or {}
     names = list(tensors)
     arr = (_lib.EncodeTensor * max(len(names), 1))()
     keep = []
@@ -112,6 +119,15 @@ def compress_model(tensors: Mapping[str, torch.Tensor], config: Optional[Compres
             e.shape[d] = s
         e.dtype_code = code
         e.usage = u
+        op = post.get(name)
+        if op is not None:
+            planes = _planes_of(code, u)
+            if op[0] == "intdelta":
+                e.post_op, e.post_plane = 1, planes - 1
+            elif op[0] == "mzs":
+                e.post_op, e.post_plane, e.post_k = 2, 0, int(op[1])
+            else:
+                raise ValueError(f"{name}: unknown per-plane op {op[0]!r}")
         n_planes.append(_planes_of(code, u))
     dev = torch.cuda.current_device() if dev is None else dev
     menu = 0
@@ -119,8 +135,13 @@ def compress_model(tensors: Mapping[str, torch.Tensor], config: Optional[Compres
         if c not in _MENU_BIT:
             raise ValueError(f"codec {c} is not offered by the device encoder (identity, huffman, rans, tans, order1_scale_ac)")
         menu |= _MENU_BIT[c]
+    tries = 0
+    for c in cfg.candidate_chains:
+        if c not in ("intdelta", "mzs"):
+            raise ValueError(f"candidate chain {c!r} is not offered by the device encoder (intdelta, mzs)")
+        tries |= 1 if c == "intdelta" else 2
     opt = _lib.EncodeOptions(_CHUNK_NONE if cfg.streaming_chunk is None else int(cfg.streaming_chunk), menu, -1 if cfg.forced_codec is None else int(cfg.forced_codec), int(cfg.emit_plane_crc),
-                             int(cfg.emit_payload_hash))
+                             int(cfg.emit_payload_hash), tries)
     torch.cuda.current_stream(dev).synchronize()
     h = C.c_void_p()
     _check(_lib.lib().ptwm_b200_encode_model(arr, len(names), C.byref(opt), dev, stream_handle(dev), C.byref(h)))

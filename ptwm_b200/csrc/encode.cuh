@@ -48,17 +48,54 @@ constexpr uint32_t GATHER_BARE = 0x100;
 constexpr uint32_t GATHER_NOFRAME = 0x200;  // an unchunked plane: inline state (if the codec has one) and payload, no frame header
 
 // layout of the table area of a chunk
-//   rANS:    freqs u16[256] | cum u16[256]                                                  (1 KiB)
+//   rANS:    freqs u16[256] | per symbol {reciprocal u32, bias u32, 2048 - freq u32, reciprocal shift u32}   (4.5 KiB)
 //   Huffman: lengths u8[256] | unused[256] | rev codes u16[256]                            (1 KiB)
 //   tANS:    norm u16[256] | delta_nb u32[256] | delta_find_state i32[256] | next-state u16[2048] | spread symbols u8[2048]
 //   O1SAC:   joint counts u32[256][256] | row-start counts u32[256] | present u8[256] | rank u16[256] |
 //            pmf u16[257][256] (row 0 marginal, row 1 + c for context c) | cum u16[257][256]
 constexpr uint32_t ENC_TABLE_BYTES = 1024;
+constexpr uint32_t ENC_RANS_TABLE_BYTES = 512 + 4096;
 constexpr uint32_t ENC_TANS_TABLE_BYTES = 512 + 1024 + 1024 + 4096 + 2048;
 constexpr uint32_t O1E_JOINT = 0, O1E_MARG = 262144, O1E_PRESENT = O1E_MARG + 1024, O1E_RANK = O1E_PRESENT + 256, O1E_PMF = O1E_RANK + 512,
                    O1E_CUM = O1E_PMF + 257 * 512, ENC_O1SAC_TABLE_BYTES = O1E_CUM + 257 * 512;
 constexpr uint32_t O1SAC_TOTAL = 4096;
-__host__ __device__ inline uint32_t enc_table_bytes(int codec) { return codec == C_TANS ? ENC_TANS_TABLE_BYTES : codec == C_O1SAC ? ENC_O1SAC_TABLE_BYTES : ENC_TABLE_BYTES; }
+__host__ __device__ inline uint32_t enc_table_bytes(int codec) {
+    return codec == C_RANS ? ENC_RANS_TABLE_BYTES : codec == C_TANS ? ENC_TANS_TABLE_BYTES : codec == C_O1SAC ? ENC_O1SAC_TABLE_BYTES : ENC_TABLE_BYTES;
+}
+
+// The bytes of [p, p + n) handed to `f` one at a time, last to first (BACKWARD) or first to last, read from memory
+// in aligned 16-byte blocks wherever a whole block lies inside the range.  An encoding thread walks its own stream:
+// with single-byte loads every byte costs a 32-byte sector fetch of its own once the lines have left the L1.
+template <bool BACKWARD, class F>
+__device__ __forceinline__ void for_each_byte(const uint8_t* p, uint32_t n, F&& f) {
+    const uintptr_t lo = reinterpret_cast<uintptr_t>(p), hi = lo + n;
+    const uintptr_t first_block = (lo + 15) & ~uintptr_t(15), last_block = hi & ~uintptr_t(15);  // whole blocks: [first_block, last_block)
+    if (first_block >= last_block) {
+        if (BACKWARD) for (uint32_t k = n; k-- > 0;) f(uint32_t(p[k]));
+        else for (uint32_t k = 0; k < n; ++k) f(uint32_t(p[k]));
+        return;
+    }
+    if (BACKWARD) {
+        for (uintptr_t a = hi; a-- > last_block;) f(uint32_t(*reinterpret_cast<const uint8_t*>(a)));
+        for (uintptr_t b = last_block; b > first_block;) {
+            b -= 16;
+            const uint4 v = *reinterpret_cast<const uint4*>(b);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 15; k >= 0; --k) f((w[k >> 2] >> (8 * (k & 3))) & 0xFFu);
+        }
+        for (uintptr_t a = first_block; a-- > lo;) f(uint32_t(*reinterpret_cast<const uint8_t*>(a)));
+    } else {
+        for (uintptr_t a = lo; a < first_block; ++a) f(uint32_t(*reinterpret_cast<const uint8_t*>(a)));
+        for (uintptr_t b = first_block; b < last_block; b += 16) {
+            const uint4 v = *reinterpret_cast<const uint4*>(b);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 0; k < 16; ++k) f((w[k >> 2] >> (8 * (k & 3))) & 0xFFu);
+        }
+        for (uintptr_t a = last_block; a < hi; ++a) f(uint32_t(*reinterpret_cast<const uint8_t*>(a)));
+    }
+}
 
 __global__ void __launch_bounds__(256) split_kernel(const SplitItem* __restrict__ items, uint32_t n_items, uint8_t* __restrict__ planes) {
     uint32_t tile = blockIdx.x;
@@ -69,7 +106,64 @@ __global__ void __launch_bounds__(256) split_kernel(const SplitItem* __restrict_
     uint32_t n = it.n - base < SPLIT_TILE ? uint32_t(it.n - base) : SPLIT_TILE;
     const int eb = kind_elem_bytes(int(it.kind));
     const uint8_t* src = it.src + base * uint64_t(eb);
-    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+    // Sixteen elements per thread and step where the source is 16-byte aligned: 128-bit loads, one 128-bit store per
+    // plane.  (Plane offsets and tile bases are multiples of 16 by construction.)  The rest goes element by element.
+    uint32_t done = 0;
+    if ((reinterpret_cast<uintptr_t>(src) & 15) == 0 && it.kind != K_PASS) {
+        const uint32_t groups = n / 16;
+        for (uint32_t g = threadIdx.x; g < groups; g += blockDim.x) {
+            const uint64_t at = base + uint64_t(g) * 16;
+            if (it.kind == K_M16) {
+                const uint4 a = reinterpret_cast<const uint4*>(src)[2 * g], b = reinterpret_cast<const uint4*>(src)[2 * g + 1];
+                const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+                uint32_t lo[4], hi[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {  // two words = four elements -> one word per plane
+                    const uint32_t r0 = ((w[2 * k] << 1) & 0xFF00FF00u) | ((w[2 * k] >> 8) & 0x00800080u) | (w[2 * k] & 0x007F007Fu);
+                    const uint32_t r1 = ((w[2 * k + 1] << 1) & 0xFF00FF00u) | ((w[2 * k + 1] >> 8) & 0x00800080u) | (w[2 * k + 1] & 0x007F007Fu);
+                    lo[k] = __byte_perm(r0, r1, 0x6420);
+                    hi[k] = __byte_perm(r0, r1, 0x7531);
+                }
+                *reinterpret_cast<uint4*>(planes + it.plane_off[0] + at) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                *reinterpret_cast<uint4*>(planes + it.plane_off[1] + at) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+            } else if (it.kind == K_M32) {
+                uint32_t pl[4][4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {  // four elements -> one word per plane
+                    const uint4 v = reinterpret_cast<const uint4*>(src)[4 * g + q];
+                    const uint32_t e[4] = {v.x, v.y, v.z, v.w};
+                    uint32_t r[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) r[k] = ((e[k] << 1) & 0xFF000000u) | ((e[k] >> 8) & 0x00800000u) | (e[k] & 0x007FFFFFu);
+                    const uint32_t t0 = __byte_perm(r[0], r[1], 0x5140), t1 = __byte_perm(r[2], r[3], 0x5140);  // bytes 0,1 of the pairs
+                    const uint32_t t2 = __byte_perm(r[0], r[1], 0x7362), t3 = __byte_perm(r[2], r[3], 0x7362);  // bytes 2,3
+                    pl[0][q] = __byte_perm(t0, t1, 0x5410); pl[1][q] = __byte_perm(t0, t1, 0x7632);
+                    pl[2][q] = __byte_perm(t2, t3, 0x5410); pl[3][q] = __byte_perm(t2, t3, 0x7632);
+                }
+#pragma unroll
+                for (int p = 0; p < 4; ++p) *reinterpret_cast<uint4*>(planes + it.plane_off[p] + at) = make_uint4(pl[p][0], pl[p][1], pl[p][2], pl[p][3]);
+            } else {
+                const uint4 v = reinterpret_cast<const uint4*>(src)[g];
+                const uint32_t e[4] = {v.x, v.y, v.z, v.w};
+                uint32_t hi[4], lo[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint32_t r = it.kind == K_E4M3 ? (((e[k] & 0x78787878u) << 1) | ((e[k] & 0x80808080u) >> 4) | (e[k] & 0x07070707u))
+                                                        : (((e[k] & 0x7C7C7C7Cu) << 1) | ((e[k] & 0x80808080u) >> 5) | (e[k] & 0x03030303u));
+                    hi[k] = (r >> 4) & 0x0F0F0F0Fu; lo[k] = r & 0x0F0F0F0Fu;
+                }
+                *reinterpret_cast<uint4*>(planes + it.plane_off[0] + at) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4*>(planes + it.plane_off[1] + at) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            }
+        }
+        done = groups * 16;
+    } else if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+        const uint32_t groups = n / 16;
+        for (uint32_t g = threadIdx.x; g < groups; g += blockDim.x)
+            *reinterpret_cast<uint4*>(planes + it.plane_off[0] + base + uint64_t(g) * 16) = reinterpret_cast<const uint4*>(src)[g];
+        done = groups * 16;
+    }
+    for (uint32_t i = done + threadIdx.x; i < n; i += blockDim.x) {
         switch (it.kind) {
             case K_PASS: planes[it.plane_off[0] + base + i] = src[i]; break;
             case K_M16: {
@@ -127,12 +221,33 @@ __global__ void __launch_bounds__(64) table_kernel(const EncChunk* __restrict__ 
     if (codec == C_O1SAC) return;  // fitted by its own kernels
     if (codec == C_RANS && c.n) {
         uint16_t* freqs = reinterpret_cast<uint16_t*>(tab);
-        uint16_t* cum = freqs + 256;
+        uint4* sym = reinterpret_cast<uint4*>(tab + 512);
         int ms = rans_normalize(raw, c.n, freqs);
         if (ms >= 0) {
+            // x' = x + bias + floor(x / f) * (2048 - f) with the quotient from a rounded-up reciprocal: exact for every
+            // state below 2^31, i.e. identical to (x / f) * 2048 + x % f + start (entropy/rans/compress.rs:140-185)
             uint32_t run = 0;
-            for (int i = 0; i < 256; ++i) { cum[i] = uint16_t(run); run += freqs[i]; }
+            for (int i = 0; i < 256; ++i) {
+                const uint32_t f = freqs[i];
+                uint4 e = make_uint4(0, 0, 0, 0);
+                if (f == 1) e = make_uint4(0xFFFFFFFFu, run + 2047u, 2047u, 0u);
+                else if (f > 1) {
+                    uint32_t shift = 0;
+                    while (f > (1u << shift)) ++shift;
+                    e = make_uint4(uint32_t(((1ull << (shift + 31)) + f - 1) / f), run, 2048u - f, shift - 1);
+                }
+                sym[i] = e;
+                run += f;
+            }
             r.hdr_n = uint32_t(ms); r.coded = 1;
+            // A chunk that cannot come out smaller than it is gets no encoding pass: the coder's output is at least the
+            // information content of the chunk under its table, less the four initial states, so when that alone (with a
+            // margin for the float logarithm) reaches the chunk's size the result would be discarded anyway
+            // (compress.rs: NotBeneficial).  Sign / mantissa planes are the usual case.
+            float bits = 0.f;
+            for (int i = 0; i <= ms; ++i) if (raw[i]) bits += float(raw[i]) * (11.f - log2f(float(freqs[i])));
+            const float lower = bits * (1.f - 1e-4f) / 8.f - 16.f + float(1 + 2 * (ms + 1) + 16);
+            if (lower >= float(c.n) + 64.f) r.coded = 0;
         }
     } else if (codec == C_HUFFMAN && c.n) {
         uint32_t nf[512]; uint16_t parent[512]; uint8_t alive[512]; uint8_t sym_of[256];
@@ -141,6 +256,10 @@ __global__ void __launch_bounds__(64) table_kernel(const EncChunk* __restrict__ 
         if (nw > 0) {
             huffman_codes(lengths, reinterpret_cast<uint16_t*>(tab + 512));
             r.hdr_n = uint32_t(nw); r.coded = 1;
+            // the four streams together hold at least ceil(total bits / 8) bytes: no encoding pass for a chunk that cannot shrink
+            uint64_t total_bits = 0;
+            for (int i = 0; i < nw; ++i) total_bits += uint64_t(raw[i]) * lengths[i];
+            if ((total_bits + 7) / 8 + (nw <= 127 ? 1 : 2) + (uint32_t(nw) + 1) / 2 + 16 >= c.n) r.coded = 0;
         }
     } else if (codec == C_TANS && c.n) {  // entropy/tans/mod.rs:199-266
         uint16_t* norm = reinterpret_cast<uint16_t*>(tab);
@@ -201,12 +320,11 @@ __global__ void __launch_bounds__(128) encode_kernel(const EncChunk* __restrict_
             nb_acc += nb; total_bits += nb;
             if (nb_acc >= 32) { w32[words++] = uint32_t(acc); acc >>= 32; nb_acc -= 32; }
         };
-        for (uint32_t k = c.n; k-- > 0;) {
-            const uint32_t b = src[k];
+        for_each_byte<true>(src, c.n, [&](uint32_t b) {
             const uint32_t nb = (value + dnb[b]) >> 16;
             add_bits(value, nb);
             value = next_state[int32_t(value >> nb) + dfs[b]];
-        }
+        });
         add_bits(value, 11);
         uint8_t* tail = reinterpret_cast<uint8_t*>(w32 + words);
         uint32_t bytes = words * 4;
@@ -234,27 +352,24 @@ __global__ void __launch_bounds__(128) encode_kernel(const EncChunk* __restrict_
     auto flush = [&]() { while (have) { --have; *--w = uint8_t(acc >> (8 * have)); } };
     const uint8_t* tab = tables + c.table_off;
     if (codec == C_RANS) {
-        const uint16_t* freqs = reinterpret_cast<const uint16_t*>(tab);
-        const uint16_t* cum = freqs + 256;
+        const uint4* syms = reinterpret_cast<const uint4*>(tab + 512);
         uint32_t x = 1u << 23;
-        for (uint32_t k = len; k-- > 0;) {
-            uint32_t sym = src[k];
-            uint32_t f = freqs[sym], cs = cum[sym];
-            uint32_t max_state = ((1u << 12) << 8) * f;  // ((L >> 11) << 8) * freq
+        for_each_byte<true>(src, len, [&](uint32_t sym) {
+            const uint4 e = __ldg(syms + sym);
+            const uint32_t max_state = (2048u - e.z) << 20;  // ((L >> 11) << 8) * freq
             while (x >= max_state) { put(x); x >>= 8; }
-            x = (x / f) * 2048u + (x % f) + cs;
-        }
+            x = x + e.y + (__umulhi(x, e.x) >> e.w) * e.z;
+        });
         put(x >> 24); put(x >> 16); put(x >> 8); put(x);  // the final state, little-endian, below the renormalisation bytes
     } else {
         const uint8_t* lengths = tab;
         const uint16_t* rev = reinterpret_cast<const uint16_t*>(tab + 512);
         uint64_t bits = 0; uint32_t cnt = 0;
-        for (uint32_t k = 0; k < len; ++k) {
-            uint32_t sym = src[k];
+        for_each_byte<false>(src, len, [&](uint32_t sym) {
             bits |= uint64_t(rev[sym]) << cnt;
             cnt += lengths[sym];
             while (cnt >= 8) { put(uint32_t(bits)); bits >>= 8; cnt -= 8; }
-        }
+        });
         if (cnt) put(uint32_t(bits));
     }
     flush();
@@ -347,6 +462,32 @@ __global__ void __launch_bounds__(128) gather_kernel(const GatherItem* __restric
         for (uint32_t i = t; i < r.stream_len[s]; i += blockDim.x) d[i] = sp[i];
         d += r.stream_len[s];
     }
+}
+
+// ---- ops between a byte split and a terminal (transforms/int_delta.rs:36-44, transforms/mantissa_zero.rs) ------
+// IntDelta forward, byte width: every byte minus the one before it, modulo 256, over the whole plane (out of place).
+__global__ void __launch_bounds__(256) delta_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t n) {
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += uint64_t(gridDim.x) * blockDim.x)
+        dst[i] = uint8_t(src[i] - (i ? src[i - 1] : 0));
+}
+// OR of all bytes of a plane: MantissaZeroStrip(k) applies when the low k bits of that are clear.
+__global__ void __launch_bounds__(256) or_bytes_kernel(const uint8_t* __restrict__ src, uint64_t n, uint32_t* __restrict__ out) {
+    uint32_t v = 0;
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += uint64_t(gridDim.x) * blockDim.x) v |= src[i];
+    v = __reduce_or_sync(0xFFFFFFFFu, v);
+    if ((threadIdx.x & 31) == 0 && v) atomicOr(out, v);
+}
+__global__ void __launch_bounds__(256) shift_right_kernel(uint8_t* __restrict__ p, uint64_t n, uint32_t k) {
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += uint64_t(gridDim.x) * blockDim.x) p[i] = uint8_t(p[i] >> k);
+}
+// The chunk histograms of a plane whose bytes were just shifted right by k (all with k clear low bits): count v moves to v >> k.
+__global__ void __launch_bounds__(256) relabel_hist_kernel(uint32_t* __restrict__ hist, uint32_t first_chunk, uint32_t k) {
+    uint32_t* h = hist + uint64_t(first_chunk + blockIdx.x) * 256;
+    const uint32_t v = threadIdx.x, c = h[v];
+    __syncthreads();
+    h[v] = 0;
+    __syncthreads();
+    if (c) h[v >> k] = c;
 }
 
 // ---- Order1ScaleAC encode (codecs/order1_scale_ac.rs:620-663, 963-1025) -------------------------------------

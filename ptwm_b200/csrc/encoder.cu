@@ -29,7 +29,8 @@ struct ChainDef {
     uint8_t kind;
     std::vector<std::pair<uint16_t, std::vector<uint8_t>>> nodes;  // (op wire id, params)
     std::vector<uint8_t> roles;                                    // compact terminal role bytes
-    bool operator==(const ChainDef& o) const { return nodes == o.nodes && roles == o.roles; }
+    int post_plane = -1;  // >= 0: the last node is an op between output `post_plane` of the split (node 2) and that plane's terminal
+    bool operator==(const ChainDef& o) const { return nodes == o.nodes && roles == o.roles && post_plane == o.post_plane; }
 };
 
 std::vector<uint8_t> source_params(const uint64_t* shape, int ndim, uint16_t chain_dtype) {
@@ -88,6 +89,12 @@ struct TensorPlan {
     uint32_t chain_id = 0;
     std::vector<PlanePlan> planes;
     uint64_t hash = 0;
+    // candidate chains: the exponent plane after IntDelta lives in a plane of its own until the choice is made
+    bool has_delta = false;
+    PlanePlan delta;          // plane index = delta_index
+    uint32_t delta_index = 0, first_plane = 0;
+    uint32_t try_mzs = 0;     // word index of the OR of mantissa plane 0's bytes, + 1 (0 = not looked at)
+    int post_op = 0, post_k = 0;  // what was chosen (or given): 1 IntDelta on the last plane, 2 MantissaZeroStrip(post_k) on plane 0
 };
 
 // Size of the whole plane under each codec of the menu, the way the reference's
@@ -99,8 +106,9 @@ struct TensorPlan {
 // information content under their normalised tables, Order1ScaleAC the
 // information content under the rows it would fit (`o1sac_bytes` < 0: the
 // codec does not accept this plane).
-int select_codec(const unsigned long long* hist, uint64_t n, uint32_t menu, double o1sac_bytes) {
+int select_codec(const unsigned long long* hist, uint64_t n, uint32_t menu, double o1sac_bytes, double* best_size = nullptr) {
     double best = 0; int best_codec = -1;
+    struct Report { double& b; double* out; ~Report() { if (out) *out = b; } } report{best, best_size};
     auto offer = [&](int codec, double size) { if (best_codec < 0 || size < best) { best = size; best_codec = codec; } };
     uint32_t raw32[256];
     for (int i = 0; i < 256; ++i) raw32[i] = uint32_t(hist[i]);
@@ -219,7 +227,7 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
     std::vector<EncChunk> chunks;
     std::vector<HashItem> hash_items;
     uint64_t planes_bytes = 0, slots_bytes = 0;
-    uint32_t n_planes = 0, tile = 0;
+    uint32_t n_planes = 0, tile = 0, n_or_words = 0;
     for (size_t i = 0; i < n_tensors; ++i) {
         const ptwm_b200_encode_tensor& t = tensors[i];
         std::string why;
@@ -230,15 +238,14 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
         for (int d = 0; d < t.ndim; ++d) { if (t.shape[d] > 0xFFFFFFFFull) return fail(PTWM_RC_UNSUPPORTED, "dimension exceeds u32"); elems *= t.shape[d]; }
         if (elems * detail::public_dtype_bytes(t.dtype_code) != t.nbytes) return fail(PTWM_RC_INVALID_INPUT, std::string(t.name) + ": nbytes does not match shape x dtype");
         if (t.nbytes && !t.dev_ptr) return fail(PTWM_RC_INVALID_INPUT, "null device pointer");
-        // a Source whose params equal the record's own shape/dtype is written bound (empty params): compressor.rs:708-715
-        ChainDef reg = plan[i].chain;
-        int cd = detail::chain_dtype_for_public(t.dtype_code);
-        if (cd >= 0 && reg.nodes[0].second == source_params(t.shape, t.ndim, uint16_t(cd))) reg.nodes[0].second.clear();
-        auto found = std::find(registry.begin(), registry.end(), reg);
-        if (found == registry.end()) { registry.push_back(reg); found = registry.end() - 1; }
-        plan[i].chain_id = uint32_t(found - registry.begin());
-        if (registry.size() > 0x8000) return fail(PTWM_RC_UNSUPPORTED, "more than 32768 distinct chains");
         const int kind = plan[i].chain.kind, np = kind_planes(kind);
+        if (t.post_op) {
+            if (kind != K_M16 && kind != K_M32) return fail(PTWM_RC_INVALID_INPUT, std::string(t.name) + ": per-plane ops go on the planes of a byte split");
+            if (t.post_op == 1 && t.post_plane != np - 1) return fail(PTWM_RC_UNSUPPORTED, std::string(t.name) + ": IntDelta goes on the exponent plane");
+            if (t.post_op == 2 && (t.post_plane != 0 || t.post_k < 1 || t.post_k > 7)) return fail(PTWM_RC_UNSUPPORTED, std::string(t.name) + ": MantissaZeroStrip(1..7) goes on mantissa plane 0");
+            if (t.post_op > 2) return fail(PTWM_RC_UNSUPPORTED, std::string(t.name) + ": unknown per-plane op");
+        }
+        plan[i].first_plane = n_planes;
         const uint64_t plane_len = t.nbytes / uint64_t(kind_elem_bytes(kind));
         if (plane_len > 0xFFFFFFFFull) return fail(PTWM_RC_UNSUPPORTED, "plane longer than 4 GiB");
         SplitItem sp{reinterpret_cast<const uint8_t*>(uintptr_t(t.dev_ptr)), {0, 0, 0, 0}, plane_len, uint32_t(kind), tile};
@@ -262,6 +269,22 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
         }
         if (plane_len) { splits.push_back(sp); tile += uint32_t((plane_len + SPLIT_TILE - 1) / SPLIT_TILE); }
         if (opt.emit_payload_hash) hash_items.push_back(HashItem{make_ref(SP_BLOB, t.dev_ptr), t.nbytes});
+        const bool split_kind = (kind == K_M16 || kind == K_M32) && plane_len;
+        plan[i].post_op = t.post_op; plan[i].post_k = t.post_k;
+        plan[i].has_delta = split_kind && (t.post_op == 1 || (!t.post_op && (opt.candidates & PTWM_B200_TRY_INTDELTA)));
+        if (split_kind && (t.post_op == 2 || (!t.post_op && (opt.candidates & PTWM_B200_TRY_MZS)))) plan[i].try_mzs = ++n_or_words;
+    }
+    // the IntDelta candidates' exponent planes: planes of their own behind the others
+    for (size_t i = 0; i < n_tensors; ++i) {
+        TensorPlan& tp = plan[i];
+        if (!tp.has_delta) continue;
+        const PlanePlan& ex = tp.planes.back();
+        PlanePlan& pp = tp.delta;
+        pp.len = ex.len; pp.buf_off = planes_bytes; pp.first_chunk = uint32_t(chunks.size()); pp.role = ex.role; pp.row_len = 0;
+        planes_bytes += align_up(pp.len, 16);
+        for (uint32_t k = 0; k < ex.n_chunks; ++k) { EncChunk c = chunks[ex.first_chunk + k]; c.plane_off = pp.buf_off + (c.plane_off - ex.buf_off); c.plane = n_planes; chunks.push_back(c); }
+        pp.n_chunks = ex.n_chunks;
+        tp.delta_index = n_planes++;
     }
     const uint32_t n_chunks = uint32_t(chunks.size());
 
@@ -274,6 +297,15 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
     CUDA_TRY(d_plane_hist.alloc(uint64_t(n_planes) * 256 * 8));
     CUDA_TRY(cudaMemsetAsync(d_plane_hist.p, 0, uint64_t(n_planes) * 256 * 8 + (n_planes ? 0 : 1), st));
     if (tile) { split_kernel<<<tile, 256, 0, st>>>(d_splits.as<SplitItem>(), uint32_t(splits.size()), d_planes.as<uint8_t>()); CUDA_TRY(cudaGetLastError()); }
+    DeviceBuf d_or;
+    std::vector<uint32_t> or_words(n_or_words);
+    if (n_or_words) { CUDA_TRY(d_or.alloc(uint64_t(n_or_words) * 4)); CUDA_TRY(cudaMemsetAsync(d_or.p, 0, uint64_t(n_or_words) * 4, st)); }
+    for (auto& tp : plan) {
+        auto blocks = [](uint64_t n) { return unsigned(std::min<uint64_t>((n + 4095) / 4096, 2368)); };
+        if (tp.has_delta) { delta_kernel<<<blocks(tp.delta.len), 256, 0, st>>>(d_planes.as<uint8_t>() + tp.planes.back().buf_off, d_planes.as<uint8_t>() + tp.delta.buf_off, tp.delta.len); CUDA_TRY(cudaGetLastError()); }
+        if (tp.try_mzs) { or_bytes_kernel<<<blocks(tp.planes[0].len), 256, 0, st>>>(d_planes.as<uint8_t>() + tp.planes[0].buf_off, tp.planes[0].len, d_or.as<uint32_t>() + tp.try_mzs - 1); CUDA_TRY(cudaGetLastError()); }
+    }
+    if (n_or_words) CUDA_TRY(cudaMemcpyAsync(or_words.data(), d_or.p, uint64_t(n_or_words) * 4, cudaMemcpyDeviceToHost, st));
     if (n_chunks) { hist_kernel<<<n_chunks, 128, 0, st>>>(d_chunks.as<EncChunk>(), d_planes.as<uint8_t>(), d_hist.as<uint32_t>(), d_plane_hist.as<unsigned long long>()); CUDA_TRY(cudaGetLastError()); }
     std::vector<unsigned long long> plane_hist(size_t(n_planes) * 256);
     if (n_planes) CUDA_TRY(cudaMemcpyAsync(plane_hist.data(), d_plane_hist.p, plane_hist.size() * 8, cudaMemcpyDeviceToHost, st));
@@ -283,10 +315,12 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
     std::vector<VerifyTensor> verify;
     uint64_t n_runs = 0;
     if (opt.emit_plane_crc) {
-        uint32_t acc = 0;
-        for (auto& tp : plan) for (auto& pp : tp.planes) {
+        auto add = [&](const PlanePlan& pp, uint32_t acc) {
             if (pp.len) { verify.push_back(VerifyTensor{make_ref(SP_OUT, pp.buf_off), pp.len, n_runs, K_PASS, acc}); n_runs += (pp.len + VERIFY_RUN - 1) / VERIFY_RUN; }
-            ++acc;
+        };
+        for (auto& tp : plan) {  // accumulator = global plane index; a plane CRC covers the terminal's bytes, so the delta planes get theirs too
+            for (size_t p = 0; p < tp.planes.size(); ++p) add(tp.planes[p], tp.first_plane + uint32_t(p));
+            if (tp.has_delta) add(tp.delta, tp.delta_index);
         }
         CUDA_TRY(upload_vec(d_verify, verify, st));
         CUDA_TRY(d_acc.alloc(uint64_t(n_planes) * 4));
@@ -346,14 +380,80 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
     std::vector<uint8_t> plane_codec(n_planes);
     std::vector<uint32_t> o1sac_chunks;
     uint64_t tables_bytes = 0;
+    std::vector<std::pair<uint32_t, uint32_t>> recrc;  // (tensor, accumulator) of planes shifted by MantissaZeroStrip: their CRC is taken again below
     {
-        uint32_t pi = 0;
         const CrcTables& T = crc_tables();
+        const uint32_t sel_menu = opt.forced_codec >= 0 ? (opt.forced_codec == C_IDENTITY ? PTWM_B200_MENU_IDENTITY : opt.forced_codec == C_HUFFMAN ? PTWM_B200_MENU_HUFFMAN :
+                                                           opt.forced_codec == C_RANS ? PTWM_B200_MENU_RANS : opt.forced_codec == C_TANS ? PTWM_B200_MENU_TANS : 0u) : menu;
+        auto pick = [&](uint32_t plane_index, const unsigned long long* hist, uint64_t len, double* size) {
+            if (opt.forced_codec == C_O1SAC) { if (size) *size = double(len); return int(C_O1SAC); }
+            int c = select_codec(hist, len, sel_menu, opt.forced_codec >= 0 ? -1.0 : o1sac_size[plane_index], size);
+            return opt.forced_codec >= 0 ? opt.forced_codec : c;
+        };
         for (size_t i = 0; i < n_tensors; ++i) {
+            TensorPlan& tp = plan[i];
             enc.plane_codecs.emplace_back();
-            for (auto& pp : plan[i].planes) {
-                pp.codec = opt.forced_codec >= 0 ? opt.forced_codec : select_codec(&plane_hist[size_t(pi) * 256], pp.len, menu, o1sac_size[pi]);
-                if (pp.codec < 0) return fail(PTWM_RC_INVALID_INPUT, "empty codec menu");
+            const size_t np = tp.planes.size();
+            std::vector<double> size(np, 0.0);
+            for (size_t p = 0; p < np; ++p) {
+                tp.planes[p].codec = pick(tp.first_plane + uint32_t(p), &plane_hist[size_t(tp.first_plane + p) * 256], tp.planes[p].len, &size[p]);
+                if (tp.planes[p].codec < 0) return fail(PTWM_RC_INVALID_INPUT, "empty codec menu");
+            }
+            // ---- chain: the plain split, or the candidate with the smallest total, the first in the reference's candidate order on ties
+            //      (split, IntDelta, MantissaZeroStrip 1..4: python/ptwm/preprocessing/_chains.py:1151-1185; compressor.rs:504-665)
+            double delta_size = 0; int delta_codec = -1;
+            if (tp.has_delta) delta_codec = pick(tp.delta_index, &plane_hist[size_t(tp.delta_index) * 256], tp.delta.len, &delta_size);
+            const uint32_t orv = tp.try_mzs ? or_words[tp.try_mzs - 1] : 0xFFu;
+            auto strip_fits = [&](int k) { return tp.planes[0].len && (orv & ((1u << k) - 1)) == 0; };
+            auto stripped = [&](int k, double* sz) {  // plane 0 after the shift: the same counts under other labels
+                unsigned long long h[256] = {0};
+                const unsigned long long* src = &plane_hist[size_t(tp.first_plane) * 256];
+                for (int v = 0; v < 256; ++v) if (src[v]) h[v >> k] += src[v];
+                return pick(tp.first_plane, h, tp.planes[0].len, sz);
+            };
+            if (tp.post_op == 2 && !strip_fits(tp.post_k))
+                return fail(PTWM_RC_INVALID_INPUT, std::string(tensors[i].name) + ": MantissaZeroStrip(" + std::to_string(tp.post_k) + "): the plane has a byte with non-zero low bits");
+            if (!tp.post_op && (tp.has_delta || tp.try_mzs)) {
+                double base = 0;
+                for (double v : size) base += v;
+                double best = base;
+                if (tp.has_delta && base - size[np - 1] + delta_size < best) { best = base - size[np - 1] + delta_size; tp.post_op = 1; }
+                if (tp.try_mzs) for (int k = 1; k <= 4 && strip_fits(k); ++k) {
+                    double sz; stripped(k, &sz);
+                    if (base - size[0] + sz < best) { best = base - size[0] + sz; tp.post_op = 2; tp.post_k = k; }
+                }
+            }
+            if (tp.post_op == 1) {  // the exponent plane is the delta plane from here on
+                if (delta_codec < 0) return fail(PTWM_RC_INTERNAL, "IntDelta chosen without its plane");
+                tp.delta.codec = delta_codec;
+                tp.planes[np - 1] = tp.delta;
+                tp.chain.nodes.push_back({uint16_t(detail::OP_INTDELTA), {}});
+                tp.chain.post_plane = int(np) - 1;
+            } else if (tp.post_op == 2) {
+                tp.planes[0].codec = stripped(tp.post_k, nullptr);
+                const uint64_t n = tp.planes[0].len;
+                shift_right_kernel<<<unsigned(std::min<uint64_t>((n + 4095) / 4096, 2368)), 256, 0, st>>>(d_planes.as<uint8_t>() + tp.planes[0].buf_off, n, uint32_t(tp.post_k));
+                CUDA_TRY(cudaGetLastError());
+                relabel_hist_kernel<<<tp.planes[0].n_chunks, 256, 0, st>>>(d_hist.as<uint32_t>(), tp.planes[0].first_chunk, uint32_t(tp.post_k));
+                CUDA_TRY(cudaGetLastError());
+                tp.chain.nodes.push_back({uint16_t(detail::OP_MZS), {uint8_t(tp.post_k)}});
+                tp.chain.post_plane = 0;
+                if (opt.emit_plane_crc) recrc.push_back({uint32_t(i), tp.first_plane});
+            }
+            // the chain is final: register it (a Source whose params equal the record's own shape/dtype is written bound: compressor.rs:708-715)
+            {
+                const ptwm_b200_encode_tensor& t = tensors[i];
+                ChainDef reg = tp.chain;
+                int cd = detail::chain_dtype_for_public(t.dtype_code);
+                if (cd >= 0 && reg.nodes[0].second == source_params(t.shape, t.ndim, uint16_t(cd))) reg.nodes[0].second.clear();
+                auto found = std::find(registry.begin(), registry.end(), reg);
+                if (found == registry.end()) { registry.push_back(reg); found = registry.end() - 1; }
+                tp.chain_id = uint32_t(found - registry.begin());
+                if (registry.size() > 0x8000) return fail(PTWM_RC_UNSUPPORTED, "more than 32768 distinct chains");
+            }
+            for (size_t p = 0; p < np; ++p) {
+                PlanePlan& pp = tp.planes[p];
+                const uint32_t pi = (tp.post_op == 1 && p == np - 1) ? tp.delta_index : tp.first_plane + uint32_t(p);
                 if (pp.codec == C_O1SAC && !chunked && pp.row_len && pp.len % pp.row_len) return fail(PTWM_RC_INVALID_INPUT, "order1_scale_ac: the row length does not divide the plane");
                 plane_codec[pi] = uint8_t(pp.codec);
                 enc.plane_codecs.back().push_back(pp.codec);
@@ -365,9 +465,30 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
                         ch.table_off = tables_bytes; tables_bytes += enc_table_bytes(pp.codec);
                         if (pp.codec == C_O1SAC) o1sac_chunks.push_back(pp.first_chunk + k);
                     }
-                ++pi;
             }
-            if (opt.emit_payload_hash) plan[i].hash = hashes[i];
+            if (opt.emit_payload_hash) tp.hash = hashes[i];
+        }
+        // planes that are not written (the exponent plane or its delta twin, whichever lost) get no encoding pass: plane_codec stays Identity
+        if (!recrc.empty()) {  // CRC of the shifted planes
+            std::vector<VerifyTensor> again;
+            uint64_t runs = 0;
+            for (auto& rc : recrc) {
+                const PlanePlan& pp = plan[rc.first].planes[0];
+                again.push_back(VerifyTensor{make_ref(SP_OUT, pp.buf_off), pp.len, runs, K_PASS, rc.second});
+                runs += (pp.len + VERIFY_RUN - 1) / VERIFY_RUN;
+                CUDA_TRY(cudaMemsetAsync(d_acc.as<uint32_t>() + rc.second, 0, 4, st));
+            }
+            DeviceBuf d_again;
+            CUDA_TRY(upload_vec(d_again, again, st));
+            Bases b{nullptr, 0, 0, nullptr, d_planes.as<uint8_t>()};
+            crc_planes_kernel<<<uint32_t((runs + 127) / 128), 128, 0, st>>>(d_again.as<VerifyTensor>(), uint32_t(again.size()), runs, b, d_tabs, d_acc.as<uint32_t>());
+            CUDA_TRY(cudaGetLastError());
+            CUDA_TRY(cudaMemcpyAsync(accs.data(), d_acc.p, accs.size() * 4, cudaMemcpyDeviceToHost, st));
+            CUDA_TRY(cudaStreamSynchronize(st));
+            for (auto& rc : recrc) {
+                PlanePlan& pp = plan[rc.first].planes[0];
+                pp.crc = ~(accs[rc.second] ^ gf2_mulmod(x_pow_8n(T.x2n, pp.len), 0xFFFFFFFFu));
+            }
         }
     }
 
@@ -456,10 +577,18 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
     put_varint(reg, registry.size());
     for (auto& c : registry) {  // CW2, every edge a spine edge (chain/wire_compact.rs:140-245)
         std::vector<uint8_t> cb;
-        put_varint(cb, c.nodes.size()); put_varint(cb, c.nodes.size() - 1); put_varint(cb, c.roles.size());
+        // nodes, edges, terminals; the leading edges (i, 0) -> (i + 1, 0) are the spine and only counted, an op between the split
+        // (node 2) and a terminal hangs off output `post_plane` by an explicit edge and takes that terminal over
+        const size_t last = c.nodes.size() - 1, split = c.post_plane >= 0 ? last - 1 : last;
+        put_varint(cb, c.nodes.size()); put_varint(cb, last); put_varint(cb, c.roles.size());
         for (auto& nd : c.nodes) { put_varint(cb, table_index(1, nd.first)); put_varint(cb, nd.second.size()); cb.insert(cb.end(), nd.second.begin(), nd.second.end()); }
-        if (c.nodes.size() > 1) put_varint(cb, c.nodes.size() - 1);
-        for (size_t i = 0; i < c.roles.size(); ++i) { cb.push_back(uint8_t(((c.nodes.size() - 1) << 4) | i)); cb.push_back(c.roles[i]); }
+        const bool on_spine = c.post_plane == 0;  // (split, 0) -> (last, 0) has the form of a spine edge and must be counted as one
+        if (last > 0) put_varint(cb, on_spine ? last : split);
+        if (c.post_plane > 0) { put_varint(cb, split); put_varint(cb, uint64_t(c.post_plane)); put_varint(cb, last); put_varint(cb, 0); cb.push_back(0); }
+        for (size_t i = 0; i < c.roles.size(); ++i) {
+            if (int(i) == c.post_plane) cb.push_back(uint8_t(last << 4)); else cb.push_back(uint8_t((split << 4) | i));
+            cb.push_back(c.roles[i]);
+        }
         put_varint(reg, cb.size());
         reg.insert(reg.end(), cb.begin(), cb.end());
     }
@@ -704,7 +833,7 @@ extern "C" {
 int64_t ptwm_b200_encode_model(const ptwm_b200_encode_tensor* tensors, size_t n, const ptwm_b200_encode_options* options, uint32_t device_ordinal, uint64_t stream,
                                ptwm_b200_encoded** out) {
     if ((!tensors && n) || !out) return fail(PTWM_RC_INVALID_INPUT, "null argument");
-    ptwm_b200_encode_options opt{0, 0, -1, 0, 0, {0, 0}};
+    ptwm_b200_encode_options opt{0, 0, -1, 0, 0, 0, {0}};
     if (options) opt = *options;
     DeviceGuard guard{int(device_ordinal)};
     if (guard.err != cudaSuccess) return fail(PTWM_RC_CUDA, std::string("cudaSetDevice: ") + cudaGetErrorString(guard.err));

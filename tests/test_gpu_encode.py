@@ -163,3 +163,76 @@ def test_scale_planes_go_to_order1_scale_ac_like_the_oracle_writer():
         h = ptwm_b200.ContainerHandle(blob, device=0)
         for (name, t), s in zip(h.decode_model(), specs):
             assert t.contiguous().view(torch.uint8).cpu().numpy().tobytes() == s.raw, name
+
+
+# ---- chains with one more op between the split and a terminal --------------------------------------------
+def _chain_model():
+    """bf16 / fp16 / fp32 tensors for the candidate chains: `smooth` has slowly varying magnitudes (its exponent bytes differ
+    little from one element to the next), `coarse` was rounded to few mantissa bits (every low mantissa byte ends in zero bits)."""
+    rng = np.random.default_rng(51)
+    n = 3 * 65536 + 777
+    env = np.exp(np.cumsum(rng.normal(0, 0.02, n))) * 1e-3
+    smooth = torch.from_numpy((env * rng.choice([-1.0, 1.0], n) * (1 + 0.3 * rng.random(n))).astype(np.float32))
+    coarse16 = (torch.randn(n, generator=torch.Generator().manual_seed(52)) * 0.02).to(torch.bfloat16).view(torch.int16) & ~0x000F
+    coarse32 = (torch.randn(n, generator=torch.Generator().manual_seed(53)) * 0.02).view(torch.int32) & ~0x0000003F
+    plain = (torch.randn(n, generator=torch.Generator().manual_seed(54)) * 0.02).to(torch.bfloat16)
+    return {"smooth.bf16": smooth.to(torch.bfloat16), "smooth.f32": smooth, "coarse.bf16": coarse16.view(torch.bfloat16), "coarse.f16": coarse16.view(torch.float16),
+            "coarse.f32": coarse32.view(torch.float32), "plain.bf16": plain}
+
+
+def _specs_of(tensors, post):
+    code = {torch.bfloat16: oracle.DT_BF16, torch.float16: oracle.DT_F16, torch.float32: oracle.DT_F32}
+    return [oracle.TensorSpec(n, code[t.dtype], list(t.shape), t.contiguous().view(torch.uint8).numpy().tobytes(), post=({p: op for p, op in [post[n]]} if n in post else None))
+            for n, t in tensors.items()]
+
+
+@pytest.mark.parametrize("chunk", [8192, None])
+@pytest.mark.parametrize("codec", [None, RANS, TANS])
+def test_given_chains_bytes_equal_oracle(chunk, codec):
+    host = _chain_model()
+    given = {"smooth.bf16": ("intdelta",), "smooth.f32": ("intdelta",), "coarse.bf16": ("mzs", 4), "coarse.f16": ("mzs", 2), "coarse.f32": ("mzs", 6)}
+    planes = {"smooth.bf16": 1, "smooth.f32": 3, "coarse.bf16": 0, "coarse.f16": 0, "coarse.f32": 0}
+    tensors = {n: t.cuda() for n, t in host.items()}
+    cfg = CompressionConfig(streaming_chunk=chunk, forced_codec=codec, codec_menu=(IDENTITY, HUFFMAN, RANS), emit_plane_crc=True, emit_payload_hash=True)
+    got = compress_model(tensors, cfg, post=given).to_bytes()
+    specs = _specs_of(host, {n: (planes[n], op) for n, op in given.items()})
+    want = oracle.write_container(specs, chunk_size=chunk, forced_codec=codec, menu=(IDENTITY, HUFFMAN, RANS), emit_crc=True, emit_hash=True)
+    if codec is not None:
+        assert got == want, next(i for i in range(min(len(got), len(want))) if got[i] != want[i])
+    else:
+        assert abs(len(got) - len(want)) <= 0.01 * len(want)
+    oc = oracle.Container(got)
+    for i, s in enumerate(specs):
+        assert oc.decode(i) == s.raw, s.name
+    h = ptwm_b200.ContainerHandle(got, device=0)
+    for (name, t), s in zip(h.decode_model(), specs):
+        assert t.contiguous().view(torch.uint8).cpu().numpy().tobytes() == s.raw, name
+    with pytest.raises(ptwm_b200.PtwmError, match="non-zero low bits"):
+        compress_model({"plain.bf16": tensors["plain.bf16"]}, cfg, post={"plain.bf16": ("mzs", 1)})
+
+
+def test_candidate_chains_pick_what_the_oracle_writer_would():
+    """Selection over {split, IntDelta, MantissaZeroStrip 1..4}: for every tensor the chain whose oracle-written container is the
+    smallest (the first candidate on ties), which is how the reference's pass 1 chooses (compressor.rs:504-665)."""
+    host = _chain_model()
+    tensors = {n: t.cuda() for n, t in host.items()}
+    cfg = CompressionConfig(streaming_chunk=16384, codec_menu=(IDENTITY, HUFFMAN, RANS), emit_plane_crc=True, candidate_chains=("intdelta", "mzs"))
+    enc = compress_model(tensors, cfg)
+    blob = enc.to_bytes()
+    h = ptwm_b200.ContainerHandle(blob, device=0)
+    for (name, t), src in zip(h.decode_model(), host.values()):
+        assert t.contiguous().view(torch.uint8).cpu().numpy().tobytes() == src.contiguous().view(torch.uint8).numpy().tobytes(), name
+    for name, t in host.items():
+        last = 3 if t.dtype == torch.float32 else 1
+        best, best_size = None, None
+        for cand in [None, (last, ("intdelta",))] + [(0, ("mzs", k)) for k in (1, 2, 3, 4)]:
+            try:
+                size = len(oracle.write_container(_specs_of({name: t}, {name: cand} if cand else {}), chunk_size=16384, menu=(IDENTITY, HUFFMAN, RANS), emit_crc=True))
+            except ValueError:
+                continue  # the strip does not apply
+            if best_size is None or size < best_size:
+                best, best_size = cand, size
+        one = compress_model({name: tensors[name]}, cfg)
+        assert abs(one.size - best_size) <= 0.005 * best_size, (name, best, one.size, best_size)
+    plain = compress_model(tensors, CompressionConfig(streaming_chunk=16384, codec_menu=(IDENTITY, HUFFMAN, RANS), emit_plane_crc=True)).size
+    assert enc.size < 0.97 * plain  # the candidates pay on this data
