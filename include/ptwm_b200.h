@@ -158,10 +158,12 @@ void ptwm_b200_plan_stats(const ptwm_b200_plan* p, uint64_t* bytes_read, uint64_
  * integer, 0 = the library's stream for the device (pass cudaStreamLegacy, 1,
  * for the legacy default stream).  Without
  * PTWM_B200_NO_SYNC the call returns after completion with all checks done
- * (ContainerReader::decode_model semantics, container.rs:1766-1780). */
+ * (ContainerReader::decode_model semantics, container.rs:1766-1780).
+ * A plan keeps one set of status words per device: at most one run of a plan
+ * may be in flight on a device (finish it before the next run); different
+ * plans, or one plan on different devices, run side by side. */
 int64_t ptwm_b200_plan_run(ptwm_b200_plan* p, uint64_t blob_dev_ptr, uint64_t blob_first, uint64_t blob_len, uint64_t out_dev_ptr, uint64_t out_cap,
                            uint64_t scratch_dev_ptr, uint64_t scratch_cap, uint32_t flags, uint32_t device_ordinal, uint64_t stream);
-/* Wait for an enqueued run and evaluate decode status and integrity checks. */
 /* Copy the plan's work lists to the device now instead of in the first
  * ptwm_b200_plan_run.  The copies are synchronous: a pipeline that enqueues large
  * transfers prepares its plans first, so that no run waits behind them. */
@@ -174,6 +176,7 @@ int64_t ptwm_b200_plan_prepare(ptwm_b200_plan* p, uint32_t device_ordinal);
  * engine, so preparing a plan does not wait behind transfers that are already queued. */
 uint64_t ptwm_b200_plan_device_bytes(const ptwm_b200_plan* p);
 int64_t ptwm_b200_plan_prepare_in(ptwm_b200_plan* p, uint32_t device_ordinal, uint64_t dev_ptr, uint64_t cap);
+/* Wait for an enqueued run and evaluate decode status and integrity checks. */
 int64_t ptwm_b200_plan_finish(ptwm_b200_plan* p, uint32_t flags, uint32_t device_ordinal, uint64_t stream);
 
 

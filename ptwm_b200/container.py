@@ -418,6 +418,27 @@ class Decompressor:
         return handle.decode("_")
 
 
+class TensorEntry:
+    """One entry of a ``.ptwm`` tensor index (``python/ptwm/random_access/__init__.py:29-33``): the name, as in the reference."""
+
+    __slots__ = ("name",)
+
+    def __init__(self, name: str) -> None:
+        object.__setattr__(self, "name", name)
+
+    def __setattr__(self, key, value):
+        raise AttributeError("TensorEntry is read-only")
+
+    def __eq__(self, other) -> bool:
+        return isinstance(other, TensorEntry) and other.name == self.name
+
+    def __hash__(self) -> int:
+        return hash(("TensorEntry", self.name))
+
+    def __repr__(self) -> str:
+        return f"TensorEntry(name={self.name!r})"
+
+
 class TensorIndex:
     """Name-indexed random-access loader over a ``.ptwm`` container file."""
 
@@ -445,6 +466,15 @@ class TensorIndex:
     def names(self) -> list[str]:
         return list(self._names)
 
+    def entries(self) -> list[TensorEntry]:
+        """Every entry in write order (``random_access/__init__.py:78-80``)."""
+        return [TensorEntry(n) for n in self._names]
+
+    def entry(self, name: str) -> TensorEntry:
+        if name not in self._handle:
+            raise KeyError(name)
+        return TensorEntry(name)
+
     def get_bytes(self, name: str) -> bytes:
         if name not in self._handle:
             raise KeyError(name)
@@ -469,3 +499,6 @@ class TensorIndex:
 
     def __iter__(self) -> Iterator[str]:
         return iter(self._names)
+
+    def __repr__(self) -> str:
+        return f"TensorIndex(path={self._path!s}, n={len(self)})"

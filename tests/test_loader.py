@@ -234,6 +234,9 @@ def test_tensor_index_opens_files_in_place(tmp_path):
     for name, tensor in idx.stream_tensors([specs[2].name, specs[0].name]):
         assert _bytes_of(tensor) == expected[name]
     assert idx.get_bytes(specs[1].name) == expected[specs[1].name]
+    assert [e.name for e in idx.entries()] == idx.names() and idx.entry(specs[0].name) == ptwm_b200.TensorEntry(specs[0].name)
+    with pytest.raises(KeyError):
+        idx.entry("absent")
     (tmp_path / "junk.ptwm").write_bytes(b"not a container at all")
     with pytest.raises(ValueError):
         ptwm_b200.TensorIndex(tmp_path / "junk.ptwm")
