@@ -150,6 +150,10 @@ class ContainerHandle:
 
     def __init__(self, buffer, skip_missing: bool = False, device: Optional[int] = None, verify: bool = True, prefetch: bool = False,
                  shard: Optional[tuple] = None):
+        resident = None
+        if isinstance(buffer, torch.Tensor) and buffer.is_cuda:  # a container already in device memory: parsed from a host copy, decoded where it lies
+            resident = buffer.contiguous().view(torch.uint8).reshape(-1)
+            buffer = resident.cpu()
         self._host = _as_u8_tensor(buffer)
         self._prefetch = None
         n = self._host.numel()
@@ -185,7 +189,7 @@ class ContainerHandle:
                 if not inf["supported"] and "third-party" in inf["unsupported_reason"]:
                     raise ValueError(f"container references an extension that is not installed: {inf['unsupported_reason']}")
         self._index = {inf["name"]: i for i, inf in enumerate(self._infos)}
-        self._blob_dev: Optional[torch.Tensor] = None
+        self._blob_dev: Optional[torch.Tensor] = resident if resident is not None and resident.device.index == self.device else None
         self._plans: dict = {}
 
     @classmethod

@@ -1090,36 +1090,255 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
 }
 
 // ---- tANS ------------------------------------------------------------------
-// One stream per chunk, so one lane per chunk: a CTA of one warp decodes 32
-// chunks.  Per chunk the decode table is kept as the spread symbols (u8 per
-// state) and (nbits << 11 | baseline) (u16 per state): 6 KiB instead of the
-// 8 KiB of a word per state, 192 KiB per CTA.  Both tables are laid out
-// [state][lane], so the address of an entry is one multiply-add from the
-// state; a lane only touches its own columns (no synchronisation between
-// lanes), and with one warp per SM the few bank conflicts of that layout cost
-// less than a longer address computation on the serial chain would.
+// One stream per chunk, so one lane per chunk, and an entry per state: the
+// spread symbols (u8 per state) and (baseline << 5 | bit count) (u16 per
+// state), 6 KiB per chunk, so an SM holds 32 chunks whatever the kernel does.
+// Both tables are laid out [state][lane]: the address of an entry is one
+// multiply-add from the state and a lane only touches its own columns.
+//
+// With 32 streams an SM's throughput is 32 / (time of one symbol), and a lone
+// warp pays for every instruction it issues, so the work is split over two
+// warps that run on different schedulers.  Warp 0 walks the state chain and
+// nothing else: per symbol one table load, three funnel shifts, the count and
+// the next state, and one store of the state it left into an exchange buffer.
+// Warp 1 turns those states into symbols (the second table), merges them with
+// the other planes' bytes, writes the output and keeps the decoder's window of
+// stream bytes filled.  They meet once per round of 32 symbols per lane, over
+// two exchange buffers in shared memory, on named barriers.  Groups that do
+// not fill a round, plane orders without a placing routine below, and the
+// checked path near a stream's end run on warp 0 alone.
 constexpr int TANS_CTA_CHUNKS = 32;
-constexpr int TANS_SYM_BYTES = 2048 * 32;      // [state][lane] of u8
-constexpr int TANS_NB_BYTES = 2048 * 2 * 32;   // [state][lane] of u16
-constexpr int TANS_SMEM = TANS_SYM_BYTES + TANS_NB_BYTES + RING_SMEM;  // and the per-lane ring of stream bytes
+constexpr int TANS_THREADS = 64;
+constexpr int TANS_SYM_BYTES = 2048 * 32;       // [state][lane] of u8
+constexpr int TANS_NB_BYTES = 2048 * 2 * 32;    // [state][lane] of u16
+constexpr int TANS_RING_WORDS = 64;             // 256 bytes of stream per lane
+constexpr int TANS_RING_BYTES = TANS_RING_WORDS * 32 * 4;
+constexpr int TANS_XCH_BYTES = 2 * 32 * 32 * 2; // [buffer][symbol of the round][lane] of u16
+constexpr int TANS_PUB_BYTES = 2 * 32 * 4;      // [buffer][lane]: read position at the end of the round
+constexpr int TANS_HAND_BYTES = 8 * 32 * 4;     // [word][lane]: rounds, position, lowest stream offset fetched, -, first stream offset, window origin (low, high)
+constexpr int TANS_NORM_BYTES = 256 * 32 * 2;   // [symbol][lane] of u16: normalised counts while the tables are built (in local memory every state would
+                                                // cost an L2 round trip); afterwards the staging area of the other planes' bytes
+constexpr int TANS_SMEM = TANS_SYM_BYTES + TANS_NB_BYTES + TANS_RING_BYTES + TANS_XCH_BYTES + TANS_PUB_BYTES + TANS_HAND_BYTES + TANS_NORM_BYTES;
 
-__global__ void __launch_bounds__(32) tans_decode_kernel(const DecodeItem* __restrict__ items, uint32_t n_items, Bases bases, uint32_t* __restrict__ status) {
+struct TansRing {
+    uint32_t* base;  // &ring[0][lane]
+    __device__ __forceinline__ uint32_t& word(uint32_t off) { return base[((off >> 2) & (TANS_RING_WORDS - 1)) * 32]; }
+    __device__ __forceinline__ uint8_t byte(uint32_t off) { return reinterpret_cast<uint8_t*>(&word(off))[off & 3]; }
+    __device__ __forceinline__ void put(uint32_t off16, uint4 v) {
+        word(off16) = v.x; word(off16 + 4) = v.y; word(off16 + 8) = v.z; word(off16 + 12) = v.w;
+    }
+};
+// How a lane's symbols are placed by the second warp.
+enum : uint32_t { TP_NONE = 0, TP_PLAIN = 1, TP_M16 = 2, TP_FP8 = 3, TP_M32 = 4 };
+__device__ __forceinline__ uint32_t tans_place_mode(const Epilogue& ep) {
+    if (!ep.fused) return TP_PLAIN;
+    if (ep.kind == K_M16) return TP_M16;
+    if (ep.kind == K_E4M3 || ep.kind == K_E5M2) return TP_FP8;
+    if (ep.kind == K_M32 && ep.slot == 3) return TP_M32;
+    return TP_NONE;
+}
+__device__ __forceinline__ uint32_t tans_elem_bytes(uint32_t mode) { return mode == TP_M16 ? 2u : mode == TP_M32 ? 4u : 1u; }
+__device__ __forceinline__ uint32_t tans_partners(uint32_t mode) { return mode == TP_PLAIN ? 0u : mode == TP_M32 ? 3u : 1u; }
+// Rounds of 32 elements that can be placed from `pos` on: the output must sit on a 32-byte boundary and round r reads
+// the aligned 32-byte block r + 2 of every partner plane, which must end inside the partner's chunk.
+__device__ __forceinline__ uint32_t tans_rounds(const Epilogue& ep, uint32_t mode, uint32_t chunk_n, uint32_t pos, uint32_t remaining) {
+    if (mode == TP_NONE) return 0;
+    if ((reinterpret_cast<uintptr_t>(ep.dst) + size_t(pos) * tans_elem_bytes(mode)) & 31) return 0;
+    uint32_t rounds = remaining >> 5;
+    const uint32_t np = tans_partners(mode);
+#pragma unroll
+    for (uint32_t p = 0; p < 3; ++p) {
+        if (p >= np) break;
+        const uintptr_t lo = reinterpret_cast<uintptr_t>(ep.partner[p]), hi = lo + chunk_n;
+        const uintptr_t q = (lo + pos) & ~uintptr_t(31);
+        const uint32_t fit = q + 96 <= hi ? uint32_t((hi - q - 96) >> 5) + 1 : 0;
+        rounds = fit < rounds ? fit : rounds;
+    }
+    return rounds;
+}
+// The two warps of a block meet on named barriers of 64 threads: the warp that filled (or emptied) an exchange
+// buffer arrives, the other one waits.  Every arrival below has exactly one matching wait (both warps run the same
+// number of rounds, taken from the same shared-memory words), and a barrier orders the shared-memory accesses of
+// the threads that take part without waiting for their global loads in flight, which a memory fence would do.
+__device__ __forceinline__ void tans_bar_arrive(uint32_t id) {
+    __syncwarp();
+    asm volatile("bar.arrive %0, 64;" ::"r"(id) : "memory");
+}
+__device__ __forceinline__ void tans_bar_wait(uint32_t id) {
+    __syncwarp();
+    asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory");
+}
+constexpr uint32_t TANS_BAR_FULL = 1, TANS_BAR_EMPTY = 3;  // + buffer index; barrier 0 is __syncthreads
+
+__global__ void __launch_bounds__(TANS_THREADS, 1) tans_decode_kernel(const DecodeItem* __restrict__ items, uint32_t n_items, Bases bases, uint32_t* __restrict__ status) {
     extern __shared__ __align__(16) uint8_t smem[];
-    const uint32_t lane = threadIdx.x;
+    const uint32_t lane = threadIdx.x & 31;
+    const bool placer = threadIdx.x >= 32;  // warp 1
     const uint32_t item_idx = blockIdx.x * TANS_CTA_CHUNKS + lane;
-    if (item_idx >= n_items) return;
-    const DecodeItem it = items[item_idx];
+    const bool live = item_idx < n_items;
+    const DecodeItem it = items[live ? item_idx : 0];
     const uint8_t* src = rd(bases, it.src);
     uint8_t* sym_tab = smem + lane;
     uint8_t* nb_tab = smem + TANS_SYM_BYTES + lane * 2;
-    Ring ring{reinterpret_cast<uint32_t*>(smem + TANS_SYM_BYTES + TANS_NB_BYTES) + lane};
+    uint8_t* area = smem + TANS_SYM_BYTES + TANS_NB_BYTES;
+    TansRing ring{reinterpret_cast<uint32_t*>(area) + lane};
+    uint16_t* xch = reinterpret_cast<uint16_t*>(area + TANS_RING_BYTES) + lane;                       // element (b, j) at xch[(b * 32 + j) * 32]
+    uint32_t* pub = reinterpret_cast<uint32_t*>(area + TANS_RING_BYTES + TANS_XCH_BYTES) + lane;      // buffer b at pub[b * 32]
+    uint32_t* hand = reinterpret_cast<uint32_t*>(area + TANS_RING_BYTES + TANS_XCH_BYTES + TANS_PUB_BYTES) + lane;  // word k at hand[k * 32]
+    uint16_t* norm_tab = reinterpret_cast<uint16_t*>(area + TANS_RING_BYTES + TANS_XCH_BYTES + TANS_PUB_BYTES + TANS_HAND_BYTES) + lane;
+    auto norm = [&](uint32_t sy) -> uint16_t& { return norm_tab[sy << 5]; };
     auto sym_at = [&](uint32_t u) -> uint8_t& { return sym_tab[u << 5]; };
     auto nb_at = [&](uint32_t u) -> uint16_t& { return *reinterpret_cast<uint16_t*>(nb_tab + (u << 6)); };
-    uint32_t err = ST_OK;
+    const Epilogue ep = make_epilogue(bases, it);
+    const uint32_t mode = tans_place_mode(ep);
+    const uintptr_t lo16 = (reinterpret_cast<uintptr_t>(bases.blob) + bases.blob_first) & ~uintptr_t(15);
+    const uintptr_t hi16 = (reinterpret_cast<uintptr_t>(bases.blob) + bases.blob_end + 15) & ~uintptr_t(15);
 
+    // ---- the placing warp -------------------------------------------------------
+    if (placer) {
+        __syncthreads();  // tables built, leading groups placed, the hand-over words written
+        const uint32_t my_rounds = hand[0];
+        const uint32_t max_rounds = __reduce_max_sync(0xFFFFFFFFu, my_rounds);
+        uint32_t pos = hand[32], fetched = hand[2 * 32];
+        const uint32_t start = hand[4 * 32];
+        const uintptr_t org = uintptr_t(hand[5 * 32]) | uintptr_t(hand[6 * 32]) << 32;
+        const uint32_t np = tans_partners(mode);
+        uintptr_t q[3] = {0, 0, 0};
+        uint32_t off[3] = {0, 0, 0};
+        // Nothing this warp asks of global memory is waited for in the round that asked: both the other planes' bytes
+        // and the stream bytes travel by asynchronous copies (cp.async) straight into shared memory, one group of
+        // copies per round, and a round waits for the group issued two rounds earlier.  Partner planes: round r
+        // merges the aligned 32-byte blocks r and r + 1 of each plane and requests block r + 3; block k waits in
+        // slot k & 3 of a staging area (the space the normalised counts used while the tables were built), laid
+        // out [slot][plane][half][lane] in 16-byte units.  Stream bytes go into the decoder's window directly.
+        const uint32_t stage = uint32_t(__cvta_generic_to_shared(area + TANS_RING_BYTES + TANS_XCH_BYTES + TANS_PUB_BYTES + TANS_HAND_BYTES)) + lane * 16;
+        auto stage_at = [&](uint32_t slot, uint32_t p, uint32_t half) -> uint32_t { return stage + (((slot & 3) * 3 + p) * 2 + half) * 512; };
+        auto stage_block = [&](uint32_t slot, uint32_t p) -> Block32 {
+            Block32 v;
+            asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]) : "r"(stage_at(slot, p, 0)) : "memory");
+            asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.w[4]), "=r"(v.w[5]), "=r"(v.w[6]), "=r"(v.w[7]) : "r"(stage_at(slot, p, 1)) : "memory");
+            return v;
+        };
+        const uint32_t ring_sh = uint32_t(__cvta_generic_to_shared(ring.base));
+        Block32 cur[3];
+        uint8_t* out = ep.dst + size_t(pos) * tans_elem_bytes(mode);
+        if (my_rounds) {
+#pragma unroll
+            for (uint32_t p = 0; p < 3; ++p) {
+                if (p >= np) break;
+                const uintptr_t lo = reinterpret_cast<uintptr_t>(ep.partner[p]);
+                q[p] = (lo + pos) & ~uintptr_t(31); off[p] = uint32_t((lo + pos) & 31);
+                cur[p] = load_block_guarded(q[p], lo, lo + it.n);  // block 0 may start below the chunk
+                // blocks 1 and 2: inside the chunk for every lane with a round (tans_rounds)
+#pragma unroll
+                for (uint32_t k = 1; k < 3; ++k)
+#pragma unroll
+                    for (uint32_t h = 0; h < 2; ++h)
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(stage_at(k, p, h)), "l"(q[p] + 32 * k + 16 * h) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");  // so that round 0 waits for the group above like any other round
+        for (uint32_t r = 0; r < max_rounds; ++r) {
+            tans_bar_wait(TANS_BAR_FULL + (r & 1));
+            const uint32_t b = r & 1;
+            if (r < my_rounds) {
+                // Stream bytes: these blocks are visible to the decoder before its round r + 4, by when it is at most
+                // 176 bytes below the position it published, so the window is brought down to 241 - 256 bytes below that.
+                const int32_t floor_off = int32_t(pub[b * 32]) - 256;
+#pragma unroll
+                for (int k = 0; k < 3; ++k) {
+                    if (int32_t(fetched) - 16 >= floor_off && fetched > start) {
+                        fetched -= 16;
+                        const uintptr_t a = org + fetched;
+                        const uint32_t n = (a >= lo16 && a < hi16) ? 4u : 0u;  // outside the blob's hull: zeros, nothing read
+#pragma unroll
+                        for (uint32_t i = 0; i < 4; ++i)
+                            asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(ring_sh + ((((fetched >> 2) + i) & (TANS_RING_WORDS - 1)) * 32) * 4), "l"(a + 4 * i), "r"(n) : "memory");
+                    }
+                }
+                if (r + 3 <= my_rounds) {
+#pragma unroll
+                    for (uint32_t p = 0; p < 3; ++p) {
+                        if (p >= np) break;
+#pragma unroll
+                        for (uint32_t h = 0; h < 2; ++h)
+                            asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(stage_at(r + 3, p, h)), "l"(q[p] + 96 + 16 * h) : "memory");
+                    }
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 2;" ::: "memory");  // the groups of rounds r - 2 and earlier have landed
+            if (r < my_rounds) {
+                uint32_t w[8];
+                const uint16_t* xs = xch + b * 32 * 32;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const uint32_t sy = sym_at(xs[j * 32]);
+                    if ((j & 3) == 0) w[j >> 2] = sy; else w[j >> 2] |= sy << (8 * (j & 3));
+                }
+                uint32_t pw[3][8];
+#pragma unroll
+                for (uint32_t p = 0; p < 3; ++p) {
+                    if (p >= np) break;
+                    const Block32 nxt = stage_block(r + 1, p);
+                    extract32(cur[p], nxt, off[p], pw[p]);
+                    cur[p] = nxt;
+                    q[p] += 32;
+                }
+                if (mode == TP_PLAIN) {
+                    stg256(out, make_uint4(w[0], w[1], w[2], w[3]), make_uint4(w[4], w[5], w[6], w[7]));
+                    out += 32;
+                } else if (mode == TP_M16) {
+                    uint4 v[4];
+                    const bool low_plane = ep.slot == 0;
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        if (low_plane) { compose16x4(w[2 * g], pw[0][2 * g], v[g].x, v[g].y); compose16x4(w[2 * g + 1], pw[0][2 * g + 1], v[g].z, v[g].w); }
+                        else { compose16x4(pw[0][2 * g], w[2 * g], v[g].x, v[g].y); compose16x4(pw[0][2 * g + 1], w[2 * g + 1], v[g].z, v[g].w); }
+                    }
+                    stg256(out, v[0], v[1]);
+                    stg256(out + 32, v[2], v[3]);
+                    out += 64;
+                } else if (mode == TP_FP8) {
+                    const bool high_plane = ep.slot == 0, e4m3 = ep.kind == K_E4M3;
+                    uint32_t v[8];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) v[k] = high_plane ? compose_fp8x4(w[k], pw[0][k], e4m3) : compose_fp8x4(pw[0][k], w[k], e4m3);
+                    stg256(out, make_uint4(v[0], v[1], v[2], v[3]), make_uint4(v[4], v[5], v[6], v[7]));
+                    out += 32;
+                } else {  // TP_M32: bytes 0..2 from the partner planes, byte 3 from this lane (transforms/fusion.rs:287-292)
+#pragma unroll
+                    for (int k = 0; k < 8; k += 2) {
+                        uint32_t v[8];
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const uint32_t t0 = __byte_perm(pw[0][k + h], pw[1][k + h], 0x5140), t1 = __byte_perm(pw[2][k + h], w[k + h], 0x5140);
+                            const uint32_t t2 = __byte_perm(pw[0][k + h], pw[1][k + h], 0x7362), t3 = __byte_perm(pw[2][k + h], w[k + h], 0x7362);
+                            v[4 * h + 0] = revert32(__byte_perm(t0, t1, 0x5410));
+                            v[4 * h + 1] = revert32(__byte_perm(t0, t1, 0x7632));
+                            v[4 * h + 2] = revert32(__byte_perm(t2, t3, 0x5410));
+                            v[4 * h + 3] = revert32(__byte_perm(t2, t3, 0x7632));
+                        }
+                        stg256(out, make_uint4(v[0], v[1], v[2], v[3]), make_uint4(v[4], v[5], v[6], v[7]));
+                        out += 32;
+                    }
+                }
+            }
+            if (r + 2 < max_rounds) tans_bar_arrive(TANS_BAR_EMPTY + b);  // the decoder waits for it before round r + 2
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");  // the stream bytes asked for in the last two rounds
+        hand[2 * 32] = fetched;
+        __syncthreads();  // the rounds are over: the decoding warp takes the window back
+        return;
+    }
+
+    // ---- the decoding warp ------------------------------------------------------
+    uint32_t err = ST_OK;
     // header (mod.rs:388-425)
     uint32_t nsym = 0;
-    if (it.src_len < 3 || src[0] != 11) err = ST_BAD_HEADER;
+    if (!live) err = ST_BAD_HEADER;  // never reported: the lane has no item
+    else if (it.src_len < 3 || src[0] != 11) err = ST_BAD_HEADER;
     else {
         nsym = uint32_t(src[1]) | uint32_t(src[2]) << 8;
         if (nsym < 2 || nsym > 256 || 3 + nsym * 3 + 8 > it.src_len) err = ST_BAD_HEADER;
@@ -1127,155 +1346,229 @@ __global__ void __launch_bounds__(32) tans_decode_kernel(const DecodeItem* __res
     // tables: the spread walks a running position and the decode entries count earlier states of the same
     // symbol, so both are sequential (mod.rs:199-211,346-369); every lane builds its own chunk's
     if (!err) {
-        uint32_t norm[256];
-        for (uint32_t i = 0; i < 256; ++i) norm[i] = 0;
+        for (uint32_t i = 0; i < 256; ++i) norm(i) = 0;
         uint32_t sum = 0;
-        for (uint32_t i = 0; i < nsym; ++i) {
-            uint32_t sy = src[3 + 3 * i], fr = uint32_t(src[4 + 3 * i]) | uint32_t(src[5 + 3 * i]) << 8;
-            if (fr == 0 || norm[sy] != 0) { err = ST_BAD_HEADER; break; }  // mod.rs:404-411
-            norm[sy] = fr;
+        bool bad = false;
+        for (uint32_t i = 0; i < nsym; ++i) {  // no early exit: the loads of later entries need not wait for the checks of earlier ones
+            const uint32_t sy = src[3 + 3 * i], fr = uint32_t(src[4 + 3 * i]) | uint32_t(src[5 + 3 * i]) << 8;
+            bad |= fr == 0 || norm(sy) != 0;  // mod.rs:404-411
+            bad |= fr > 2048;                 // the sum cannot come out right; keeps the 16-bit counters exact
+            if (!bad) norm(sy) = uint16_t(fr);
             sum += fr;
         }
-        if (!err && sum != 2048) err = ST_BAD_HEADER;
+        if (bad || sum != 2048) err = ST_BAD_HEADER;
         if (!err) {
             uint32_t pos = 0;
-            for (uint32_t sy = 0; sy < 256; ++sy)
-                for (uint32_t k = 0; k < norm[sy]; ++k) { sym_at(pos) = uint8_t(sy); pos = (pos + 1283u) & 2047u; }
-            for (uint32_t u = 0; u < 2048; ++u) {
-                uint32_t sy = sym_at(u);
-                uint32_t x = norm[sy]++;
-                uint32_t nb = 11 - (31 - __clz(x));
-                nb_at(u) = uint16_t((((x << nb) - 2048) << 5) | nb);  // baseline above the bit count: a shift by the entry takes its low five bits
+            for (uint32_t sy = 0; sy < 256; ++sy) {
+                const uint32_t f = norm(sy);
+                for (uint32_t k = 0; k < f; ++k) { sym_at(pos) = uint8_t(sy); pos = (pos + 1283u) & 2047u; }
             }
-        }
-    }
-    if (!err) {
-        Epilogue ep = make_epilogue(bases, it);
-        const uint8_t* hp = src + 3 + nsym * 3;
-        const uint64_t total_bits = uint64_t(ld_u32_unaligned(hp)) | uint64_t(ld_u32_unaligned(hp + 4)) << 32;
-        const uint8_t* bs = hp + 8;
-        const uint64_t bslen = it.src_len - (3 + nsym * 3 + 8);
-        if (total_bits > bslen * 8) err = ST_BAD_HEADER;
-        else {
-            // LIFO reader (mod.rs:118-147): the stream is read from its last byte down, every byte from its high bit
-            // down.  The `cnt` unread bits sit at the top of the 64-bit container c_hi:c_lo, the next to be used highest, so taking n bits is
-            // one funnel shift; a word read little-endian from below the read position has its bytes in that order.
-            uint32_t bi = uint32_t((total_bits + 7) >> 3);  // bytes that hold declared bits; the next to load is bs[bi-1]
-            // (the container is two words, so that every shift on the way of a symbol is one funnel shift)
-            uint32_t c_hi = 0, c_lo = 0;
-            int32_t cnt = 0;
-            const uint32_t top = uint32_t(total_bits & 7);
-            if (top) { --bi; c_hi = (bs[bi] & ((1u << top) - 1)) << (32 - top); cnt = int32_t(top); }
-            // Stream bytes pass through a 64-byte ring per lane in shared memory, filled downward in aligned 16-byte
-            // blocks that are requested one step ahead (`pending`).  Positions are 32-bit offsets from `org`, a
-            // 16-byte aligned address two blocks below the stream.  A lane's loads must not be waited for by the other
-            // lanes of the warp (the scoreboard is per warp), so blocks are taken by all lanes with room at once, when
-            // any lane runs low, every few groups.
-            const uintptr_t lo16 = (reinterpret_cast<uintptr_t>(bases.blob) + bases.blob_first) & ~uintptr_t(15);
-            const uintptr_t hi16 = (reinterpret_cast<uintptr_t>(bases.blob) + bases.blob_end + 15) & ~uintptr_t(15);
-            const uintptr_t org = (reinterpret_cast<uintptr_t>(bs) & ~uintptr_t(15)) - 32;
-            const uint32_t start = uint32_t(reinterpret_cast<uintptr_t>(bs) - org);
-            uint32_t rp = start + bi;  // one past the next byte to read (moves down)
-            uint32_t fetched = (rp + 15) & ~15u;
-            for (int k = 0; k < 3; ++k) { fetched -= 16; ring.put(fetched, fetch16(org + fetched, lo16, hi16)); }
-            uint4 pending = fetch16(org + fetched - 16, lo16, hi16);
-            auto ring_top_up = [&]() {
-                if (__any_sync(__activemask(), rp - fetched < 32 && fetched > start)) {
-                    if (rp - fetched <= 48 && fetched > start) { fetched -= 16; ring.put(fetched, pending); pending = fetch16(org + fetched - 16, lo16, hi16); }
-                }
-            };
-            auto refill = [&]() {  // up to more than 32 bits, by bytes until the position is word aligned, then by words
-                while (uint32_t(cnt) <= 32u && rp > start) {  // (a negative count only occurs in a group that is about to be decoded again)
-                    if (rp - start >= 4 && (rp & 3) == 0) {
-                        const uint32_t word = ring.word(rp - 4);
-                        const uint32_t s = uint32_t(32 - cnt);  // 0..32: the word goes below the cnt bits held
-                        c_hi |= __funnelshift_lc(word, 0u, s);
-                        c_lo |= __funnelshift_lc(0u, word, s);
-                        cnt += 32; rp -= 4;
-                    } else {
-                        --rp;
-                        const uint64_t t = uint64_t(ring.byte(rp)) << (56 - cnt);
-                        c_hi |= uint32_t(t >> 32); c_lo |= uint32_t(t);
-                        cnt += 8;
-                    }
-                }
-            };
-            auto take = [&](uint32_t e) -> uint32_t {  // the bit count (<= 11) is the low five bits of e, which is all a funnel shift looks at
-                const uint32_t v = __funnelshift_l(c_hi, 0u, e);  // the top bits; 0 for a count of 0
-                c_hi = __funnelshift_l(c_lo, c_hi, e);
-                c_lo = __funnelshift_l(0u, c_lo, e);
-                cnt -= int32_t(e & 31u);
-                return v;
-            };
-            refill();
-            uint32_t state = 0;
-            if (cnt < 11) err = ST_STREAM_UNDERRUN; else state = take(11);
-            // one symbol with the reference's checks
-            auto one_symbol = [&]() -> uint32_t {
-                refill();
-                const uint32_t sy = sym_at(state), e = nb_at(state), nb = e & 31u;
-                if (int32_t(nb) > cnt) { err = ST_STREAM_UNDERRUN; return sy; }
-                state = (e >> 5) + take(e);
-                if (state >= 2048) { err = ST_STREAM_UNDERRUN; state = 0; }
-                return sy;
-            };
-            // Eight symbols in two halves of four: after a refill the container holds more than 32 bits (unless the
-            // stream is at its end) and four symbols take at most 44, around ten on an exponent plane, so the
-            // halves run unchecked; a group that ran out of bits is decoded again one symbol at a time.
-            auto dec8 = [&](uint32_t& s_lo, uint32_t& s_hi) {
-                const uint32_t hi0 = c_hi, lo0 = c_lo;
-                const int32_t cnt0 = cnt;
-                ring_top_up();
-                const uint32_t rp0 = rp, state0 = state;
-                int32_t lowest = 0;
-                s_lo = 0; s_hi = 0;
-                // Away from the stream's first bytes the read position is word aligned and stays so: a refill is then
-                // one word, taken or not, with no loop and no byte steps.  `lowest` starts negative otherwise, which
-                // sends the group down the checked path.
-                const bool words = (rp & 3) == 0 && rp - start >= 8;
-                if (!words) lowest = -1;
+            // the symbols of eight states are read ahead of the counter updates, which depend on one another through memory
+            for (uint32_t u0 = 0; u0 < 2048; u0 += 8) {
+                uint32_t sy[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    if ((j & 3) == 0 && cnt <= 32) {
-                        const uint32_t word = ring.word(rp - 4);
-                        const uint32_t s = uint32_t(32 - cnt);
-                        c_hi |= __funnelshift_lc(word, 0u, s);
-                        c_lo |= __funnelshift_lc(0u, word, s);
-                        cnt += 32; rp -= 4;
-                    }
-                    const uint32_t sy = sym_at(state), e = nb_at(state);
-                    state = (e >> 5) + take(e);  // below 2048 whatever the stream holds: the baseline has its low bits clear and the stream adds fewer than 2^count
-                    if ((j & 3) == 3) lowest |= cnt;  // the count only falls between two refills
-                    const uint32_t ins = (0x3210u & ~(0xFu << (4 * (j & 3)))) | (4u << (4 * (j & 3)));
-                    if (j < 4) s_lo = __byte_perm(s_lo, sy, ins); else s_hi = __byte_perm(s_hi, sy, ins);
+                for (int i = 0; i < 8; ++i) sy[i] = sym_at(u0 + i);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t x = norm(sy[i]);
+                    norm(sy[i]) = uint16_t(x + 1);
+                    const uint32_t nb = 11 - (31 - __clz(x));
+                    nb_at(u0 + i) = uint16_t((((x << nb) - 2048) << 5) | nb);  // baseline above the bit count: a shift by the entry takes its low five bits
                 }
-                if (lowest < 0) {
-                    c_hi = hi0; c_lo = lo0; cnt = cnt0; rp = rp0; state = state0;
-                    s_lo = 0; s_hi = 0;
-                    for (uint32_t j = 0; j < 8 && !err; ++j) {
-                        uint32_t sy = one_symbol();
-                        if (j < 4) s_lo |= sy << (8 * j); else s_hi |= sy << (8 * (j - 4));
-                    }
-                }
-            };
-            uint32_t pos = 0, remaining = it.n;
-            auto short_group = [&](uint32_t g) {
-                uint64_t syms = 0;
-                ring_top_up();
-                for (uint32_t j = 0; j < g && !err; ++j) syms |= uint64_t(one_symbol()) << (8 * j);
-                emit(ep, pos, g, syms);
-                pos += g; remaining -= g;
-            };
-            if (!err && remaining) {
-                uint32_t g = first_group(ep, pos, remaining);
-                if (g < 8 || remaining < 16) short_group(g);
             }
-            if (!err) fast_groups(ep, it.n, pos, remaining, dec8);
-            while (remaining && !err) short_group(remaining < 8 ? remaining : 8);
-            if (!err && (cnt != 0 || rp != start || state != 0)) err = ST_NOT_CONSUMED;  // mod.rs:442-449
         }
     }
-    if (err) atomicMax(&status[it.id], err);
+    uint64_t total_bits = 0, bslen = 0;
+    const uint8_t* bs = src;
+    if (!err) {
+        const uint8_t* hp = src + 3 + nsym * 3;
+        total_bits = uint64_t(ld_u32_unaligned(hp)) | uint64_t(ld_u32_unaligned(hp + 4)) << 32;
+        bs = hp + 8;
+        bslen = it.src_len - (3 + nsym * 3 + 8);
+        if (total_bits > bslen * 8) err = ST_BAD_HEADER;
+    }
+    // LIFO reader (mod.rs:118-147): the stream is read from its last byte down, every byte from its high bit
+    // down.  The `cnt` unread bits sit at the top of the 64-bit container c_hi:c_lo, the next to be used highest, so taking n bits is
+    // one funnel shift; a word read little-endian from below the read position has its bytes in that order.
+    // (the container is two words, so that every shift on the way of a symbol is one funnel shift)
+    uint32_t c_hi = 0, c_lo = 0;
+    int32_t cnt = 0;
+    // Stream bytes pass through a 256-byte ring per lane in shared memory, filled downward in aligned 16-byte
+    // blocks.  Positions are 32-bit offsets from `org`, a 16-byte aligned address two blocks below the stream.
+    // While this warp decodes alone it requests blocks one step ahead (`pending`); a lane's loads must not be
+    // waited for by the other lanes of the warp (the scoreboard is per warp), so blocks are taken by all lanes
+    // with room at once, when any lane runs low, every few groups.
+    const uintptr_t org = (reinterpret_cast<uintptr_t>(bs) & ~uintptr_t(15)) - 32;
+    const uint32_t start = uint32_t(reinterpret_cast<uintptr_t>(bs) - org);
+    uint32_t rp = start, fetched = start, state = 0;
+    uint4 pending = make_uint4(0, 0, 0, 0);
+    uint32_t pos = 0, remaining = err ? 0 : it.n;
+    auto ring_top_up = [&]() {
+        if (__any_sync(__activemask(), rp - fetched < 32 && fetched > start)) {
+            if (rp - fetched <= 240 && fetched > start) { fetched -= 16; ring.put(fetched, pending); pending = fetch16(org + fetched - 16, lo16, hi16); }
+        }
+    };
+    auto refill = [&]() {  // up to more than 32 bits, by bytes until the position is word aligned, then by words
+        while (uint32_t(cnt) <= 32u && rp > start) {  // (a negative count only occurs in a group that is about to be decoded again)
+            if (rp - start >= 4 && (rp & 3) == 0) {
+                const uint32_t word = ring.word(rp - 4);
+                const uint32_t s = uint32_t(32 - cnt);  // 0..32: the word goes below the cnt bits held
+                c_hi |= __funnelshift_lc(word, 0u, s);
+                c_lo |= __funnelshift_lc(0u, word, s);
+                cnt += 32; rp -= 4;
+            } else {
+                --rp;
+                const uint64_t t = uint64_t(ring.byte(rp)) << (56 - cnt);
+                c_hi |= uint32_t(t >> 32); c_lo |= uint32_t(t);
+                cnt += 8;
+            }
+        }
+    };
+    auto take = [&](uint32_t e) -> uint32_t {  // the bit count (<= 11) is the low five bits of e, which is all a funnel shift looks at
+        const uint32_t v = __funnelshift_l(c_hi, 0u, e);  // the top bits; 0 for a count of 0
+        c_hi = __funnelshift_l(c_lo, c_hi, e);
+        c_lo = __funnelshift_l(0u, c_lo, e);
+        cnt -= int32_t(e & 31u);
+        return v;
+    };
+    // one symbol with the reference's checks
+    auto one_symbol = [&]() -> uint32_t {
+        refill();
+        const uint32_t sy = sym_at(state), e = nb_at(state), nb = e & 31u;
+        if (int32_t(nb) > cnt) { err = ST_STREAM_UNDERRUN; return sy; }
+        state = (e >> 5) + take(e);
+        if (state >= 2048) { err = ST_STREAM_UNDERRUN; state = 0; }
+        return sy;
+    };
+    // a refill by one aligned word, taken when 32 bits or fewer are held
+    auto refill_word = [&]() {
+        if (cnt <= 32) {
+            const uint32_t word = ring.word(rp - 4);
+            const uint32_t s = uint32_t(32 - cnt);
+            c_hi |= __funnelshift_lc(word, 0u, s);
+            c_lo |= __funnelshift_lc(0u, word, s);
+            cnt += 32; rp -= 4;
+        }
+    };
+    // Eight symbols in two halves of four: after a refill the container holds more than 32 bits (unless the
+    // stream is at its end) and four symbols take at most 44, around ten on an exponent plane, so the
+    // halves run unchecked; a group that ran out of bits is decoded again one symbol at a time.
+    auto dec8 = [&](uint32_t& s_lo, uint32_t& s_hi) {
+        const uint32_t hi0 = c_hi, lo0 = c_lo;
+        const int32_t cnt0 = cnt;
+        ring_top_up();
+        const uint32_t rp0 = rp, state0 = state;
+        int32_t lowest = 0;
+        s_lo = 0; s_hi = 0;
+        // Away from the stream's first bytes the read position is word aligned and stays so: a refill is then
+        // one word, taken or not, with no loop and no byte steps.  `lowest` starts negative otherwise, which
+        // sends the group down the checked path.
+        const bool words = (rp & 3) == 0 && rp - start >= 8;
+        if (!words) lowest = -1;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if ((j & 3) == 0) refill_word();
+            const uint32_t sy = sym_at(state), e = nb_at(state);
+            state = (e >> 5) + take(e);  // below 2048 whatever the stream holds: the baseline has its low bits clear and the stream adds fewer than 2^count
+            if ((j & 3) == 3) lowest |= cnt;  // the count only falls between two refills
+            const uint32_t ins = (0x3210u & ~(0xFu << (4 * (j & 3)))) | (4u << (4 * (j & 3)));
+            if (j < 4) s_lo = __byte_perm(s_lo, sy, ins); else s_hi = __byte_perm(s_hi, sy, ins);
+        }
+        if (lowest < 0) {
+            c_hi = hi0; c_lo = lo0; cnt = cnt0; rp = rp0; state = state0;
+            s_lo = 0; s_hi = 0;
+            for (uint32_t j = 0; j < 8 && !err; ++j) {
+                uint32_t sy = one_symbol();
+                if (j < 4) s_lo |= sy << (8 * j); else s_hi |= sy << (8 * (j - 4));
+            }
+        }
+    };
+    auto short_group = [&](uint32_t g) {
+        uint64_t syms = 0;
+        ring_top_up();
+        for (uint32_t j = 0; j < g && !err; ++j) syms |= uint64_t(one_symbol()) << (8 * j);
+        emit(ep, pos, g, syms);
+        pos += g; remaining -= g;
+    };
+    uint32_t rounds = 0;
+    if (!err) {
+        uint32_t bi = uint32_t((total_bits + 7) >> 3);  // bytes that hold declared bits; the next to load is bs[bi-1]
+        const uint32_t top = uint32_t(total_bits & 7);
+        if (top) { --bi; c_hi = (bs[bi] & ((1u << top) - 1)) << (32 - top); cnt = int32_t(top); }
+        rp = start + bi;  // one past the next byte to read (moves down)
+        fetched = (rp + 15) & ~15u;
+        for (int k = 0; k < 15; ++k) { if (fetched <= start) break; fetched -= 16; ring.put(fetched, fetch16(org + fetched, lo16, hi16)); }
+        pending = fetch16(org + fetched - 16, lo16, hi16);
+        refill();
+        if (cnt < 11) err = ST_STREAM_UNDERRUN; else state = take(11);
+        // leading groups, until the elements that follow start on a 32-byte boundary of the output
+        if (!err && remaining) {
+            uint32_t g = first_group(ep, pos, remaining);
+            if (g < 8 || remaining < 16) short_group(g);
+        }
+        const uint32_t eb = tans_elem_bytes(mode);
+        while (!err && mode != TP_NONE && remaining >= 40 && ((reinterpret_cast<uintptr_t>(ep.dst) + size_t(pos) * eb) & 31) != 0) short_group(8);
+        if (!err) rounds = tans_rounds(ep, mode, it.n, pos, remaining);
+        if (rounds) {
+            // hand the window over full: what the second warp adds becomes visible from the fifth round on
+            while (int32_t(fetched) - 16 >= int32_t(rp) - 256 && fetched > start) { fetched -= 16; ring.put(fetched, pending); pending = fetch16(org + fetched - 16, lo16, hi16); }
+        }
+    }
+    hand[0] = rounds; hand[32] = pos; hand[2 * 32] = fetched; hand[4 * 32] = start;
+    hand[5 * 32] = uint32_t(org); hand[6 * 32] = uint32_t(uint64_t(org) >> 32);
+    __syncthreads();
+    {
+        const uint32_t max_rounds = __reduce_max_sync(0xFFFFFFFFu, rounds);
+        for (uint32_t r = 0; r < max_rounds; ++r) {
+            if (r >= 2) tans_bar_wait(TANS_BAR_EMPTY + (r & 1));  // the buffer of round r - 2 has been placed
+            if (r < rounds) {
+                uint16_t* xs = xch + (r & 1) * 32 * 32;
+                const uint32_t hi0 = c_hi, lo0 = c_lo, rp0 = rp, state0 = state;
+                const int32_t cnt0 = cnt;
+                // eight word refills at most: the read position must be word aligned and 32 bytes above the stream's first
+                int32_t lowest = ((rp & 3) == 0 && rp - start >= 32) ? 0 : -1;
+                if (lowest == 0) {
+                    // The word a refill would take is loaded four symbols before the count says whether it is
+                    // taken, so that no shared-memory load sits between a symbol's bits and the next state.
+                    uint32_t ahead_word = ring.word(rp - 4);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if ((j & 3) == 0) {
+                            const bool need = cnt <= 32;
+                            const uint32_t sft = uint32_t(32 - cnt);  // clamped to 32 by the shifts; unused when the word is not taken
+                            const uint32_t in_hi = __funnelshift_lc(ahead_word, 0u, sft), in_lo = __funnelshift_lc(0u, ahead_word, sft);
+                            c_hi |= need ? in_hi : 0u; c_lo |= need ? in_lo : 0u;
+                            cnt += need ? 32 : 0; rp -= need ? 4u : 0u;
+                            ahead_word = ring.word(rp - 4);
+                        }
+                        const uint32_t e = nb_at(state);
+                        xs[j * 32] = uint16_t(state);
+                        state = (e >> 5) + take(e);
+                        if ((j & 3) == 3) lowest |= cnt;
+                    }
+                }
+                if (lowest < 0) {  // near the stream's end, or out of bits: again with the reference's checks
+                    c_hi = hi0; c_lo = lo0; cnt = cnt0; rp = rp0; state = state0;
+                    for (uint32_t j = 0; j < 32; ++j) {
+                        xs[j * 32] = uint16_t(state);
+                        if (!err) one_symbol();
+                    }
+                }
+                pub[(r & 1) * 32] = rp;
+            }
+            tans_bar_arrive(TANS_BAR_FULL + (r & 1));
+        }
+    }
+    __syncthreads();
+    if (rounds) {
+        pos += rounds * 32; remaining -= rounds * 32;
+        fetched = hand[2 * 32];
+        pending = fetch16(org + fetched - 16, lo16, hi16);
+    }
+    if (!err) fast_groups(ep, it.n, pos, remaining, dec8);
+    while (remaining && !err) short_group(remaining < 8 ? remaining : 8);
+    if (!err && (cnt != 0 || rp != start || state != 0)) err = ST_NOT_CONSUMED;  // mod.rs:442-449
+    if (err && live) atomicMax(&status[it.id], err);
 }
 
 // ---- Order1ScaleAC ---------------------------------------------------------

@@ -112,7 +112,7 @@ extern "C" int64_t ptwm_b200_decode_plane_noalloc(uint8_t state_format_version, 
     switch (codec) {
         case C_RANS: rans_decode_kernel_t<false><<<1, 32, rans_smem_bytes(rans_l_entries(255)), st>>>(d_it, 1, bases, d_status, rans_l_entries(255)); break;
         case C_HUFFMAN: huffman_decode_kernel<<<1, 32, HUF_SMEM, st>>>(d_it, 1, bases, d_status); break;
-        case C_TANS: tans_decode_kernel<<<1, 32, TANS_SMEM, st>>>(d_it, 1, bases, d_status); break;
+        case C_TANS: tans_decode_kernel<<<1, TANS_THREADS, TANS_SMEM, st>>>(d_it, 1, bases, d_status); break;
         default: o1sac_decode_kernel<<<1, 32, 0, st>>>(d_it, 1, bases, d_status); break;
     }
     CUDA_TRY(cudaGetLastError());

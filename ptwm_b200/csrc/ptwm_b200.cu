@@ -397,7 +397,7 @@ int64_t enqueue(ptwm_b200_plan& pl, DevicePlan& d, const Bases& bases, uint32_t 
                     break;
                 }
                 case 1: huffman_decode_kernel<<<(n + HUF_WARP_CHUNKS - 1) / HUF_WARP_CHUNKS, 32, HUF_SMEM, st>>>(it, n, bases, status); break;
-                case 2: tans_decode_kernel<<<(n + TANS_CTA_CHUNKS - 1) / TANS_CTA_CHUNKS, 32, TANS_SMEM, st>>>(it, n, bases, status); break;
+                case 2: tans_decode_kernel<<<(n + TANS_CTA_CHUNKS - 1) / TANS_CTA_CHUNKS, TANS_THREADS, TANS_SMEM, st>>>(it, n, bases, status); break;
                 default: o1sac_decode_kernel<<<n, 32, 0, st>>>(it, n, bases, status); break;
             }
             CUDA_TRY(cudaGetLastError());
@@ -573,7 +573,7 @@ int64_t decode_plane_cuda(uint8_t sfv, const uint8_t* state, size_t state_len, c
     switch (codec) {
         case C_RANS: rans_decode_kernel_t<false><<<1, 32, rans_smem_bytes(rans_l_entries(255)), st>>>(d_it, 1, bases, d_status, rans_l_entries(255)); break;
         case C_HUFFMAN: huffman_decode_kernel<<<1, 32, HUF_SMEM, st>>>(d_it, 1, bases, d_status); break;
-        case C_TANS: tans_decode_kernel<<<1, 32, TANS_SMEM, st>>>(d_it, 1, bases, d_status); break;
+        case C_TANS: tans_decode_kernel<<<1, TANS_THREADS, TANS_SMEM, st>>>(d_it, 1, bases, d_status); break;
         default: o1sac_decode_kernel<<<1, 32, 0, st>>>(d_it, 1, bases, d_status); break;
     }
     CUDA_TRY(cudaGetLastError());

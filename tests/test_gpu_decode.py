@@ -297,7 +297,7 @@ def _hard_plane(n, seed):
     return plane.tobytes()
 
 
-@pytest.mark.parametrize("codec", [oracle.RANS, oracle.HUFFMAN])
+@pytest.mark.parametrize("codec", [oracle.RANS, oracle.HUFFMAN, oracle.TANS])
 @pytest.mark.parametrize("offset", [0, 3])
 def test_fused_16bit_leaves_and_reenters_the_fast_loops(codec, offset):
     n = 5 * 65536 + 12345
@@ -312,7 +312,9 @@ def test_fused_16bit_leaves_and_reenters_the_fast_loops(codec, offset):
 
 
 @pytest.mark.parametrize("case", [dict(forced_codec=oracle.RANS, chunk_size=65536), dict(forced_codec=oracle.HUFFMAN, chunk_size=20001, emit_crc=True),
-                                  dict(menu=(oracle.HUFFMAN, oracle.RANS), chunk_size=32768, emit_hash=True), dict(forced_codec=oracle.RANS, chunk_size=20001)])
+                                  dict(menu=(oracle.HUFFMAN, oracle.RANS), chunk_size=32768, emit_hash=True), dict(forced_codec=oracle.RANS, chunk_size=20001),
+                                  dict(forced_codec=oracle.TANS, chunk_size=20001, emit_crc=True), dict(forced_codec=oracle.TANS, chunk_size=65536),
+                                  dict(forced_codec=oracle.TANS, chunk_size=4099)])
 def test_larger_mixed_model_runs_the_round_loops(case):
     """Tensors of several chunks each, chunk sizes that leave every stream and partner plane at an odd address:
     the 32- and 16-element round loops of the 16-bit, fp8 and fp32 paths, their heads and tails."""
@@ -405,6 +407,17 @@ def test_tans_full_size_planes():
     blob = oracle.write_container(specs, chunk_size=65536, forced_codec=oracle.TANS)
     h = ptwm_b200.ContainerHandle(blob, device=0, verify=False)
     assert any(c == oracle.TANS for t in oracle.Container(blob).tensors for c in [p["codec"] for p in t["planes"]])
+    for (name, t), s in zip(h.decode_model(), specs):
+        assert name == s.name and bytes_of(t) == s.raw
+
+
+def test_container_already_in_device_memory():
+    # what the device encoder leaves behind: parsed from a host copy, decoded from where it lies
+    specs = mixed_model()
+    blob = oracle.write_container(specs, chunk_size=4096)
+    on_device = torch.frombuffer(bytearray(blob), dtype=torch.uint8).cuda()
+    h = ptwm_b200.ContainerHandle(on_device, device=0)
+    assert h.blob_on_device().data_ptr() == on_device.data_ptr()
     for (name, t), s in zip(h.decode_model(), specs):
         assert name == s.name and bytes_of(t) == s.raw
 
