@@ -411,6 +411,37 @@ def test_tans_full_size_planes():
         assert name == s.name and bytes_of(t) == s.raw
 
 
+@pytest.mark.parametrize("seed", range(12))
+def test_random_containers(seed):
+    """Seeded random state dicts: tensor count, dtypes, shapes (odd sizes, so streams and partner planes land on
+    every alignment), chunk size, codec and integrity fields all drawn at random; decoded bytes equal the source."""
+    rng = np.random.default_rng(1000 + seed)
+    specs = []
+    for t in range(int(rng.integers(2, 6))):
+        kind = ["bf16", "f16", "f32", "fp8", "u8", "bf16"][int(rng.integers(0, 6))]
+        rows, cols = int(rng.integers(1, 160)), int(rng.integers(1, 3000))
+        if kind == "bf16":
+            specs.append(spec_bf16(f"t{t}.bf16", rows, cols, seed * 10 + t, sigma_rows=bool(rng.integers(0, 2))))
+        elif kind == "f16":
+            w = (torch.randn(rows, cols, generator=torch.Generator().manual_seed(seed * 10 + t)) * 0.02).to(torch.float16)
+            specs.append(oracle.TensorSpec(f"t{t}.f16", oracle.DT_F16, [rows, cols], w.view(torch.uint8).numpy().tobytes()))
+        elif kind == "f32":
+            specs.append(spec_f32(f"t{t}.f32", rows, cols, seed * 10 + t))
+        elif kind == "fp8":
+            specs += specs_fp8(f"t{t}.fp8", rows, cols, seed * 10 + t)
+        else:
+            n = rows * cols
+            specs.append(oracle.TensorSpec(f"t{t}.u8", oracle.DT_U8, [n], ((rng.normal(0, 2.5, n).astype(np.int64) + 100) % 256).astype(np.uint8).tobytes()))
+    case = dict(chunk_size=int(rng.choice([777, 4099, 8192, 20001, 32768, 65536])), emit_crc=bool(rng.integers(0, 2)), emit_hash=bool(rng.integers(0, 2)))
+    pick = int(rng.integers(0, 5))
+    if pick < 3:
+        case["forced_codec"] = [oracle.RANS, oracle.HUFFMAN, oracle.TANS][pick]
+    elif pick == 3:
+        case["menu"] = (oracle.HUFFMAN, oracle.RANS, oracle.TANS)
+    blob = oracle.write_container(specs, **case)
+    check_container(blob, {s.name: s.raw for s in specs})
+
+
 def test_container_already_in_device_memory():
     # what the device encoder leaves behind: parsed from a host copy, decoded from where it lies
     specs = mixed_model()
