@@ -317,6 +317,18 @@ def run_extras(shapes, device, args, peak):
         out[which] = e
         del tensors
         torch.cuda.empty_cache()
+    # the scale planes of a large MXFP4 model: enough Order1ScaleAC chunks to fill every SM several times over
+    scales, usage = {}, {}
+    for i in range(170):
+        blk = sigma_row_weights(14336, 4096, 5000 + i, device).reshape(14336, 128, 32)
+        scales[f"l{i}.scales"] = (127 + torch.ceil(torch.log2(blk.abs().amax(-1).clamp_min(1e-30) / 6.0))).clamp(0, 254).to(torch.uint8).contiguous()
+        usage[f"l{i}.scales"] = "scale"
+        del blk
+    e = measure_case(scales, usage, CompressionConfig(streaming_chunk=args.chunk, codec_menu=full), device, peak, reps=3)
+    e["sample"] = "mx_scales: the E8M0 scale planes of 170 MXFP4 [14336, 4096] projections (312 MB, 9520 chunks), full codec menu: Order1ScaleAC at full occupancy"
+    out["mx_scales"] = e
+    del scales
+    torch.cuda.empty_cache()
     out["l2"] = "a 256 MB buffer is overwritten before every timed pass (config1 and the scale planes are smaller than the 126 MB L2)"
     return out
 

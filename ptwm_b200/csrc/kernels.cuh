@@ -1573,9 +1573,16 @@ __global__ void __launch_bounds__(TANS_THREADS, 1) tans_decode_kernel(const Deco
 
 // ---- Order1ScaleAC ---------------------------------------------------------
 // One range-coder stream per chunk, one warp per chunk.  The warp first turns
-// the chunk's PMFs into cumulative tables in the scratch arena (u16, 257 per
-// context), then decodes the stream together.
-__global__ void __launch_bounds__(32) o1sac_decode_kernel(const DecodeItem* __restrict__ items, uint32_t n_items, Bases bases, uint32_t* __restrict__ status) {
+// the chunk's PMFs into cumulative tables (u16, 256 per context: the count
+// below each symbol), then decodes the stream together: every lane carries the
+// same coder state.  The tables live in shared memory when the launch was
+// given room for the chunk's contexts (`smem_tables`, the largest table count
+// of the launch), else in the scratch arena.
+constexpr uint32_t O1_MAX_SMEM_TABLES = 192;  // 96 KiB; launches with more contexts per chunk keep their tables in global memory
+template <bool SMEM, bool LEAN>
+__global__ void __launch_bounds__(32) o1sac_decode_kernel_t(const DecodeItem* __restrict__ items, uint32_t n_items, Bases bases, uint32_t* __restrict__ status,
+                                                            uint32_t smem_tables) {
+    extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t lane = threadIdx.x;
     const uint32_t item_idx = blockIdx.x;
     if (item_idx >= n_items) return;
@@ -1591,6 +1598,7 @@ __global__ void __launch_bounds__(32) o1sac_decode_kernel(const DecodeItem* __re
         __syncwarp();
         for (int i = 0; i < 32; ++i) pop += __popc(uint32_t(bitmap[i]));
         if (it.state_len != 32 + 512 + pop * 512) err = ST_BAD_STATE;
+        if (SMEM && 1 + pop > smem_tables) err = ST_BAD_STATE;  // the host sized the launch from the same lengths
     }
     if (err) { if (lane == 0) atomicMax(&status[it.id], err); return; }
     // rank of every context (order1_scale_ac.rs:95-103)
@@ -1600,9 +1608,8 @@ __global__ void __launch_bounds__(32) o1sac_decode_kernel(const DecodeItem* __re
         r += __popc(uint32_t(bitmap[p >> 3]) & ((1u << (p & 7)) - 1));
         table_of[p] = ((bitmap[p >> 3] >> (p & 7)) & 1) ? uint16_t(1 + r) : uint16_t(0);
     }
-    // cumulative tables: table t (0 = marginal, 1+r = row r) = 256 u16 at work + t*512 (the count below each symbol;
-    // the total is 4096 by the check below)
-    uint16_t* cum = reinterpret_cast<uint16_t*>(wr(bases, it.work));
+    // cumulative tables: table t (0 = marginal, 1+r = row r) = 256 u16 at cum + t*256; the total is 4096 by the check below
+    uint16_t* cum = SMEM ? reinterpret_cast<uint16_t*>(smem) : reinterpret_cast<uint16_t*>(wr(bases, it.work));
     for (uint32_t t = lane; t < 1 + pop; t += 32) {
         const uint8_t* pm = st + 32 + t * 512;
         uint16_t* ct = cum + t * 256;
@@ -1620,42 +1627,51 @@ __global__ void __launch_bounds__(32) o1sac_decode_kernel(const DecodeItem* __re
     __threadfence_block();
     if (err) { if (lane == 0) atomicMax(&status[it.id], err); return; }
 
-    // The stream is serial, so the warp shares it: every lane carries the same coder state, the search for the
-    // symbol (the largest index whose cumulative count is <= target, order1_scale_ac.rs:474-486) is 256 parallel
-    // probes and three warp reductions instead of eight dependent loads, and lane 0 places the symbols.
+    // The stream is serial, so the warp shares it: one 16-byte load per lane brings the whole table of the context,
+    // every lane counts those of its eight counts that are at or below the target (order1_scale_ac.rs:474-486: the
+    // symbol is the largest index whose count is <= target) and a warp reduction gives the symbol.  Lane 0 places
+    // the symbols.  Two ways to the symbol's count and probability, by the size of the launch: with fewer chunks
+    // than the GPU holds warps a chunk's own chain is what counts, with more the instructions issued are.
     Epilogue ep = make_epilogue(bases, it);
     const uint8_t* src = rd(bases, it.src);
     const uint32_t slen = it.src_len;
-    // range_coder.rs:137-155
-    uint64_t code = 0; uint32_t rpos = 0;
+    // range_coder.rs:137-155: five bytes start the code register, of which the last four count
+    uint32_t code = 0, rpos = 0;
     for (; rpos < 5; ++rpos) code = (code << 8) | (rpos < slen ? src[rpos] : 0);
-    uint32_t low = 0;
-    uint64_t range = 0xFFFFFFFFull;
+    uint32_t low = 0, range = 0xFFFFFFFFu;
     const uint32_t row_len = it.row_len ? it.row_len : (it.n ? it.n : 1);
     uint32_t row_pos = 0; int prev = -1;
     uint64_t pos = 0;
     uint32_t remaining = it.n;
     uint32_t g = remaining ? first_group(ep, pos, remaining) : 0;
-    // the next stream bytes, four at a time, so that renormalising does not wait for memory (zero past the end)
+    // the next stream bytes, four at a time (zero past the end)
     auto next_bytes = [&](uint32_t at) -> uint32_t {
         uint32_t v = 0;
         for (uint32_t k = 0; k < 4; ++k) if (at + k < slen) v |= uint32_t(src[at + k]) << (8 * k);
         return v;
     };
     uint32_t ahead = next_bytes(rpos), ahead_left = 4;
-    while (remaining) {
-        uint64_t syms = 0;
-        for (uint32_t j = 0; j < g; ++j) {
-            if (row_pos == 0) prev = -1;
-            const uint16_t* ct = cum + (prev >= 0 ? uint32_t(table_of[prev]) * 256u : 0u);
-            const uint32_t rpt = uint32_t(range >> 12);  // range / 4096
-            const uint32_t offset = uint32_t(code) - low;
-            // target = min(offset / rpt, 4095) and "count <= target" is "count * rpt <= offset": no division
-            // (counts are below 4096, rpt < 2^20, so the products fit 32 bits).  One 16-byte load per lane brings
-            // the whole table; the symbol is the number of counts that qualify minus one, its count the largest
-            // that qualifies, the next count the smallest that does not (4096 when all do).
-            const uint4 q = *reinterpret_cast<const uint4*>(ct + lane * 8);
-            const uint32_t c[8] = {q.x & 0xFFFFu, q.x >> 16, q.y & 0xFFFFu, q.y >> 16, q.z & 0xFFFFu, q.z >> 16, q.w & 0xFFFFu, q.w >> 16};
+    auto one_symbol = [&]() -> uint32_t {
+        if (row_pos == 0) prev = -1;
+        const uint16_t* ct = cum + (prev >= 0 ? uint32_t(table_of[prev]) * 256u : 0u);
+        const uint4 q = *reinterpret_cast<const uint4*>(ct + lane * 8);  // the lane's eight counts, ascending
+        const uint32_t rpt = range >> 12;  // range / 4096
+        const uint32_t offset = code - low;
+        // target = min(offset / rpt, 4095) and "count <= target" is "count * rpt <= offset": no division
+        // (counts are below 4096, rpt < 2^20, so the products fit 32 bits)
+        const uint32_t c[8] = {q.x & 0xFFFFu, q.x >> 16, q.y & 0xFFFFu, q.y >> 16, q.z & 0xFFFFu, q.z >> 16, q.w & 0xFFFFu, q.w >> 16};
+        uint32_t lo, cumv, nextv;
+        if (LEAN) {
+            // few instructions: count, one reduction, then the symbol's count and the next one read back from the table
+            uint32_t fit = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) fit += c[i] * rpt <= offset ? 1u : 0u;
+            lo = __reduce_add_sync(0xFFFFFFFFu, fit) - 1;  // >= 0: entry 0 is 0
+            cumv = ct[lo];
+            nextv = lo < 255u ? uint32_t(ct[lo + 1]) : 4096u;
+        } else {
+            // short chain: the symbol's count is the largest that qualifies, the next count the smallest that does not
+            // (4096 when all do); three reductions side by side and no second look at the table
             uint32_t fit = 0, below = 0, above = 4096;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -1664,28 +1680,56 @@ __global__ void __launch_bounds__(32) o1sac_decode_kernel(const DecodeItem* __re
                 below = ok ? max(below, c[i]) : below;
                 above = ok ? above : min(above, c[i]);
             }
-            const uint32_t lo = __reduce_add_sync(0xFFFFFFFFu, fit) - 1;  // >= 0: entry 0 is 0
-            const uint32_t cumv = __reduce_max_sync(0xFFFFFFFFu, below);
-            const uint32_t prob = __reduce_min_sync(0xFFFFFFFFu, above) - cumv;
-            low = low + cumv * rpt;  // & 0xFFFFFFFF by width
-            range = uint64_t(prob) * rpt;
-            while (range < (1ull << 24)) {
-                if (ahead_left == 0) { ahead = next_bytes(rpos); ahead_left = 4; }
-                const uint32_t b = ahead & 0xFFu;
-                ahead >>= 8; --ahead_left;
-                ++rpos;
-                code = ((code & 0xFFFFFFFFFFull) << 8) | b;
-                low = (low & 0x00FFFFFFu) << 8;
-                range <<= 8;
-            }
-            syms |= uint64_t(lo) << (8 * j);
-            prev = int(lo);
-            row_pos = row_pos + 1 == row_len ? 0 : row_pos + 1;
+            lo = __reduce_add_sync(0xFFFFFFFFu, fit) - 1;
+            cumv = __reduce_max_sync(0xFFFFFFFFu, below);
+            nextv = __reduce_min_sync(0xFFFFFFFFu, above);
         }
-        if (lane == 0) emit(ep, pos, g, syms);
+        low += cumv * rpt;
+        range = (nextv - cumv) * rpt;
+        while (range < (1u << 24)) {
+            if (ahead_left == 0) { ahead = next_bytes(rpos); ahead_left = 4; }
+            const uint32_t b = ahead & 0xFFu;
+            ahead >>= 8; --ahead_left;
+            ++rpos;
+            code = (code << 8) | b;
+            low <<= 8;
+            range <<= 8;
+        }
+        prev = int(lo);
+        row_pos = row_pos + 1 == row_len ? 0 : row_pos + 1;
+        return lo;
+    };
+    while (remaining) {
+        uint32_t s_lo = 0, s_hi = 0;
+        if (g == 8) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t sy = one_symbol();
+                if (j < 4) s_lo |= sy << (8 * j); else s_hi |= sy << (8 * (j - 4));
+            }
+        } else {
+            for (uint32_t j = 0; j < g; ++j) {
+                const uint32_t sy = one_symbol();
+                if (j < 4) s_lo |= sy << (8 * j); else s_hi |= sy << (8 * (j - 4));
+            }
+        }
+        if (lane == 0) emit(ep, pos, g, uint64_t(s_lo) | uint64_t(s_hi) << 32);
         pos += g; remaining -= g;
         g = remaining < 8 ? remaining : 8;
     }
+}
+
+// Tables of a chunk whose state has `state_len` bytes (0 when the state is too short to hold any).
+inline uint32_t o1sac_tables(uint64_t state_len) { return state_len >= 32 + 512 ? uint32_t((state_len - 32 - 512) / 512) + 1 : 0; }
+// `tables` = the largest table count among the items.  A launch that fills the GPU several times over runs the variant
+// with fewer instructions and its tables in shared memory (when they fit); a smaller one the variant with the shorter chain.
+constexpr uint32_t O1_LEAN_FROM_ITEMS = 1024;  // about seven warps per SM: 2016 chunks measured 8.7 ms this way against 10.4 ms the other, 168 chunks 6.9 against 6.3
+inline void o1sac_launch(const DecodeItem* items, uint32_t n, const Bases& bases, uint32_t* status, uint32_t tables, cudaStream_t st) {
+    if (n >= O1_LEAN_FROM_ITEMS && tables && tables <= O1_MAX_SMEM_TABLES) o1sac_decode_kernel_t<true, true><<<n, 32, tables * 512, st>>>(items, n, bases, status, tables);
+    else o1sac_decode_kernel_t<false, false><<<n, 32, 0, st>>>(items, n, bases, status, 0);
+}
+inline cudaError_t o1sac_allow_shared_tables() {
+    return cudaFuncSetAttribute(o1sac_decode_kernel_t<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(O1_MAX_SMEM_TABLES * 512));
 }
 
 // ---- stand-alone merge / copy ---------------------------------------------

@@ -34,6 +34,7 @@ int64_t noalloc_scratch_for(int device, uint8_t** out) {
         CUDA_TRY(cudaFuncSetAttribute(rans_decode_kernel_t<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(rans_smem_bytes(rans_l_entries(255)))));
         CUDA_TRY(cudaFuncSetAttribute(huffman_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, HUF_SMEM));
         CUDA_TRY(cudaFuncSetAttribute(tans_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TANS_SMEM));
+        CUDA_TRY(o1sac_allow_shared_tables());
         it = g_noalloc_ptr.emplace(device, static_cast<uint8_t*>(p)).first;
     }
     *out = it->second;
@@ -113,7 +114,7 @@ extern "C" int64_t ptwm_b200_decode_plane_noalloc(uint8_t state_format_version, 
         case C_RANS: rans_decode_kernel_t<false><<<1, 32, rans_smem_bytes(rans_l_entries(255)), st>>>(d_it, 1, bases, d_status, rans_l_entries(255)); break;
         case C_HUFFMAN: huffman_decode_kernel<<<1, 32, HUF_SMEM, st>>>(d_it, 1, bases, d_status); break;
         case C_TANS: tans_decode_kernel<<<1, TANS_THREADS, TANS_SMEM, st>>>(d_it, 1, bases, d_status); break;
-        default: o1sac_decode_kernel<<<1, 32, 0, st>>>(d_it, 1, bases, d_status); break;
+        default: o1sac_launch(d_it, 1, bases, d_status, o1sac_tables(state_len), st); break;
     }
     CUDA_TRY(cudaGetLastError());
     uint32_t status = 0;

@@ -51,6 +51,7 @@ int64_t device_state(int dev, DeviceState** out) {
         CUDA_TRY(cudaFuncSetAttribute(rans_decode_kernel_t<true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         CUDA_TRY(cudaFuncSetAttribute(huffman_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, HUF_SMEM));
         CUDA_TRY(cudaFuncSetAttribute(tans_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TANS_SMEM));
+        CUDA_TRY(o1sac_allow_shared_tables());
         // the decoders are limited by how many chunk tables fit in an SM: ask for the largest shared-memory carve-out
         CUDA_TRY(cudaFuncSetAttribute(rans_decode_kernel_t<false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         CUDA_TRY(cudaFuncSetAttribute(huffman_decode_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
@@ -124,6 +125,7 @@ struct ptwm_b200_plan {
     // rANS chunks per phase: the first `rans_narrow` items hold few distinct symbols and go to the kernel with a symbol
     // list per lane (`rans_rows` rows); the rest go to the general kernel, whose shared list is sized by the most distinct symbols among them.
     uint32_t rans_wide_distinct[2] = {0, 0}, rans_narrow[2] = {0, 0}, rans_rows[2] = {0, 0};
+    uint32_t o1_tables[2] = {0, 0};  // most cumulative tables among the Order1ScaleAC chunks of a phase
     uint64_t slot_bytes[12] = {0};
     uint32_t slot_items[12] = {0};
     std::mutex mu;
@@ -274,6 +276,7 @@ void finish_lists(ptwm_b200_plan& pl) {
                 pl.rans_rows[ph] = most + 2;
                 if (pl.rans_narrow[ph] && pl.rans_narrow[ph] < v.size()) pl.launches++;
             }
+            if (cc == 3) for (auto& it : v) pl.o1_tables[ph] = std::max(pl.o1_tables[ph], o1sac_tables(it.state_len));
             for (auto& it : v) {
                 uint64_t np = it.fused ? uint64_t(kind_planes(it.kind)) : 1, eb = it.fused ? uint64_t(kind_elem_bytes(it.kind)) : 1;
                 pl.slot_bytes[slot] += uint64_t(it.src_len) + it.state_len + uint64_t(it.n) * (np - 1) + uint64_t(it.n) * eb;
@@ -398,7 +401,7 @@ int64_t enqueue(ptwm_b200_plan& pl, DevicePlan& d, const Bases& bases, uint32_t 
                 }
                 case 1: huffman_decode_kernel<<<(n + HUF_WARP_CHUNKS - 1) / HUF_WARP_CHUNKS, 32, HUF_SMEM, st>>>(it, n, bases, status); break;
                 case 2: tans_decode_kernel<<<(n + TANS_CTA_CHUNKS - 1) / TANS_CTA_CHUNKS, TANS_THREADS, TANS_SMEM, st>>>(it, n, bases, status); break;
-                default: o1sac_decode_kernel<<<n, 32, 0, st>>>(it, n, bases, status); break;
+                default: o1sac_launch(it, n, bases, status, pl.o1_tables[ph], st); break;
             }
             CUDA_TRY(cudaGetLastError());
             CUDA_TRY(mark(ph * 5 + cc, 1));
@@ -574,7 +577,7 @@ int64_t decode_plane_cuda(uint8_t sfv, const uint8_t* state, size_t state_len, c
         case C_RANS: rans_decode_kernel_t<false><<<1, 32, rans_smem_bytes(rans_l_entries(255)), st>>>(d_it, 1, bases, d_status, rans_l_entries(255)); break;
         case C_HUFFMAN: huffman_decode_kernel<<<1, 32, HUF_SMEM, st>>>(d_it, 1, bases, d_status); break;
         case C_TANS: tans_decode_kernel<<<1, TANS_THREADS, TANS_SMEM, st>>>(d_it, 1, bases, d_status); break;
-        default: o1sac_decode_kernel<<<1, 32, 0, st>>>(d_it, 1, bases, d_status); break;
+        default: o1sac_launch(d_it, 1, bases, d_status, o1sac_tables(state_len), st); break;
     }
     CUDA_TRY(cudaGetLastError());
     uint32_t status = 0;

@@ -442,6 +442,22 @@ def test_random_containers(seed):
     check_container(blob, {s.name: s.raw for s in specs})
 
 
+def test_many_scale_chunks_take_the_low_instruction_coder():
+    # more Order1ScaleAC chunks than the launch-size threshold of the decoder: the variant with its tables in shared memory
+    rng = np.random.default_rng(77)
+    rows, cols = 2304, 512
+    walk = (120 + np.cumsum(rng.integers(-1, 2, (rows, cols)), axis=1) // 8 + rng.integers(0, 3, (rows, 1))).clip(0, 254).astype(np.uint8)
+    specs = [oracle.TensorSpec("big.scales", oracle.DT_U8, [rows, cols], walk.tobytes(), usage="scale"),
+             oracle.TensorSpec("tail.scales", oracle.DT_U8, [3, 100], walk[:3, :100].tobytes(), usage="scale")]
+    blob = oracle.write_container(specs, chunk_size=512, forced_codec=oracle.O1SAC)
+    h, _ = check_container(blob, {s.name: s.raw for s in specs})
+    plan = h.plan()
+    out = torch.empty(plan.out_bytes, dtype=torch.uint8, device="cuda:0")
+    scratch = torch.empty(max(plan.scratch_bytes, 1), dtype=torch.uint8, device="cuda:0")
+    plan.run(h.blob_on_device(), out, scratch, flags=ptwm_b200.TIME_KERNELS)
+    assert sum(v[2] for k, v in plan.timings(0).items() if k.startswith("o1sac")) >= 2048
+
+
 def test_container_already_in_device_memory():
     # what the device encoder leaves behind: parsed from a host copy, decoded from where it lies
     specs = mixed_model()
