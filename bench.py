@@ -537,11 +537,25 @@ def run_ours(args):
             if it >= 2:
                 rep_times.append(float(dt.item()))
             n_rep = len(decoded)
+            if it == 0 and not args.no_check:
+                # every tensor of the replica against its owner's device-resident decode (checked against the source above):
+                # 32-bit word sums, the owners' gathered by a sum over ranks
+                def word_sum(t):
+                    b = t.contiguous().view(torch.uint8).reshape(-1)
+                    n4 = b.numel() // 4 * 4
+                    return int(b[:n4].view(torch.int32).sum(dtype=torch.int64).item()) + int(b[n4:].sum(dtype=torch.int64).item())
+                got = torch.tensor([word_sum(t) for _, t in decoded], device=device, dtype=torch.int64)
+                own = torch.zeros(len(infos), device=device, dtype=torch.int64)
+                for i, view in zip(mine, plan.views(out)):
+                    own[i] = word_sum(view)
+                dist.all_reduce(own, op=dist.ReduceOp.SUM)
+                if got.numel() != own.numel() or not torch.equal(got, own):
+                    raise SystemExit(f"rank {rank}: replica decode differs from the owners' decode")
             del decoded
         sec = statistics.mean(rep_times)
         replica = {"value": raw_total / sec / 1e9, "unit": "GB/s per replica", "ms_per_step": sec * 1e3, "tensors_per_rank": n_rep,
                    "nvlink_bytes_received_per_rank": int(nvlink), "h2d_bytes_per_rank": int(compressed - nvlink),
-                   "includes": "per rank: H2D of its span of the compressed container (1 / N of it), one NCCL broadcast per owner into place, one full local decode; container already parsed"}
+                   "includes": "per rank: H2D of its span of the compressed container (1 / N of it), the spans exchanged in four slices each (one NCCL broadcast per slice and owner, into place, while later slices are still crossing PCIe), one full local decode; container already parsed"}
         del hr
 
     # ---- optional: the same container as a file (page cache warm) -> load_file --------------------------------

@@ -73,6 +73,17 @@ def replica_spans(infos: Sequence[dict], world: int) -> list[tuple[int, int]]:
     return spans
 
 
+REPLICA_SLICES = 4
+
+
+def span_slices(a: int, b: int, pieces: int = REPLICA_SLICES, align: int = 1 << 20) -> list[tuple[int, int]]:
+    """[a, b) cut into at most `pieces` contiguous parts of equal length (a multiple of `align`, the last one shorter), none empty."""
+    if b <= a:
+        return []
+    step = -(-(-(-(b - a) // pieces)) // align) * align
+    return [(x, min(b, x + step)) for x in range(a, b, step)]
+
+
 def all_gather_compressed(host_blob: torch.Tensor, infos: Sequence[dict], group=None, device=None):
     """Every rank ends up with file bytes [lo, hi) of the container in its own
     memory: it copies its own span from `host_blob` (the container in host
@@ -88,14 +99,43 @@ def all_gather_compressed(host_blob: torch.Tensor, infos: Sequence[dict], group=
     dev = torch.device("cpu") if device is None else torch.device("cuda", int(device))
     buf = torch.empty(max(hi - lo, 1), dtype=torch.uint8, device=dev)
     a, b = spans[rank]
-    if b > a:
-        buf[a - lo:b - lo].copy_(host_blob[a:b], non_blocking=True)
-    received = 0
-    if world > 1:
-        for r, (ra, rb) in enumerate(spans):
-            if rb > ra:
-                dist.broadcast(buf[ra - lo:rb - lo], src=dist.get_global_rank(group, r) if group is not None else r, group=group)
-                received += (rb - ra) if r != rank else 0
+    received = sum(rb - ra for r, (ra, rb) in enumerate(spans) if r != rank) if world > 1 else 0
+
+    def src_of(r):
+        return dist.get_global_rank(group, r) if group is not None else r
+
+    if device is None or world == 1:
+        if b > a:
+            buf[a - lo:b - lo].copy_(host_blob[a:b], non_blocking=True)
+        if world > 1:
+            for r, (ra, rb) in enumerate(spans):
+                if rb > ra:
+                    dist.broadcast(buf[ra - lo:rb - lo], src=src_of(r), group=group)
+        return buf, lo, received
+    # On GPUs a span travels in slices: slice k of every span is broadcast while slice k + 1 is still crossing PCIe,
+    # so NVLink works beside the host copies instead of after them.  The cuts are a function of the span alone:
+    # every rank makes the same calls in the same order.
+    copier = torch.cuda.Stream(dev)
+    buf.record_stream(copier)
+    landed = []
+    with torch.cuda.stream(copier):
+        copier.wait_stream(torch.cuda.current_stream(dev))
+        for sa, sb in span_slices(a, b):
+            buf[sa - lo:sb - lo].copy_(host_blob[sa:sb], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(copier)
+            landed.append(ev)
+    cuts = [span_slices(ra, rb) for ra, rb in spans]
+    works = []
+    for k in range(max((len(c) for c in cuts), default=0)):
+        for r in range(world):
+            if k < len(cuts[r]):
+                sa, sb = cuts[r][k]
+                if r == rank:
+                    torch.cuda.current_stream(dev).wait_event(landed[k])  # the collective starts after what the current stream waits for
+                works.append(dist.broadcast(buf[sa - lo:sb - lo], src=src_of(r), group=group, async_op=True))
+    for w in works:
+        w.wait()
     return buf, lo, received
 
 

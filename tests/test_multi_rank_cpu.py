@@ -140,3 +140,14 @@ def test_replica_spans_edge_cases():
     many = replica_spans(infos, 4)  # more ranks than tensors: the extra ranks bring nothing
     assert many[0][0] == 100 and many[-1][1] == 150 and all(a <= b for a, b in many) and all(many[i][1] == many[i + 1][0] for i in range(3))
     assert replica_spans([], 3) == [(0, 0)] * 3
+
+
+def test_span_slices_tile_the_span():
+    from ptwm_b200.sharding import REPLICA_SLICES, span_slices
+    for a, b in [(0, 0), (5, 6), (100, 5_000_100), (123_456_789, 1_423_456_789), (0, 1 << 20), (7, (1 << 20) + 9), (3, 3 + 4 * (1 << 20) + 1)]:
+        cuts = span_slices(a, b)
+        assert len(cuts) <= REPLICA_SLICES
+        if a == b:
+            assert cuts == []
+            continue
+        assert cuts[0][0] == a and cuts[-1][1] == b and all(x[1] == y[0] for x, y in zip(cuts, cuts[1:])) and all(y > x for x, y in cuts)
