@@ -220,6 +220,9 @@ typedef struct ptwm_b200_encode_options {
 } ptwm_b200_encode_options;
 #define PTWM_B200_TRY_INTDELTA 1u   /* split + IntDelta on the exponent plane */
 #define PTWM_B200_TRY_MZS      2u   /* split + MantissaZeroStrip(k), k = 1..4, on mantissa plane 0 */
+#define PTWM_B200_TRY_SHARED_STATE 4u /* whole planes only (chunk_size = PTWM_B200_CHUNK_NONE), codec chosen from the menu: fit shared Order1ScaleAC states over all
+                                         scale planes (clusters chosen by description length), write them to the prelude, and let every scale plane code
+                                         against one of them when that is smaller (compressor.rs:834-939, fit/order1.rs) */
 
 typedef struct ptwm_b200_encoded ptwm_b200_encoded;
 
@@ -284,6 +287,14 @@ int64_t ptwm_b200_plan_timings(ptwm_b200_plan* p, uint32_t device_ordinal, float
 /* CRC-32 computed the way the verification kernel does it (per-run remainders,
  * GF(2) shifts, XOR fold), on the host, for testing that arithmetic without a GPU. */
 uint32_t ptwm_b200_crc32_by_runs(const uint8_t* data, size_t len, size_t run);
+
+/* The shared-state fit of the encoder (PTWM_B200_TRY_SHARED_STATE) on planes in host memory, with the pairwise
+ * distances of the GPU kernel computed by the same arithmetic in a host loop: for testing the counting, the states,
+ * the clustering and the choice of the cluster count without a GPU (fit/order1.rs).  planes[k] has lens[k] bytes in
+ * rows of row_lens[k].  Returns the number of shared states (0..8); their serialized bytes are written back to back to
+ * `out` and their lengths to state_lens[0..]; -2 when `cap` is too small. */
+int64_t ptwm_b200_fit_shared_states_host(const uint8_t* const* planes, const uint64_t* lens, const uint32_t* row_lens, size_t n, uint8_t* out, size_t cap,
+                                         uint32_t state_lens[8]);
 
 #ifdef __cplusplus
 }

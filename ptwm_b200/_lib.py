@@ -86,6 +86,8 @@ _SIGNATURES = {
     "ptwm_b200_decode_plane_noalloc": (C.c_int64, [C.c_uint8, C.c_void_p, C.c_size_t, C.c_char_p, C.c_size_t, C.c_uint64, C.c_size_t, C.c_uint64,
                                                    C.c_size_t, C.c_uint32, C.c_uint64]),
     "ptwm_b200_crc32_by_runs": (C.c_uint32, [C.c_char_p, C.c_size_t, C.c_size_t]),
+    "ptwm_b200_fit_shared_states_host": (C.c_int64, [C.POINTER(C.c_char_p), C.POINTER(C.c_uint64), C.POINTER(C.c_uint32), C.c_size_t, C.c_void_p, C.c_size_t,
+                                                     C.POINTER(C.c_uint32)]),
     "ptwm_hardware_backend_v1_cuda_stream_handle": (C.c_uint64, [C.c_uint32]),
     "ptwm_plane_codec_v1_cuda_stream_handle": (C.c_uint64, [C.c_uint32]),
     "ptwm_hardware_backend_v1_dispatch_decode_cuda": (C.c_int64, [C.c_uint8, C.c_void_p, C.c_size_t, C.c_char_p, C.c_size_t, C.c_uint64, C.c_size_t,
@@ -122,6 +124,25 @@ def lib():
 
 def last_error() -> str:
     return lib().ptwm_b200_last_error().decode("utf-8", "replace")
+
+
+def fit_shared_states_host(planes, row_lens) -> list[bytes]:
+    """The encoder's shared Order1ScaleAC states for these planes (bytes objects, rows of row_lens[k]), fitted on the host."""
+    n = len(planes)
+    arr = (C.c_char_p * n)(*[bytes(p) for p in planes])
+    lens = (C.c_uint64 * n)(*[len(p) for p in planes])
+    rows = (C.c_uint32 * n)(*[int(r) for r in row_lens])
+    cap = 8 * (32 + 512 + 512 * 256)
+    out = C.create_string_buffer(cap)
+    state_lens = (C.c_uint32 * 8)()
+    k = lib().ptwm_b200_fit_shared_states_host(arr, lens, rows, n, out, cap, state_lens)
+    if k < 0:
+        raise RuntimeError(last_error())
+    states, pos = [], 0
+    for i in range(k):
+        states.append(out.raw[pos:pos + state_lens[i]])
+        pos += state_lens[i]
+    return states
 
 
 def xxh64(data: bytes) -> int:

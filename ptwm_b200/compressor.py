@@ -42,6 +42,11 @@ class CompressionConfig:
     # exponent plane; "mzs": MantissaZeroStrip(1..4) on mantissa plane 0); the smallest total wins, the plain split on ties
     # (the reference's STANDARD candidate lists, python/ptwm/preprocessing/_chains.py:1151-1185, as far as the decoder goes).
     candidate_chains: Sequence[str] = ()
+    # The writer's passes 2 and 3 (compressor.rs:834-939): Order1ScaleAC states fitted over all scale planes of the model
+    # (clustered, the cluster count chosen by description length), stored once in the container's prelude, and used by
+    # every scale plane whose payload comes out smaller that way.  Whole planes only (streaming_chunk=None) and only when
+    # the codec is chosen from the menu; ignored otherwise, as in the reference.
+    shared_states: bool = False
     forced_codec: Optional[int] = None
     emit_plane_crc: bool = False
     emit_payload_hash: bool = False
@@ -140,6 +145,8 @@ def compress_model(tensors: Mapping[str, torch.Tensor], config: Optional[Compres
         if c not in ("intdelta", "mzs"):
             raise ValueError(f"candidate chain {c!r} is not offered by the device encoder (intdelta, mzs)")
         tries |= 1 if c == "intdelta" else 2
+    if cfg.shared_states:
+        tries |= 4
     opt = _lib.EncodeOptions(_CHUNK_NONE if cfg.streaming_chunk is None else int(cfg.streaming_chunk), menu, -1 if cfg.forced_codec is None else int(cfg.forced_codec), int(cfg.emit_plane_crc),
                              int(cfg.emit_payload_hash), tries)
     torch.cuda.current_stream(dev).synchronize()

@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "encode.cuh"
+#include "shared_fit.cuh"
 #include "format.hpp"
 #include "host_common.hpp"
 
@@ -83,6 +84,7 @@ struct PlanePlan {
     // layout
     std::vector<uint64_t> frame_size;  // per chunk (or one entry for an empty plane)
     uint64_t payload_len = 0, state_len = 0;  // state_len: inline state of an unchunked Order1ScaleAC plane
+    int shared = -1;         // Order1ScaleAC against this shared state of the prelude instead of a state of its own
 };
 struct TensorPlan {
     ChainDef chain;
@@ -345,9 +347,11 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
 
     // Lag-1 counts of every plane Order1ScaleAC accepts, with the plane's rows, for the size comparison below.
     std::vector<double> o1sac_size(n_planes, -1.0);
+    std::vector<uint32_t> counts, which;      // the counts stay for the shared-state passes
+    std::vector<int> counts_of(n_planes, -1); // plane -> its place in `which`
     if (opt.forced_codec < 0 && (menu & PTWM_B200_MENU_O1SAC)) {
         std::vector<EncChunk> whole;
-        std::vector<uint32_t> which, list;
+        std::vector<uint32_t> list;
         uint32_t pi = 0;
         for (auto& tp : plan) for (auto& pp : tp.planes) {
             if (pp.len && o1sac_accepts(pp.role, pp.row_len) && pp.len % pp.row_len == 0) {
@@ -365,20 +369,49 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
             CUDA_TRY(cudaMemsetAsync(d_counts.p, 0, whole.size() * size_t(O1E_PRESENT), st));
             o1sac_count_kernel<<<uint32_t(whole.size()), 256, 0, st>>>(d_whole.as<EncChunk>(), d_list.as<uint32_t>(), d_planes.as<uint8_t>(), d_counts.as<uint8_t>());
             CUDA_TRY(cudaGetLastError());
-            std::vector<uint32_t> counts(whole.size() * size_t(O1E_PRESENT / 4));
+            counts.resize(whole.size() * size_t(O1E_PRESENT / 4));
             CUDA_TRY(cudaMemcpyAsync(counts.data(), d_counts.p, counts.size() * 4, cudaMemcpyDeviceToHost, st));
             CUDA_TRY(cudaStreamSynchronize(st));
             for (size_t k = 0; k < whole.size(); ++k) {
                 const uint32_t* base = counts.data() + k * size_t(O1E_PRESENT / 4);
                 o1sac_size[which[k]] = o1sac_estimate(base + O1E_JOINT / 4, base + O1E_MARG / 4);
+                counts_of[which[k]] = int(k);
             }
         }
     }
     CUDA_TRY(cudaStreamSynchronize(st));
 
+    // ---- shared states (compressor.rs:834-881): only whole planes can use one (a chunked plane carries its states inline,
+    //      compressor.rs:324-381), and only when the codec is chosen, not forced
+    FitResult shared;
+    std::vector<std::vector<uint8_t>> shared_bytes;
+    if (!chunked && opt.forced_codec < 0 && (opt.candidates & PTWM_B200_TRY_SHARED_STATE) && !which.empty()) {
+        std::vector<FitCounts> fc;
+        for (size_t k = 0; k < which.size(); ++k) {
+            const uint32_t* base = counts.data() + k * size_t(O1E_PRESENT / 4);
+            fc.push_back(FitCounts{base + O1E_JOINT / 4, base + O1E_MARG / 4});
+        }
+        cudaError_t fit_err = cudaSuccess;
+        shared = fit_shared_order1(fc, [&](const std::vector<FitState>& own, const std::vector<uint32_t>& pairs) {
+            std::vector<double> d(pairs.size() / 2, 0.0);
+            std::vector<uint16_t> dense(own.size() * size_t(257 * 256));
+            for (size_t k = 0; k < own.size(); ++k) fit_dense_rows(own[k], dense.data() + k * size_t(257 * 256));
+            DeviceBuf d_dense, d_pairs, d_dist;
+            if ((fit_err = upload_vec(d_dense, dense, st)) != cudaSuccess || (fit_err = upload_vec(d_pairs, pairs, st)) != cudaSuccess ||
+                (fit_err = d_dist.alloc(d.size() * sizeof(double))) != cudaSuccess) return d;
+            fit_pair_distance_kernel<<<uint32_t(d.size()), 256, 0, st>>>(d_dense.as<uint16_t>(), d_pairs.as<uint32_t>(), d_dist.as<double>());
+            if ((fit_err = cudaGetLastError()) != cudaSuccess) return d;
+            if ((fit_err = cudaMemcpyAsync(d.data(), d_dist.p, d.size() * sizeof(double), cudaMemcpyDeviceToHost, st)) != cudaSuccess) return d;
+            fit_err = cudaStreamSynchronize(st);
+            return d;
+        });
+        CUDA_TRY(fit_err);
+        for (auto& stt : shared.states) shared_bytes.push_back(stt.serialize());
+    }
+
     // ---- codec per plane ------------------------------------------------------
     std::vector<uint8_t> plane_codec(n_planes);
-    std::vector<uint32_t> o1sac_chunks;
+    std::vector<uint32_t> o1sac_chunks, o1shared_chunks, o1shared_state;  // chunks that fit their own state / that code against shared state o1shared_state[k]
     uint64_t tables_bytes = 0;
     std::vector<std::pair<uint32_t, uint32_t>> recrc;  // (tensor, accumulator) of planes shifted by MantissaZeroStrip: their CRC is taken again below
     {
@@ -398,6 +431,17 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
             for (size_t p = 0; p < np; ++p) {
                 tp.planes[p].codec = pick(tp.first_plane + uint32_t(p), &plane_hist[size_t(tp.first_plane + p) * 256], tp.planes[p].len, &size[p]);
                 if (tp.planes[p].codec < 0) return fail(PTWM_RC_INVALID_INPUT, "empty codec menu");
+                // the same plane against every shared state, in prelude order: such a payload carries no state, and the first
+                // strictly smaller candidate wins (compressor.rs:883-939, select.rs:27-64)
+                const int ck = counts_of[tp.first_plane + p];
+                if (ck >= 0 && !shared.states.empty()) {
+                    const uint32_t* base = counts.data() + size_t(ck) * size_t(O1E_PRESENT / 4);
+                    const FitCounts fc{base + O1E_JOINT / 4, base + O1E_MARG / 4};
+                    for (size_t sj = 0; sj < shared.states.size(); ++sj) {
+                        const double est = std::ceil(fit_cross_entropy_bits(fc, shared.states[sj]) / 8) + 6;
+                        if (est < size[p]) { size[p] = est; tp.planes[p].codec = C_O1SAC; tp.planes[p].shared = int(sj); }
+                    }
+                }
             }
             // ---- chain: the plain split, or the candidate with the smallest total, the first in the reference's candidate order on ties
             //      (split, IntDelta, MantissaZeroStrip 1..4: python/ptwm/preprocessing/_chains.py:1151-1185; compressor.rs:504-665)
@@ -463,7 +507,8 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
                         EncChunk& ch = chunks[pp.first_chunk + k];
                         ch.slot_off = slots_bytes; slots_bytes += uint64_t(ch.slot_cap) * 4;
                         ch.table_off = tables_bytes; tables_bytes += enc_table_bytes(pp.codec);
-                        if (pp.codec == C_O1SAC) o1sac_chunks.push_back(pp.first_chunk + k);
+                        if (pp.codec == C_O1SAC) (pp.shared >= 0 ? o1shared_chunks : o1sac_chunks).push_back(pp.first_chunk + k);
+                        if (pp.codec == C_O1SAC && pp.shared >= 0) o1shared_state.push_back(uint32_t(pp.shared));
                     }
             }
             if (opt.emit_payload_hash) tp.hash = hashes[i];
@@ -513,6 +558,38 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
                                                              d_slots.as<uint8_t>(), d_results.as<EncResult>());
         CUDA_TRY(cudaGetLastError());
     }
+    DeviceBuf d_o1shared;
+    if (!o1shared_chunks.empty()) {  // the coder's tables of a shared state, laid out like the ones o1sac_fit_kernel leaves, one copy per plane
+        std::vector<std::vector<uint8_t>> images;
+        for (auto& stt : shared.states) {
+            images.emplace_back(size_t(ENC_O1SAC_TABLE_BYTES - O1E_PRESENT), uint8_t(0));
+            uint8_t* img = images.back().data();
+            uint8_t* present = img;
+            uint16_t* rank = reinterpret_cast<uint16_t*>(img + (O1E_RANK - O1E_PRESENT));
+            uint16_t* pmf = reinterpret_cast<uint16_t*>(img + (O1E_PMF - O1E_PRESENT));
+            uint16_t* cum = reinterpret_cast<uint16_t*>(img + (O1E_CUM - O1E_PRESENT));
+            auto put_row = [&](uint32_t row, const uint16_t* src) {
+                uint32_t acc = 0;
+                for (int i = 0; i < 256; ++i) { pmf[256 * row + i] = src[i]; cum[256 * row + i] = uint16_t(acc); acc += src[i]; }
+            };
+            put_row(0, stt.marginal);
+            uint32_t k = 0;
+            for (uint32_t ctx = 0; ctx < 256; ++ctx) {
+                const bool has = (stt.bitmap[ctx >> 3] >> (ctx & 7)) & 1;
+                present[ctx] = has; rank[ctx] = uint16_t(k);
+                if (has) put_row(1 + ctx, stt.rows[k++].data());
+            }
+        }
+        for (size_t k = 0; k < o1shared_chunks.size(); ++k)
+            CUDA_TRY(cudaMemcpyAsync(d_tables.as<uint8_t>() + chunks[o1shared_chunks[k]].table_off + O1E_PRESENT, images[o1shared_state[k]].data(),
+                                     images[o1shared_state[k]].size(), cudaMemcpyHostToDevice, st));
+        CUDA_TRY(upload_vec(d_o1shared, o1shared_chunks, st));
+        const uint32_t n_sh = uint32_t(o1shared_chunks.size());
+        o1sac_encode_kernel<<<(n_sh + 63) / 64, 64, 0, st>>>(d_chunks.as<EncChunk>(), d_o1shared.as<uint32_t>(), n_sh, d_planes.as<uint8_t>(), d_tables.as<uint8_t>(),
+                                                             d_slots.as<uint8_t>(), d_results.as<EncResult>());
+        CUDA_TRY(cudaGetLastError());
+        CUDA_TRY(cudaStreamSynchronize(st));  // the images are host memory of this scope
+    }
     if (n_chunks) {
         table_kernel<<<(n_chunks + 63) / 64, 64, 0, st>>>(d_chunks.as<EncChunk>(), n_chunks, d_codec.as<uint8_t>(), d_hist.as<uint32_t>(), d_tables.as<uint8_t>(), d_results.as<EncResult>());
         CUDA_TRY(cudaGetLastError());
@@ -540,9 +617,10 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
             uint64_t n = chunks[ci].n, size;
             if (pp.codec == C_IDENTITY) { chunk_mode[ci] = 0; size = frame_hdr + n; }
             else if (pp.codec == C_O1SAC) {
-                chunk_mode[ci] = 5;
-                size = frame_hdr + r.stream_len[1] + r.stream_len[0];  // the state sits in front of the coder's bytes either way
-                if (!chunked) pp.state_len = r.stream_len[1];
+                chunk_mode[ci] = pp.shared >= 0 ? (5 | GATHER_BARE) : 5;
+                const uint64_t own_state = pp.shared >= 0 ? 0 : r.stream_len[1];
+                size = frame_hdr + own_state + r.stream_len[0];  // a plane's own state sits in front of the coder's bytes
+                if (!chunked) pp.state_len = own_state;
             } else {
                 uint64_t blob;
                 if (pp.codec == C_TANS) blob = 3 + 3 * uint64_t(r.hdr_n) + 8 + r.stream_len[0];
@@ -571,7 +649,30 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
         if (used) table.push_back({2, uint16_t(codec)});
     }
     auto table_index = [&](uint8_t tag, uint16_t id) { return uint64_t(std::find(table.begin(), table.end(), std::make_pair(tag, id)) - table.begin()); };
-    std::vector<uint8_t> et, prelude(4, 0), reg;
+    std::vector<uint8_t> et, prelude, reg;
+    {   // prelude.rs:23-57: the shared states some plane uses, under the ids the fit gave them (compressor.rs:945-949)
+        std::vector<char> used(shared.states.size(), 0);
+        for (auto& tp : plan) for (auto& pp : tp.planes) if (pp.shared >= 0) used[size_t(pp.shared)] = 1;
+        uint32_t n_used = 0;
+        for (char u : used) n_used += u;
+        put_u32(prelude, n_used);
+        for (size_t k = 0; k < used.size(); ++k) {
+            if (!used[k]) continue;
+            const std::vector<uint8_t>& sb = shared_bytes[k];
+            const std::string& name = shared.names[k];
+            prelude.push_back(uint8_t(k)); prelude.push_back(uint8_t(k >> 8));
+            prelude.push_back(uint8_t(C_O1SAC)); prelude.push_back(uint8_t(C_O1SAC >> 8));
+            prelude.push_back(1);       // state_format_version of Order1ScaleAC
+            prelude.push_back(0x02);    // applies_to_mask: scale planes (fit/order1.rs:333,369)
+            prelude.push_back(0); prelude.push_back(0);
+            put_u64(prelude, xxh64_host(sb.data(), sb.size()));
+            prelude.push_back(uint8_t(name.size())); prelude.push_back(uint8_t(name.size() >> 8));
+            prelude.insert(prelude.end(), name.begin(), name.end());
+            for (size_t z = (4 - name.size() % 4) % 4; z; --z) prelude.push_back(0);
+            put_u32(prelude, uint32_t(sb.size()));
+            prelude.insert(prelude.end(), sb.begin(), sb.end());
+        }
+    }
     put_varint(et, table.size());
     for (auto& e : table) { et.push_back(e.first); put_varint(et, e.second); }
     put_varint(reg, registry.size());
@@ -628,11 +729,12 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
             if (!chunked) {
                 // one payload per plane with the state in front of it (tensor_record_compact.rs:203-493): every codec but Identity
                 // is written with an inline state (empty unless Order1ScaleAC), the plane's row layout is recorded
-                const bool inline_state = pp.codec != C_IDENTITY, extra = pp.codec == C_O1SAC;
-                b.push_back(uint8_t((inline_state ? 0x04 : 0) | (opt.emit_plane_crc ? 0x01 : 0) | (pp.row_len ? 0x10 : 0) | (extra ? 0x20 : 0)));
+                // (a plane coded against a shared state names it instead: state source Shared, the state's version and id)
+                const bool use_shared = pp.shared >= 0, inline_state = pp.codec != C_IDENTITY && !use_shared, extra = pp.codec == C_O1SAC;
+                b.push_back(uint8_t((inline_state ? 0x04 : 0) | (use_shared ? 0x08 : 0) | (opt.emit_plane_crc ? 0x01 : 0) | (pp.row_len ? 0x10 : 0) | (extra ? 0x20 : 0)));
                 b.push_back(plane_role_byte(plan[i].chain.roles[p]));
                 put_varint(b, table_index(2, uint16_t(pp.codec)));
-                if (extra) { b.push_back(1); put_varint(b, 0); }
+                if (extra) { b.push_back(1); put_varint(b, use_shared ? uint64_t(pp.shared) : 0); }
                 if (inline_state) put_varint(b, pp.state_len);
                 put_varint(b, pp.payload_len - pp.state_len);
                 if (pp.row_len) put_varint(b, pp.row_len);
@@ -847,6 +949,54 @@ int64_t ptwm_b200_encode_model(const ptwm_b200_encode_tensor* tensors, size_t n,
         if (rc < 0) return rc;
         *out = e.release();
         return 0;
+    } catch (const std::exception& ex) { return fail(PTWM_RC_INTERNAL, ex.what()); }
+}
+int64_t ptwm_b200_fit_shared_states_host(const uint8_t* const* planes, const uint64_t* lens, const uint32_t* row_lens, size_t n, uint8_t* out, size_t cap,
+                                         uint32_t state_lens[8]) {
+    if ((n && (!planes || !lens || !row_lens)) || !state_lens || (cap && !out)) return fail(PTWM_RC_INVALID_INPUT, "null argument");
+    try {
+        // counts per plane (order1_scale_ac.rs:974-995): the first symbol of a row to the marginal, every other one after its predecessor
+        std::vector<std::vector<uint32_t>> joint(n, std::vector<uint32_t>(65536, 0)), marg(n, std::vector<uint32_t>(256, 0));
+        std::vector<FitCounts> fc;
+        for (size_t k = 0; k < n; ++k) {
+            if (!row_lens[k]) return fail(PTWM_RC_INVALID_INPUT, "row length 0");
+            const uint8_t* p = planes[k];
+            for (uint64_t i = 0; i < lens[k]; ++i) {
+                if (i % row_lens[k] == 0) marg[k][p[i]]++;
+                else joint[k][size_t(p[i - 1]) * 256 + p[i]]++;
+            }
+            fc.push_back(FitCounts{joint[k].data(), marg[k].data()});
+        }
+        FitResult r = fit_shared_order1(fc, [](const std::vector<FitState>& own, const std::vector<uint32_t>& pairs) {
+            std::vector<double> d(pairs.size() / 2);
+            for (size_t k = 0; k < d.size(); ++k) {  // what fit_pair_distance_kernel computes, in the same order
+                const FitState& P = own[pairs[2 * k]];
+                const FitState& Q = own[pairs[2 * k + 1]];
+                double total = 0;
+                for (int prev = 0; prev < 256; ++prev) {
+                    const uint16_t* p = P.row_or_marginal(prev);
+                    const uint16_t* q = Q.row_or_marginal(prev);
+                    double kl_pq = 0, kl_qp = 0;
+                    for (int i = 0; i < 256; ++i) {
+                        const double pp = double(p[i]) / 4096.0, qq = double(q[i]) / 4096.0;
+                        if (pp > 0.0 && qq > 0.0) { kl_pq += pp * std::log(pp / qq); kl_qp += qq * std::log(qq / pp); }
+                    }
+                    const double ln2 = 0.693147180559945309417232121458;
+                    total += 0.5 * (double(P.marginal[prev]) / 4096.0 + double(Q.marginal[prev]) / 4096.0) * (kl_pq / ln2 + kl_qp / ln2);
+                }
+                d[k] = total;
+            }
+            return d;
+        });
+        size_t pos = 0;
+        for (size_t k = 0; k < r.states.size(); ++k) {
+            const std::vector<uint8_t> b = r.states[k].serialize();
+            if (pos + b.size() > cap) return fail(PTWM_RC_BUFFER_TOO_SMALL, "shared states do not fit the buffer");
+            std::memcpy(out + pos, b.data(), b.size());
+            state_lens[k] = uint32_t(b.size());
+            pos += b.size();
+        }
+        return int64_t(r.states.size());
     } catch (const std::exception& ex) { return fail(PTWM_RC_INTERNAL, ex.what()); }
 }
 uint64_t ptwm_b200_encoded_size(const ptwm_b200_encoded* e) { return e ? e->size : 0; }

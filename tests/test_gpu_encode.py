@@ -165,6 +165,43 @@ def test_scale_planes_go_to_order1_scale_ac_like_the_oracle_writer():
             assert t.contiguous().view(torch.uint8).cpu().numpy().tobytes() == s.raw, name
 
 
+def test_shared_scale_states_are_fitted_stored_once_and_used():
+    """Passes 2 and 3 of the writer on unchunked planes: scale planes of two families get Order1ScaleAC states fitted over
+    the whole model, the prelude stores the ones in use, the planes name them instead of carrying a state, the container is
+    smaller than with a state per plane, and both decoders read it."""
+    rng = np.random.default_rng(5)
+    specs = []
+    for k in range(6):  # two families of block scales over the same four values: one changes rarely along a row, one is noise
+        rows, cols = 192 + 16 * k, 256
+        if k % 2 == 0:
+            vals = 120 + np.cumsum(rng.random((rows, cols)) < 0.06, axis=1) % 4
+        else:
+            vals = 120 + rng.integers(0, 4, (rows, cols))
+        specs.append(oracle.TensorSpec(f"l{k}.scales", oracle.DT_U8, [rows, cols], vals.astype(np.uint8).tobytes(), usage="scale"))
+    specs.append(oracle.TensorSpec("w.bf16", oracle.DT_BF16, [64, 512], (torch.randn(64, 512, generator=torch.Generator().manual_seed(3)) * 0.02).to(torch.bfloat16).view(torch.uint8).numpy().tobytes()))
+    tensors, usage, specs = to_cuda(specs)
+    base = compress_model(tensors, CompressionConfig(streaming_chunk=None, emit_plane_crc=True), usage=usage)
+    enc = compress_model(tensors, CompressionConfig(streaming_chunk=None, emit_plane_crc=True, shared_states=True), usage=usage)
+    blob = enc.to_bytes()
+    assert b"order1_scale_ac/cluster_0_of_" in blob and b"order1_scale_ac/cluster_0_of_" not in base.to_bytes()
+    assert enc.size < base.size, (enc.size, base.size)
+    from ptwm_b200 import _lib
+    host_states = _lib.fit_shared_states_host([sp.raw for sp in specs[:6]], [256] * 6)  # the same fit with the distances computed on the host
+    assert len(host_states) == 2 and host_states[0] in blob
+    assert b"_of_2" in blob  # two clusters describe the model in fewer bits than one; only states some plane uses are stored
+    assert [enc.plane_codecs[f"l{k}.scales"] for k in (0, 2, 4)] == [[ORDER1_SCALE_AC]] * 3
+    oc = oracle.Container(blob)
+    for i, sp in enumerate(specs):
+        assert oc.decode(i) == sp.raw, sp.name
+    h = ptwm_b200.ContainerHandle(blob, device=0)
+    for (name, t), sp in zip(h.decode_model(), specs):
+        assert t.contiguous().view(torch.uint8).cpu().numpy().tobytes() == sp.raw, name
+    # chunked planes carry their states inline whatever the option says
+    a = compress_model(tensors, CompressionConfig(streaming_chunk=8192, shared_states=True), usage=usage).to_bytes()
+    b = compress_model(tensors, CompressionConfig(streaming_chunk=8192), usage=usage).to_bytes()
+    assert a == b
+
+
 # ---- chains with one more op between the split and a terminal --------------------------------------------
 def _chain_model():
     """bf16 / fp16 / fp32 tensors for the candidate chains: `smooth` has slowly varying magnitudes (its exponent bytes differ

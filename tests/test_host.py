@@ -313,3 +313,25 @@ def test_sharded_open_partitions_the_records(L):
         assert seen == list(range(len(names))), world
     hs = C.c_void_p()
     assert L.ptwm_b200_open_shard(C.addressof(buf), len(blob), 2, 2, C.byref(hs)) < 0
+
+
+def test_shared_state_fit_on_the_host(L):
+    """Pass 2 of the writer without a GPU.  One plane: the shared state is the state the codec fits to that plane
+    (the oracle's, pinned by the reference's fixtures).  Planes that behave alike: one state, fitted to their pooled
+    counts.  Two families over the same symbols that behave differently: two states."""
+    rng = np.random.default_rng(9)
+    slow = lambda rows: (120 + np.cumsum(rng.random((rows, 256)) < 0.06, axis=1) % 4).astype(np.uint8).tobytes()
+    noise = lambda rows: (120 + rng.integers(0, 4, (rows, 256))).astype(np.uint8).tobytes()
+    a = slow(64)
+    st, sv, _ = oracle.plane_encode(oracle.O1SAC, a, 256)
+    assert sv == 1 and _lib.fit_shared_states_host([a], [256]) == [st]
+    b, c = slow(80), slow(48)
+    pooled, _, _ = oracle.plane_encode(oracle.O1SAC, a + b + c, 256)
+    assert _lib.fit_shared_states_host([a, b, c], [256, 256, 256]) == [pooled]
+    planes = [slow(200), noise(200), slow(220), noise(180), slow(190), noise(210)]
+    states = _lib.fit_shared_states_host(planes, [256] * 6)
+    assert len(states) == 2
+    # each state is the fit of one family's pooled counts, in the order of the families' first planes
+    assert states[0] == oracle.plane_encode(oracle.O1SAC, planes[0] + planes[2] + planes[4], 256)[0]
+    assert states[1] == oracle.plane_encode(oracle.O1SAC, planes[1] + planes[3] + planes[5], 256)[0]
+    assert _lib.fit_shared_states_host([], []) == []
