@@ -202,6 +202,49 @@ def test_shared_scale_states_are_fitted_stored_once_and_used():
     assert a == b
 
 
+@pytest.mark.parametrize("seed", range(10))
+def test_random_models_round_trip_through_both_decoders(seed):
+    """Seeded random state dicts through the device encoder with random options (chunk size or whole planes, menu or a
+    forced codec, candidate chains, integrity fields): the oracle and the device decoder both return the source bytes."""
+    rng = np.random.default_rng(2000 + seed)
+    tensors = {}
+    for t in range(int(rng.integers(2, 6))):
+        kind = ["bf16", "f16", "f32", "fp8", "u8", "bf16", "sparse_bf16"][int(rng.integers(0, 7))]
+        rows, cols = int(rng.integers(1, 120)), int(rng.integers(1, 2500))
+        g = torch.Generator().manual_seed(seed * 16 + t)
+        w = torch.randn(rows, cols, generator=g) * 0.02
+        if kind == "bf16":
+            x = w.to(torch.bfloat16)
+        elif kind == "sparse_bf16":  # low mantissa bits clear: what MantissaZeroStrip is for
+            x = (w.to(torch.bfloat16).view(torch.int16) & ~0x7).view(torch.bfloat16)
+        elif kind == "f16":
+            x = w.to(torch.float16)
+        elif kind == "f32":
+            x = w
+        elif kind == "fp8":
+            x = (w / w.abs().amax() * 200).to(torch.float8_e4m3fn)
+        else:
+            x = ((torch.randn(rows * cols, generator=g) * 2.5).round().to(torch.int64) + 100).clamp(0, 255).to(torch.uint8)
+        tensors[f"t{t}.{kind}"] = x.cuda()
+    chunk = [None, 777, 4099, 8192, 32768, 65536][int(rng.integers(0, 6))]
+    kw = dict(streaming_chunk=chunk, emit_plane_crc=bool(rng.integers(0, 2)), emit_payload_hash=bool(rng.integers(0, 2)))
+    pick = int(rng.integers(0, 6))
+    if pick < 4:
+        kw["forced_codec"] = [IDENTITY, HUFFMAN, RANS, TANS][pick]
+    elif pick == 4:
+        kw["codec_menu"] = (IDENTITY, HUFFMAN, RANS, TANS)
+    if pick >= 4 and rng.integers(0, 2):
+        kw["candidate_chains"] = ("intdelta", "mzs")
+    enc = compress_model(tensors, CompressionConfig(**kw))
+    blob = enc.to_bytes()
+    oc = oracle.Container(blob)
+    h = ptwm_b200.ContainerHandle(blob, device=0)
+    for i, ((name, got), (want_name, want)) in enumerate(zip(h.decode_model(), tensors.items())):
+        raw = want.contiguous().view(torch.uint8).cpu().numpy().tobytes()
+        assert name == want_name and got.contiguous().view(torch.uint8).cpu().numpy().tobytes() == raw, (name, kw)
+        assert oc.decode(i) == raw, (name, kw)
+
+
 # ---- chains with one more op between the split and a terminal --------------------------------------------
 def _chain_model():
     """bf16 / fp16 / fp32 tensors for the candidate chains: `smooth` has slowly varying magnitudes (its exponent bytes differ
