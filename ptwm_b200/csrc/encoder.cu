@@ -4,6 +4,9 @@
 // tensor_record_compact.rs:203-493, chain/wire_compact.rs:140-245,
 // extension/compact_table.rs:123-158 of the reference).
 #include <algorithm>
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
 #include <cmath>
 #include <cstring>
 #include <memory>
@@ -222,6 +225,16 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
         opt.forced_codec != C_O1SAC)
         return fail(PTWM_RC_UNSUPPORTED, "device encode offers identity, huffman, rans, tans and order1_scale_ac");
 
+    // PTWM_B200_PROFILE=1 prints the wall time of every phase to stderr (the reference's PTWM_PROFILE, compressor.rs:1004-1016)
+    const bool profile = std::getenv("PTWM_B200_PROFILE") != nullptr;
+    auto prof_t = std::chrono::steady_clock::now();
+    auto prof = [&](const char* label) {
+        if (!profile) return;
+        cudaStreamSynchronize(st);
+        auto now = std::chrono::steady_clock::now();
+        std::fprintf(stderr, "[ptwm_b200-profile] %s: %.2f ms\n", label, std::chrono::duration<double, std::milli>(now - prof_t).count());
+        prof_t = now;
+    };
     // ---- chains, registry, planes, chunks -----------------------------------
     std::vector<TensorPlan> plan(n_tensors);
     std::vector<ChainDef> registry;
@@ -290,6 +303,7 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
     }
     const uint32_t n_chunks = uint32_t(chunks.size());
 
+    prof("plan (host)");
     // ---- device pipeline: split, histograms ---------------------------------
     DeviceBuf d_planes, d_splits, d_chunks, d_hist, d_plane_hist, d_codec, d_tables, d_results, d_slots;
     CUDA_TRY(d_planes.alloc(planes_bytes));
@@ -381,6 +395,7 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
     }
     CUDA_TRY(cudaStreamSynchronize(st));
 
+    prof("split, histograms, CRC / hash, counts");
     // ---- shared states (compressor.rs:834-881): only whole planes can use one (a chunked plane carries its states inline,
     //      compressor.rs:324-381), and only when the codec is chosen, not forced
     FitResult shared;
@@ -409,6 +424,7 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
         for (auto& stt : shared.states) shared_bytes.push_back(stt.serialize());
     }
 
+    prof("shared-state fit");
     // ---- codec per plane ------------------------------------------------------
     std::vector<uint8_t> plane_codec(n_planes);
     std::vector<uint32_t> o1sac_chunks, o1shared_chunks, o1shared_state;  // chunks that fit their own state / that code against shared state o1shared_state[k]
@@ -537,6 +553,7 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
         }
     }
 
+    prof("codec and chain choice (host)");
     // ---- tables and streams ---------------------------------------------------
     CUDA_TRY(upload_vec(d_codec, plane_codec, st));
     if (n_chunks) CUDA_TRY(cudaMemcpyAsync(d_chunks.p, chunks.data(), chunks.size() * sizeof(EncChunk), cudaMemcpyHostToDevice, st));
@@ -599,6 +616,7 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
     }
     CUDA_TRY(cudaStreamSynchronize(st));
 
+    prof("tables and streams");
     // ---- layout: chunk frames, plane payloads, records ------------------------
     std::vector<uint32_t> chunk_mode(n_chunks);
     const uint64_t frame_hdr = chunked ? 5 : 0;  // [state_version][state_len u32] in front of every chunk; an unchunked plane has none
@@ -798,6 +816,7 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
         pos += tail.size();
     }
 
+    prof("layout and records (host)");
     // ---- write the container ----------------------------------------------------
     enc.size = pos; enc.device = device;
     CUDA_TRY(cudaMalloc(&enc.d_out, pos));
@@ -813,6 +832,7 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
         CUDA_TRY(cudaGetLastError());
     }
     CUDA_TRY(cudaStreamSynchronize(st));
+    prof("scatter and gather");
     return 0;
 }
 
