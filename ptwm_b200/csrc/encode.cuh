@@ -195,16 +195,38 @@ __global__ void __launch_bounds__(256) split_kernel(const SplitItem* __restrict_
 // counts go to global memory and are added to the plane's totals.
 __global__ void __launch_bounds__(128) hist_kernel(const EncChunk* __restrict__ chunks, const uint8_t* __restrict__ planes, uint32_t* __restrict__ hist,
                                                    unsigned long long* __restrict__ plane_hist) {
-    __shared__ uint32_t h[256];
+    // Eight copies of the histogram, laid out [symbol][copy]: the lanes of a warp spread over the copies (an exponent plane
+    // sends most of them to the same three or four symbols) and the copies of a symbol sit in different banks.  The plane
+    // is read 16 bytes at a time.
+    __shared__ uint32_t h[256 * 8];
     const EncChunk c = chunks[blockIdx.x];
-    for (uint32_t i = threadIdx.x; i < 256; i += blockDim.x) h[i] = 0;
+    for (uint32_t i = threadIdx.x; i < 256 * 8; i += blockDim.x) h[i] = 0;
     __syncthreads();
     const uint8_t* p = planes + c.plane_off;
-    for (uint32_t i = threadIdx.x; i < c.n; i += blockDim.x) atomicAdd(&h[p[i]], 1u);
+    uint32_t* mine = h + (threadIdx.x & 7);
+    const uintptr_t lo = reinterpret_cast<uintptr_t>(p), hi = lo + c.n;
+    const uintptr_t first_block = (lo + 15) & ~uintptr_t(15), last_block = hi & ~uintptr_t(15);
+    if (first_block >= last_block) {
+        for (uint32_t i = threadIdx.x; i < c.n; i += blockDim.x) atomicAdd(&mine[uint32_t(p[i]) * 8], 1u);
+    } else {
+        const uint32_t head = uint32_t(first_block - lo), tail = uint32_t(hi - last_block);
+        if (threadIdx.x < head) atomicAdd(&mine[uint32_t(p[threadIdx.x]) * 8], 1u);
+        if (threadIdx.x < tail) atomicAdd(&mine[uint32_t(*reinterpret_cast<const uint8_t*>(last_block + threadIdx.x)) * 8], 1u);
+        const uint32_t blocks = uint32_t((last_block - first_block) >> 4);
+        for (uint32_t b = threadIdx.x; b < blocks; b += blockDim.x) {
+            const uint4 v = *reinterpret_cast<const uint4*>(first_block + 16 * uintptr_t(b));
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 0; k < 16; ++k) atomicAdd(&mine[((w[k >> 2] >> (8 * (k & 3))) & 0xFFu) * 8], 1u);
+        }
+    }
     __syncthreads();
     for (uint32_t i = threadIdx.x; i < 256; i += blockDim.x) {
-        hist[uint64_t(blockIdx.x) * 256 + i] = h[i];
-        if (h[i]) atomicAdd(&plane_hist[uint64_t(c.plane) * 256 + i], (unsigned long long)h[i]);
+        uint32_t total = 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) total += h[i * 8 + k];
+        hist[uint64_t(blockIdx.x) * 256 + i] = total;
+        if (total) atomicAdd(&plane_hist[uint64_t(c.plane) * 256 + i], (unsigned long long)total);
     }
 }
 
@@ -376,6 +398,29 @@ __global__ void __launch_bounds__(128) encode_kernel(const EncChunk* __restrict_
     results[ci].stream_len[s] = uint32_t(slot_end - w);
 }
 
+// n bytes from s to d by the threads of a block: d is brought to a 16-byte boundary, then every thread moves 16 bytes at
+// a time, the source words taken aligned and shifted into place (a word that holds a needed byte is read whole; device
+// allocations are padded beyond that).
+__device__ __forceinline__ void block_copy(uint8_t* d, const uint8_t* s, uint32_t n, uint32_t t, uint32_t nt) {
+    uint32_t head = uint32_t((16 - (reinterpret_cast<uintptr_t>(d) & 15)) & 15);
+    if (head > n) head = n;
+    for (uint32_t i = t; i < head; i += nt) d[i] = s[i];
+    d += head; s += head; n -= head;
+    const uint32_t blocks = n >> 4;
+    const uint32_t sh = uint32_t(reinterpret_cast<uintptr_t>(s) & 3) * 8;
+    const uint32_t* sw = reinterpret_cast<const uint32_t*>(reinterpret_cast<uintptr_t>(s) & ~uintptr_t(3));
+    for (uint32_t b = t; b < blocks; b += nt) {
+        const uint32_t* q = sw + 4 * size_t(b);
+        const uint32_t w0 = q[0], w1 = q[1], w2 = q[2], w3 = q[3];
+        uint4 v = make_uint4(w0, w1, w2, w3);
+        if (sh) {
+            const uint32_t w4 = q[4];
+            v = make_uint4(__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh), __funnelshift_r(w2, w3, sh), __funnelshift_r(w3, w4, sh));
+        }
+        *reinterpret_cast<uint4*>(d + 16 * size_t(b)) = v;
+    }
+    for (uint32_t i = blocks * 16 + t; i < n; i += nt) d[i] = s[i];
+}
 // One CTA per chunk frame: [state_version 0][state_len 0 u32] then the codec
 // payload, written at its final place in the container.
 __global__ void __launch_bounds__(128) gather_kernel(const GatherItem* __restrict__ items, const EncChunk* __restrict__ chunks, const EncResult* __restrict__ results,
@@ -395,7 +440,7 @@ __global__ void __launch_bounds__(128) gather_kernel(const GatherItem* __restric
     if (mode <= 1) {
         if (mode == 1) { if (t == 0) d[0] = 0; d += 1; }
         const uint8_t* p = planes + c.plane_off;
-        for (uint32_t i = t; i < c.n; i += blockDim.x) d[i] = p[i];
+        block_copy(d, p, c.n, t, blockDim.x);
         return;
     }
     const uint8_t* tab = tables + c.table_off;
@@ -420,7 +465,7 @@ __global__ void __launch_bounds__(128) gather_kernel(const GatherItem* __restric
             d += state_len;
         }
         const uint8_t* sp = slots + c.slot_off;
-        for (uint32_t i = t; i < r.stream_len[0]; i += blockDim.x) d[i] = sp[i];
+        block_copy(d, sp, r.stream_len[0], t, blockDim.x);
         return;
     }
     if (t == 0) { d[0] = 1; d[1] = uint8_t(c.n); d[2] = uint8_t(c.n >> 8); d[3] = uint8_t(c.n >> 16); d[4] = uint8_t(c.n >> 24); }
@@ -435,7 +480,7 @@ __global__ void __launch_bounds__(128) gather_kernel(const GatherItem* __restric
         }
         d += 3 + 3 * r.hdr_n + 8;
         const uint8_t* sp = slots + c.slot_off;
-        for (uint32_t i = t; i < r.stream_len[0]; i += blockDim.x) d[i] = sp[i];
+        block_copy(d, sp, r.stream_len[0], t, blockDim.x);
         return;
     }
     uint32_t hdr;
@@ -459,7 +504,7 @@ __global__ void __launch_bounds__(128) gather_kernel(const GatherItem* __restric
     d += 16;
     for (uint32_t s = 0; s < 4; ++s) {
         const uint8_t* sp = slots + c.slot_off + uint64_t(s + 1) * c.slot_cap - r.stream_len[s];
-        for (uint32_t i = t; i < r.stream_len[s]; i += blockDim.x) d[i] = sp[i];
+        block_copy(d, sp, r.stream_len[s], t, blockDim.x);
         d += r.stream_len[s];
     }
 }

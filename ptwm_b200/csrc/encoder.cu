@@ -562,6 +562,7 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
     CUDA_TRY(cudaMemsetAsync(d_results.p, 0, uint64_t(n_chunks) * sizeof(EncResult) + (n_chunks ? 0 : 1), st));
     CUDA_TRY(d_slots.alloc(slots_bytes));
     std::vector<EncResult> results(n_chunks);
+    prof("  work memory for tables and streams");
     DeviceBuf d_o1list;
     if (!o1sac_chunks.empty()) {  // Order1ScaleAC: counts, rows, then the range coder, one chunk per block / thread
         CUDA_TRY(upload_vec(d_o1list, o1sac_chunks, st));
@@ -607,11 +608,14 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
         CUDA_TRY(cudaGetLastError());
         CUDA_TRY(cudaStreamSynchronize(st));  // the images are host memory of this scope
     }
+    prof("  order1_scale_ac chunks");
     if (n_chunks) {
         table_kernel<<<(n_chunks + 63) / 64, 64, 0, st>>>(d_chunks.as<EncChunk>(), n_chunks, d_codec.as<uint8_t>(), d_hist.as<uint32_t>(), d_tables.as<uint8_t>(), d_results.as<EncResult>());
         CUDA_TRY(cudaGetLastError());
+        prof("  table_kernel");
         encode_kernel<<<(n_chunks * 4 + 127) / 128, 128, 0, st>>>(d_chunks.as<EncChunk>(), n_chunks, d_codec.as<uint8_t>(), d_planes.as<uint8_t>(), d_tables.as<uint8_t>(), d_slots.as<uint8_t>(), d_results.as<EncResult>());
         CUDA_TRY(cudaGetLastError());
+        prof("  encode_kernel");
         CUDA_TRY(cudaMemcpyAsync(results.data(), d_results.p, results.size() * sizeof(EncResult), cudaMemcpyDeviceToHost, st));
     }
     CUDA_TRY(cudaStreamSynchronize(st));
