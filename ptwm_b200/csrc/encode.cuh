@@ -315,6 +315,88 @@ __global__ void __launch_bounds__(64) table_kernel(const EncChunk* __restrict__ 
     results[ci] = r;
 }
 
+// tANS (entropy/tans/mod.rs:268-318): one stream per chunk, so one lane per chunk; the symbols are walked last to first and the
+// bits go upward from the start of the chunk's slot area.  A symbol is two table look-ups that depend on the running
+// state, so the tables of the 32 chunks of a block sit in shared memory, laid out [entry][lane] like the decoder's:
+// next state (u16 x 2048), and per symbol the bit-count term (u32) and the state offset (i16).  With the tables in global
+// memory every symbol waited for the L2 twice.
+constexpr int TENC_CHUNKS = 32;
+constexpr int TENC_NEXT_BYTES = 2048 * 32 * 2, TENC_DNB_BYTES = 256 * 32 * 4, TENC_DFS_BYTES = 256 * 32 * 2;
+constexpr int TENC_SMEM = TENC_NEXT_BYTES + TENC_DNB_BYTES + TENC_DFS_BYTES;
+__global__ void __launch_bounds__(32, 1) tans_encode_kernel(const EncChunk* __restrict__ chunks, const uint32_t* __restrict__ list, uint32_t n_list,
+                                                            const uint8_t* __restrict__ planes, const uint8_t* __restrict__ tables, uint8_t* __restrict__ slots,
+                                                            EncResult* __restrict__ results) {
+    extern __shared__ __align__(16) uint8_t tenc_smem[];
+    const uint32_t lane = threadIdx.x, li = blockIdx.x * TENC_CHUNKS + lane;
+    if (li >= n_list) return;
+    const uint32_t ci = list[li];
+    const EncChunk c = chunks[ci];
+    if (!results[ci].coded || !c.n) return;  // lanes do not depend on one another
+    uint16_t* next_state = reinterpret_cast<uint16_t*>(tenc_smem) + lane;                                 // entry e at next_state[e * 32]
+    uint32_t* dnb = reinterpret_cast<uint32_t*>(tenc_smem + TENC_NEXT_BYTES) + lane;                       // symbol s at dnb[s * 32]
+    int16_t* dfs = reinterpret_cast<int16_t*>(tenc_smem + TENC_NEXT_BYTES + TENC_DNB_BYTES) + lane;       // symbol s at dfs[s * 32]
+    {
+        const uint8_t* tab = tables + c.table_off;  // table areas start on 16-byte boundaries
+        const uint4* g_dnb = reinterpret_cast<const uint4*>(tab + 512);
+        const uint4* g_dfs = reinterpret_cast<const uint4*>(tab + 1536);
+        const uint4* g_next = reinterpret_cast<const uint4*>(tab + 2560);
+        for (uint32_t k = 0; k < 64; ++k) {
+            const uint4 a = g_dnb[k], b = g_dfs[k];
+            dnb[(4 * k + 0) * 32] = a.x; dnb[(4 * k + 1) * 32] = a.y; dnb[(4 * k + 2) * 32] = a.z; dnb[(4 * k + 3) * 32] = a.w;
+            dfs[(4 * k + 0) * 32] = int16_t(int32_t(b.x)); dfs[(4 * k + 1) * 32] = int16_t(int32_t(b.y));
+            dfs[(4 * k + 2) * 32] = int16_t(int32_t(b.z)); dfs[(4 * k + 3) * 32] = int16_t(int32_t(b.w));
+        }
+        for (uint32_t k = 0; k < 256; ++k) {
+            const uint4 v = g_next[k];
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) next_state[(8 * k + j) * 32] = uint16_t(w[j >> 1] >> (16 * (j & 1)));
+        }
+    }
+    uint32_t* w32 = reinterpret_cast<uint32_t*>(slots + c.slot_off);  // slot areas start on 16-byte boundaries
+    uint64_t acc = 0, total_bits = 0;
+    uint32_t nb_acc = 0, words = 0, value = 2048;
+    auto add_bits = [&](uint32_t v, uint32_t nb) {
+        acc |= uint64_t(v & ((1u << nb) - 1u)) << nb_acc;
+        nb_acc += nb; total_bits += nb;
+        if (nb_acc >= 32) { w32[words++] = uint32_t(acc); acc >>= 32; nb_acc -= 32; }
+    };
+    auto step = [&](uint32_t b) {
+        const uint32_t nb = (value + dnb[b * 32]) >> 16;
+        add_bits(value, nb);
+        value = next_state[uint32_t(int32_t(value >> nb) + int32_t(dfs[b * 32])) * 32];
+    };
+    // the plane's bytes last to first: single bytes down to a 16-byte boundary, then aligned blocks, each requested while the
+    // one before it is coded, then the bytes below the first boundary
+    const uintptr_t lo = reinterpret_cast<uintptr_t>(planes + c.plane_off), hi = lo + c.n;
+    const uintptr_t first_block = (lo + 15) & ~uintptr_t(15), last_block = hi & ~uintptr_t(15);
+    if (first_block >= last_block) {
+        for (uintptr_t a = hi; a-- > lo;) step(*reinterpret_cast<const uint8_t*>(a));
+    } else {
+        for (uintptr_t a = hi; a-- > last_block;) step(*reinterpret_cast<const uint8_t*>(a));
+        uintptr_t b = last_block - 16;
+        uint4 ahead = *reinterpret_cast<const uint4*>(b);
+        for (;;) {
+            const uint4 v = ahead;
+            const bool more = b > first_block;
+            if (more) ahead = *reinterpret_cast<const uint4*>(b - 16);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 15; k >= 0; --k) step((w[k >> 2] >> (8 * (k & 3))) & 0xFFu);
+            if (!more) break;
+            b -= 16;
+        }
+        for (uintptr_t a = first_block; a-- > lo;) step(*reinterpret_cast<const uint8_t*>(a));
+    }
+    add_bits(value, 11);
+    uint8_t* tail = reinterpret_cast<uint8_t*>(w32 + words);
+    uint32_t bytes = words * 4;
+    while (nb_acc > 0) { *tail++ = uint8_t(acc); acc >>= 8; nb_acc = nb_acc > 8 ? nb_acc - 8 : 0; ++bytes; }
+    results[ci].stream_len[0] = bytes;
+    results[ci].stream_len[1] = uint32_t(total_bits);
+    results[ci].stream_len[2] = uint32_t(total_bits >> 32);
+}
+
 // One thread per stream.  Bytes are produced last-to-first for both codecs, so
 // each stream is written downward from the end of its slot and ends up in
 // decode order; stream_len tells the gather where it starts.
@@ -326,36 +408,7 @@ __global__ void __launch_bounds__(128) encode_kernel(const EncChunk* __restrict_
     if (ci >= n_chunks) return;
     const EncChunk c = chunks[ci];
     int codec = plane_codec[c.plane];
-    if (codec == C_O1SAC || !results[ci].coded) return;
-    if (codec == C_TANS) {  // one stream per chunk, bits appended upward from the start of the slot area (mod.rs:268-318)
-        if (s) return;
-        const uint8_t* tab = tables + c.table_off;
-        const uint32_t* dnb = reinterpret_cast<const uint32_t*>(tab + 512);
-        const int32_t* dfs = reinterpret_cast<const int32_t*>(tab + 1536);
-        const uint16_t* next_state = reinterpret_cast<const uint16_t*>(tab + 2560);
-        const uint8_t* src = planes + c.plane_off;
-        uint32_t* w32 = reinterpret_cast<uint32_t*>(slots + c.slot_off);  // slot areas start on 16-byte boundaries
-        uint64_t acc = 0, total_bits = 0;
-        uint32_t nb_acc = 0, words = 0, value = 2048;
-        auto add_bits = [&](uint32_t v, uint32_t nb) {
-            acc |= uint64_t(v & ((1u << nb) - 1u)) << nb_acc;
-            nb_acc += nb; total_bits += nb;
-            if (nb_acc >= 32) { w32[words++] = uint32_t(acc); acc >>= 32; nb_acc -= 32; }
-        };
-        for_each_byte<true>(src, c.n, [&](uint32_t b) {
-            const uint32_t nb = (value + dnb[b]) >> 16;
-            add_bits(value, nb);
-            value = next_state[int32_t(value >> nb) + dfs[b]];
-        });
-        add_bits(value, 11);
-        uint8_t* tail = reinterpret_cast<uint8_t*>(w32 + words);
-        uint32_t bytes = words * 4;
-        while (nb_acc > 0) { *tail++ = uint8_t(acc); acc >>= 8; nb_acc = nb_acc > 8 ? nb_acc - 8 : 0; ++bytes; }
-        results[ci].stream_len[0] = bytes;
-        results[ci].stream_len[1] = uint32_t(total_bits);
-        results[ci].stream_len[2] = uint32_t(total_bits >> 32);
-        return;
-    }
+    if (codec == C_O1SAC || codec == C_TANS || !results[ci].coded) return;  // those two have kernels of their own
     uint32_t start, len;
     split_four_dev(c.n, s, start, len);
     const uint8_t* src = planes + c.plane_off + start;

@@ -427,6 +427,7 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
     prof("shared-state fit");
     // ---- codec per plane ------------------------------------------------------
     std::vector<uint8_t> plane_codec(n_planes);
+    std::vector<uint32_t> tans_chunks;  // chunks of tANS planes, for the kernel that codes them
     std::vector<uint32_t> o1sac_chunks, o1shared_chunks, o1shared_state;  // chunks that fit their own state / that code against shared state o1shared_state[k]
     uint64_t tables_bytes = 0;
     std::vector<std::pair<uint32_t, uint32_t>> recrc;  // (tensor, accumulator) of planes shifted by MantissaZeroStrip: their CRC is taken again below
@@ -524,6 +525,7 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
                         ch.slot_off = slots_bytes; slots_bytes += uint64_t(ch.slot_cap) * 4;
                         ch.table_off = tables_bytes; tables_bytes += enc_table_bytes(pp.codec);
                         if (pp.codec == C_O1SAC) (pp.shared >= 0 ? o1shared_chunks : o1sac_chunks).push_back(pp.first_chunk + k);
+                        if (pp.codec == C_TANS) tans_chunks.push_back(pp.first_chunk + k);
                         if (pp.codec == C_O1SAC && pp.shared >= 0) o1shared_state.push_back(uint32_t(pp.shared));
                     }
             }
@@ -563,7 +565,7 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
     CUDA_TRY(d_slots.alloc(slots_bytes));
     std::vector<EncResult> results(n_chunks);
     prof("  work memory for tables and streams");
-    DeviceBuf d_o1list;
+    DeviceBuf d_o1list, d_tanslist;
     if (!o1sac_chunks.empty()) {  // Order1ScaleAC: counts, rows, then the range coder, one chunk per block / thread
         CUDA_TRY(upload_vec(d_o1list, o1sac_chunks, st));
         for (uint32_t ci : o1sac_chunks) CUDA_TRY(cudaMemsetAsync(d_tables.as<uint8_t>() + chunks[ci].table_off, 0, O1E_PRESENT, st));
@@ -615,6 +617,14 @@ int64_t encode_impl(const ptwm_b200_encode_tensor* tensors, size_t n_tensors, co
         prof("  table_kernel");
         encode_kernel<<<(n_chunks * 4 + 127) / 128, 128, 0, st>>>(d_chunks.as<EncChunk>(), n_chunks, d_codec.as<uint8_t>(), d_planes.as<uint8_t>(), d_tables.as<uint8_t>(), d_slots.as<uint8_t>(), d_results.as<EncResult>());
         CUDA_TRY(cudaGetLastError());
+        if (!tans_chunks.empty()) {
+            CUDA_TRY(upload_vec(d_tanslist, tans_chunks, st));
+            const uint32_t n_t = uint32_t(tans_chunks.size());
+            CUDA_TRY(cudaFuncSetAttribute(tans_encode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TENC_SMEM));  // per device; cheap to repeat
+            tans_encode_kernel<<<(n_t + TENC_CHUNKS - 1) / TENC_CHUNKS, 32, TENC_SMEM, st>>>(d_chunks.as<EncChunk>(), d_tanslist.as<uint32_t>(), n_t, d_planes.as<uint8_t>(),
+                                                                                         d_tables.as<uint8_t>(), d_slots.as<uint8_t>(), d_results.as<EncResult>());
+            CUDA_TRY(cudaGetLastError());
+        }
         prof("  encode_kernel");
         CUDA_TRY(cudaMemcpyAsync(results.data(), d_results.p, results.size() * sizeof(EncResult), cudaMemcpyDeviceToHost, st));
     }
@@ -859,7 +869,7 @@ int64_t ptwm::encode_plane_cuda(int codec, const uint8_t* state, size_t state_le
         return int64_t(n);
     }
     if (n > 0xFFFFFFFFull && codec == C_O1SAC) return fail(PTWM_RC_UNSUPPORTED, "plane too long for the device encoder");
-    DeviceBuf d_chunk, d_codec, d_hist, d_phist, d_tables, d_results, d_slots, d_gather, d_list;
+    DeviceBuf d_chunk, d_codec, d_hist, d_phist, d_tables, d_results, d_slots, d_gather, d_list, d_tlist;
     const uint64_t slot_cap = ((n / 4 + 1) * 12 + 7) / 8 + 64;  // a symbol takes at most 12 bits in any of the codecs
     EncChunk chunk{0, 0, 0, uint32_t(n), uint32_t(slot_cap), 0, 0};
     const uint8_t codec_byte = uint8_t(codec);
@@ -924,6 +934,12 @@ int64_t ptwm::encode_plane_cuda(int codec, const uint8_t* state, size_t state_le
         hist_kernel<<<1, 128, 0, st>>>(d_chunk.as<EncChunk>(), in, d_hist.as<uint32_t>(), d_phist.as<unsigned long long>());
         table_kernel<<<1, 64, 0, st>>>(d_chunk.as<EncChunk>(), 1, d_codec.as<uint8_t>(), d_hist.as<uint32_t>(), d_tables.as<uint8_t>(), d_results.as<EncResult>());
         encode_kernel<<<1, 128, 0, st>>>(d_chunk.as<EncChunk>(), 1, d_codec.as<uint8_t>(), in, d_tables.as<uint8_t>(), d_slots.as<uint8_t>(), d_results.as<EncResult>());
+        if (codec == C_TANS) {
+            CUDA_TRY(d_tlist.alloc(4));
+            CUDA_TRY(cudaMemsetAsync(d_tlist.p, 0, 4, st));  // the list of chunks to code: chunk 0
+            CUDA_TRY(cudaFuncSetAttribute(tans_encode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TENC_SMEM));
+            tans_encode_kernel<<<1, 32, TENC_SMEM, st>>>(d_chunk.as<EncChunk>(), d_tlist.as<uint32_t>(), 1, in, d_tables.as<uint8_t>(), d_slots.as<uint8_t>(), d_results.as<EncResult>());
+        }
         CUDA_TRY(cudaGetLastError());
         EncResult r;
         CUDA_TRY(cudaMemcpyAsync(&r, d_results.p, sizeof(r), cudaMemcpyDeviceToHost, st));
