@@ -1733,7 +1733,7 @@ inline cudaError_t o1sac_allow_shared_tables() {
 }
 
 // ---- stand-alone merge / copy ---------------------------------------------
-constexpr uint32_t MERGE_TILE = 8192;  // elements per CTA
+constexpr uint32_t MERGE_TILE = 32768;  // elements per CTA: one chunk of the default size, so the search for the item is paid once per chunk
 __global__ void __launch_bounds__(256) merge_kernel(const MergeItem* __restrict__ items, const uint32_t* __restrict__ tile_first, uint32_t n_items, Bases bases) {
     // tile_first[i] = first tile index of item i (n_items + 1 entries); find the item by binary search
     uint32_t tile = blockIdx.x;
@@ -1746,20 +1746,73 @@ __global__ void __launch_bounds__(256) merge_kernel(const MergeItem* __restrict_
     const uint8_t* src[4];
     for (int p = 0; p < 4; ++p) src[p] = p < np ? rd(bases, it.src[p]) + base : nullptr;
     uint8_t* dst = wr(bases, it.dst) + base * uint64_t(kind_elem_bytes(int(it.kind)));
-    // groups are aligned to the destination: a short head, full groups, a tail
-    uintptr_t a = reinterpret_cast<uintptr_t>(dst) / uint32_t(kind_elem_bytes(int(it.kind)));
-    uint32_t head = uint32_t((8 - (a & 7)) & 7);
+    // Sixteen elements per thread where the destination allows it: 16 bytes of every plane (two aligned 16-byte loads,
+    // shifted into place; a block that is not wholly inside the plane is read bytewise) and 16 x element size bytes out,
+    // on a boundary of that size.  The elements before the first such boundary and after the last go in groups of eight.
+    const uint32_t eb = uint32_t(kind_elem_bytes(int(it.kind)));
+    const uintptr_t a = reinterpret_cast<uintptr_t>(dst) / eb;
+    uint32_t head = uint32_t((16 - (a & 15)) & 15);
     if (head > n) head = n;
-    uint32_t full = (n - head) >> 3;
-    for (uint32_t gidx = threadIdx.x; gidx < full + 2; gidx += blockDim.x) {
-        uint32_t pos, count;
-        if (gidx == 0) { pos = 0; count = head; }
-        else if (gidx <= full) { pos = head + (gidx - 1) * 8; count = 8; }
-        else { pos = head + full * 8; count = n - pos; }
-        if (count == 0) continue;
+    const uint32_t full = (n - head) >> 4, tail_at = head + full * 16;
+    auto slow = [&](uint32_t begin, uint32_t end) {  // fewer than 16 elements: at most two groups
+        const uint32_t pos = begin + 8 * threadIdx.x;
+        if (pos >= end) return;
+        const uint32_t count = end - pos < 8 ? end - pos : 8;
         uint64_t b[4] = {0, 0, 0, 0};
-        for (int p = 0; p < np; ++p) b[p] = count == 8 ? ld8_unaligned(src[p] + pos) : ld_bytes(src[p] + pos, count);
+        for (int p = 0; p < np; ++p) b[p] = ld_bytes(src[p] + pos, count);
         compose_store(int(it.kind), dst, pos, count, b);
+    };
+    slow(0, head);
+    slow(tail_at, n);
+    uintptr_t p_lo[4] = {0, 0, 0, 0}, p_hi[4] = {0, 0, 0, 0};
+    for (int p = 0; p < np; ++p) { p_lo[p] = reinterpret_cast<uintptr_t>(rd(bases, it.src[p])); p_hi[p] = p_lo[p] + it.n; }
+    for (uint32_t g = threadIdx.x; g < full; g += blockDim.x) {
+        const uint32_t pos = head + g * 16;
+        uint32_t pw[4][4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            if (p >= np) break;
+            const uintptr_t at = reinterpret_cast<uintptr_t>(src[p]) + pos, q = at & ~uintptr_t(15);
+            const uint4 cur = load_block16_guarded(q, p_lo[p], p_hi[p]);
+            const uint32_t off = uint32_t(at & 15);
+            if (off) { const uint4 nxt = load_block16_guarded(q + 16, p_lo[p], p_hi[p]); extract16(cur, nxt, off, pw[p]); }
+            else { pw[p][0] = cur.x; pw[p][1] = cur.y; pw[p][2] = cur.z; pw[p][3] = cur.w; }
+        }
+        uint8_t* out = dst + size_t(pos) * eb;
+        switch (int(it.kind)) {
+            case K_PASS: *reinterpret_cast<uint4*>(out) = make_uint4(pw[0][0], pw[0][1], pw[0][2], pw[0][3]); break;
+            case K_E4M3:
+            case K_E5M2: {
+                const bool e4m3 = it.kind == K_E4M3;
+                *reinterpret_cast<uint4*>(out) = make_uint4(compose_fp8x4(pw[0][0], pw[1][0], e4m3), compose_fp8x4(pw[0][1], pw[1][1], e4m3),
+                                                            compose_fp8x4(pw[0][2], pw[1][2], e4m3), compose_fp8x4(pw[0][3], pw[1][3], e4m3));
+                break;
+            }
+            case K_M16: {
+                uint4 v[2];
+                compose16x4(pw[0][0], pw[1][0], v[0].x, v[0].y); compose16x4(pw[0][1], pw[1][1], v[0].z, v[0].w);
+                compose16x4(pw[0][2], pw[1][2], v[1].x, v[1].y); compose16x4(pw[0][3], pw[1][3], v[1].z, v[1].w);
+                stg256(out, v[0], v[1]);
+                break;
+            }
+            default: {  // K_M32 (transforms/fusion.rs:287-292)
+#pragma unroll
+                for (int k = 0; k < 4; k += 2) {
+                    uint32_t w[8];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t t0 = __byte_perm(pw[0][k + h], pw[1][k + h], 0x5140), t1 = __byte_perm(pw[2][k + h], pw[3][k + h], 0x5140);
+                        const uint32_t t2 = __byte_perm(pw[0][k + h], pw[1][k + h], 0x7362), t3 = __byte_perm(pw[2][k + h], pw[3][k + h], 0x7362);
+                        w[4 * h + 0] = revert32(__byte_perm(t0, t1, 0x5410));
+                        w[4 * h + 1] = revert32(__byte_perm(t0, t1, 0x7632));
+                        w[4 * h + 2] = revert32(__byte_perm(t2, t3, 0x5410));
+                        w[4 * h + 3] = revert32(__byte_perm(t2, t3, 0x7632));
+                    }
+                    stg256(out + 16 * k, make_uint4(w[0], w[1], w[2], w[3]), make_uint4(w[4], w[5], w[6], w[7]));
+                }
+                break;
+            }
+        }
     }
 }
 
