@@ -1238,7 +1238,7 @@ __global__ void __launch_bounds__(TANS_THREADS, 1) tans_decode_kernel(const Deco
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.commit_group;" ::: "memory");  // so that round 0 waits for the group above like any other round
+        asm volatile("cp.async.commit_group;" ::: "memory");  // so that the first round waits for the group above like every later one
         for (uint32_t r = 0; r < max_rounds; ++r) {
             tans_bar_wait(TANS_BAR_FULL + (r & 1));
             const uint32_t b = r & 1;
