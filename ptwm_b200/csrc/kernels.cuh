@@ -1993,8 +1993,11 @@ __global__ void __launch_bounds__(128) crc_planes_kernel(const VerifyTensor* __r
             uint32_t i = 0;
             if (wide) {
                 const uint4* q = reinterpret_cast<const uint4*>(out + first);
+                uint4 ahead = i + 16 <= n ? __ldg(q) : make_uint4(0, 0, 0, 0);  // the next block is on its way while this one is folded in
                 for (; i + 16 <= n; i += 16) {
-                    const uint4 v = __ldg(q++);
+                    const uint4 v = ahead;
+                    ++q;
+                    if (i + 2 * 16 <= n) ahead = __ldg(q);
                     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                     for (int k = 0; k < 16; ++k) c[0] = step(c[0], w[k >> 2] >> (8 * (k & 3)));
@@ -2011,8 +2014,11 @@ __global__ void __launch_bounds__(128) crc_planes_kernel(const VerifyTensor* __r
             uint32_t i = 0;
             if (wide) {
                 const uint4* q = reinterpret_cast<const uint4*>(out + first * 2);
+                uint4 ahead = i + 8 <= n ? __ldg(q) : make_uint4(0, 0, 0, 0);  // the next block is on its way while this one is folded in
                 for (; i + 8 <= n; i += 8) {
-                    const uint4 v = __ldg(q++);
+                    const uint4 v = ahead;
+                    ++q;
+                    if (i + 2 * 8 <= n) ahead = __ldg(q);
                     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {  // two elements per word: the forward reorder of split/dtype16.rs:11-18 on both halves
@@ -2037,8 +2043,11 @@ __global__ void __launch_bounds__(128) crc_planes_kernel(const VerifyTensor* __r
             uint32_t i = 0;
             if (wide) {
                 const uint4* q = reinterpret_cast<const uint4*>(out + first * 4);
+                uint4 ahead = i + 4 <= n ? __ldg(q) : make_uint4(0, 0, 0, 0);  // the next block is on its way while this one is folded in
                 for (; i + 4 <= n; i += 4) {
-                    const uint4 v = __ldg(q++);
+                    const uint4 v = ahead;
+                    ++q;
+                    if (i + 2 * 4 <= n) ahead = __ldg(q);
                     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
@@ -2062,8 +2071,11 @@ __global__ void __launch_bounds__(128) crc_planes_kernel(const VerifyTensor* __r
             uint32_t i = 0;
             if (wide) {
                 const uint4* q = reinterpret_cast<const uint4*>(out + first);
+                uint4 ahead = i + 16 <= n ? __ldg(q) : make_uint4(0, 0, 0, 0);  // the next block is on its way while this one is folded in
                 for (; i + 16 <= n; i += 16) {
-                    const uint4 v = __ldg(q++);
+                    const uint4 v = ahead;
+                    ++q;
+                    if (i + 2 * 16 <= n) ahead = __ldg(q);
                     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                     for (int k = 0; k < 16; ++k) {
