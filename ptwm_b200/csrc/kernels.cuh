@@ -826,12 +826,18 @@ struct HuffCanon {
 };
 // One symbol from the low `max_bits` bits of `window` (stream order, first bit lowest): (length << 8) | symbol.
 // A window that no code covers reads as symbol 0 of full length, like an unassigned slot of the reference's table
-// (huffman/tree.rs:128-177).
-__device__ __forceinline__ uint32_t huff_canon_decode(const HuffCanon& hc, uint32_t max_bits, uint32_t window, uint32_t shortest = 1) {
+// (huffman/tree.rs:128-177).  Kept out of line: the decode loops meet a code longer than the table's window once in a
+// few hundred symbols, and eight inlined copies of this loop per group of eight symbols, in every instance of the
+// group decoder, made the kernel wait for its own instructions.  Four scalar arguments travel in registers; the
+// canonical description (symbols, then first code / count / list offset per length) is addressed from its base.
+__device__ __noinline__ uint32_t huff_canon_decode(const uint8_t* canon, uint32_t max_bits, uint32_t window, uint32_t shortest) {
+    const uint16_t* first = reinterpret_cast<const uint16_t*>(canon + 256);
+    const uint16_t* count = reinterpret_cast<const uint16_t*>(canon + 256 + 32);
+    const uint16_t* offs = reinterpret_cast<const uint16_t*>(canon + 256 + 64);
     const uint32_t v = __brev(window) >> (32 - max_bits);  // code bits, first bit highest
     for (uint32_t len = shortest; len <= max_bits; ++len) {
-        uint32_t d = (v >> (max_bits - len)) - hc.first[len];
-        if (d < hc.count[len]) return (len << 8) | hc.syms[hc.offs[len] + d];
+        uint32_t d = (v >> (max_bits - len)) - first[len];
+        if (d < count[len]) return (len << 8) | canon[offs[len] + d];
     }
     return max_bits << 8;
 }
@@ -1016,7 +1022,7 @@ __global__ void __launch_bounds__(32) huffman_decode_kernel(const DecodeItem* __
         // (length << 8) | symbol of the next code, without consuming it
         auto peek = [&]() -> uint32_t {
             uint32_t e = lut[c_lo & ((1u << HUF_LUT_BITS) - 1)];
-            if (e == 0) e = huff_canon_decode(hc, max_bits, c_lo & mask, HUF_LUT_BITS + 1);  // the rarest symbols, or a window no code covers
+            if (e == 0) e = huff_canon_decode(hc.syms, max_bits, c_lo & mask, HUF_LUT_BITS + 1);  // the rarest symbols, or a window no code covers
             return e;
         };
         // one symbol with the reference's checks (decompress.rs:176-196)
